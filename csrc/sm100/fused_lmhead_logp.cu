@@ -1,0 +1,764 @@
+// Fused LM-head + log-probability kernel for sm_100a.
+//
+//   logp[r] = scale * <H[r,:], W[ids[r],:]>  -  logsumexp_v( scale * <H[r,:], W[v,:]> )
+//
+// H is [M, K] bf16 (row-major), W is this rank's vocabulary shard [V_local, K] bf16
+// (row-major); the [M, V] logits are never written to memory. bf16 tiles are brought in by
+// TMA, multiplied by tcgen05.mma into fp32 accumulators in TMEM, and the epilogue warps keep
+// a running (max, sum-exp, target-logit) per row straight out of TMEM.
+//
+// Reproducibility contract (per row, bitwise):
+//   * the global vocabulary is cut into 8 canonical slices of ceil(V/8) columns, each slice
+//     into sub-slices of 2048 columns, each sub-slice into 256-column MMA tiles;
+//   * one thread owns one row of one sub-slice and folds its tiles left to right;
+//   * sub-slices of a slice are merged left to right, the 8 slices by a balanced binary
+//     tree. A rank that holds 8/N contiguous slices evaluates a whole subtree locally and the
+//     top log2(N) levels after the exchange, so 1, 2, 4 and 8 GPUs run the same arithmetic.
+//   Nothing depends on M, on which CTA processed a tile, or on arrival order.
+//
+// Multi-GPU: after a rank has merged its slices for a 128-row block it stores the block's
+// (max, sum-exp, target) triples into every peer's exchange buffer with plain peer stores,
+// then releases a per-(source rank, block) flag; each rank finishes the blocks it pushed by
+// waiting (bounded) for the other ranks' flags and running the top of the tree.
+//
+// Replaces the reference's `torch.matmul` + `SamplerBackend.compute_logp`
+// (rl_engine/kernels/sampling.py:91-112), which materialises [G, L, V] logits twice.
+
+#include <cfloat>
+#include <cstdint>
+#include <cstdio>
+#include <cuda_bf16.h>
+#include <math_constants.h>
+
+#include "common/bounded_wait.cuh"
+#include "common/ptx.cuh"
+#include "common/tmap.cuh"
+#include "fused_lmhead_logp.h"
+
+namespace ka {
+namespace {
+
+constexpr int kBM = 128;         // rows per CTA (TMEM lanes)
+constexpr int kBN = 256;         // columns per MMA tile
+constexpr int kBK = 64;          // bf16 elements per 128-byte swizzled row
+constexpr int kUmmaK = 16;       // K per tcgen05.mma of kind::f16
+constexpr int kSubCols = 2048;   // columns per canonical sub-slice (8 tiles)
+constexpr int kSlices = 8;       // canonical slices of the global vocabulary
+constexpr int kThreads = 192;    // warps 0-3 epilogue, 4 TMA producer, 5 MMA issuer
+constexpr int kMaxDeferred = 512;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+template <int G>
+struct Cfg {
+  static constexpr int kBRows = kBN / G;                 // W rows each CTA loads per stage
+  static constexpr int kABytes = kBM * kBK * 2;          // 16 KiB
+  static constexpr int kBBytes = kBRows * kBK * 2;       // 32 KiB (G=1) or 16 KiB (G=2)
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = (G == 1) ? 4 : 6;
+  static constexpr int kTxBytes = kStageBytes * G;       // bytes counted on the leader's barrier
+  static constexpr int kTileBytes = kStages * kStageBytes;
+  static constexpr int kSmemBytes = kTileBytes + 1024 /*alignment*/ + 2048 /*control*/;
+};
+
+struct Control {
+  uint64_t full[8];
+  uint64_t empty[8];
+  uint64_t tfull[2];
+  uint64_t tempty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+  int is_last;
+  int n_deferred;
+  uint16_t deferred[kMaxDeferred];
+};
+static_assert(sizeof(Control) <= 2048, "control block too large");
+
+enum Where : int {
+  kWhereProducerEmpty = 1,
+  kWhereMmaFull = 2,
+  kWhereMmaTmemEmpty = 3,
+  kWhereEpiTmemFull = 4,
+  kWherePeerFlag = 5
+};
+
+struct Item {
+  int m_tile;
+  int chunk;
+  int col_begin;
+  int col_end;
+  int n_tiles;
+};
+
+__device__ __forceinline__ void decode_item(const LogpParams& p, int i, Item& it) {
+  const int per_group = p.mg * p.n_chunks;
+  const int g = i / per_group;
+  const int mg_sz = min(p.mg, p.n_mtiles - g * p.mg);
+  const int r = i - g * per_group;
+  const int h = r / (mg_sz * p.cg);
+  const int cg_sz = min(p.cg, p.n_chunks - h * p.cg);
+  const int r2 = r - h * mg_sz * p.cg;
+  const int m_local = r2 / cg_sz;
+  const int c_local = r2 - m_local * cg_sz;
+  it.m_tile = g * p.mg + m_local;
+  it.chunk = h * p.cg + c_local;
+  const int sl = it.chunk / p.sub;
+  const int q = it.chunk - sl * p.sub;
+  const int slice_begin = sl * p.vs;
+  const int slice_end = min(slice_begin + p.vs, p.v_local);
+  it.col_begin = slice_begin + q * kSubCols;
+  it.col_end = min(it.col_begin + kSubCols, slice_end);
+  it.n_tiles = it.col_end > it.col_begin ? (it.col_end - it.col_begin + kBN - 1) / kBN : 0;
+}
+
+// (m, l) describes sum_j exp(x_j) = l * exp(scale * m) with m the running maximum of the raw
+// accumulator values. s2 = scale * log2(e). The arithmetic is spelled with explicit
+// intrinsics so that every call site rounds identically.
+__device__ __forceinline__ void merge2(float& m, float& l, float m2, float l2, float s2) {
+  const float mn = fmaxf(m, m2);
+  const float a = (m == -CUDART_INF_F) ? 0.f : ex2_approx(__fmul_rn(__fsub_rn(m, mn), s2));
+  const float b = (m2 == -CUDART_INF_F) ? 0.f : ex2_approx(__fmul_rn(__fsub_rn(m2, mn), s2));
+  l = __fadd_rn(__fmul_rn(l, a), __fmul_rn(l2, b));
+  m = mn;
+}
+
+__device__ __forceinline__ void tmem_ld_wait_dep(uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.wait::ld.sync.aligned;"
+      : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]),
+        "+r"(v[7]), "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]),
+        "+r"(v[14]), "+r"(v[15]), "+r"(v[16]), "+r"(v[17]), "+r"(v[18]), "+r"(v[19]),
+        "+r"(v[20]), "+r"(v[21]), "+r"(v[22]), "+r"(v[23]), "+r"(v[24]), "+r"(v[25]),
+        "+r"(v[26]), "+r"(v[27]), "+r"(v[28]), "+r"(v[29]), "+r"(v[30]), "+r"(v[31])
+      :
+      : "memory");
+}
+
+// Fold 32 consecutive columns of one row into the running state.
+//   col0   first column of the group inside the tile
+//   valid  number of real columns in the tile (the rest is masked out)
+//   tcol   target column inside the tile, or a negative / large value if not in the tile
+__device__ __forceinline__ void fold32(const uint32_t (&v)[32], int col0, int valid, int tcol,
+                                       float s2, float& m, float& l, float& t) {
+  float x[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(v[j]);
+  if (col0 + 32 > valid) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (col0 + j >= valid) x[j] = -CUDART_INF_F;
+  }
+  const int tj = tcol - col0;
+  if (static_cast<unsigned>(tj) < 32u) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j == tj) t = x[j];
+  }
+  float c0 = fmaxf(x[0], x[1]), c1 = fmaxf(x[2], x[3]), c2 = fmaxf(x[4], x[5]),
+        c3 = fmaxf(x[6], x[7]);
+#pragma unroll
+  for (int j = 8; j < 32; j += 8) {
+    c0 = fmaxf(c0, fmaxf(x[j], x[j + 1]));
+    c1 = fmaxf(c1, fmaxf(x[j + 2], x[j + 3]));
+    c2 = fmaxf(c2, fmaxf(x[j + 4], x[j + 5]));
+    c3 = fmaxf(c3, fmaxf(x[j + 6], x[j + 7]));
+  }
+  const float mn = fmaxf(m, fmaxf(fmaxf(c0, c1), fmaxf(c2, c3)));
+  // Exponents are taken relative to R(m) = round(m * s2); the running sum is rescaled by
+  // 2^(R(m_old) - R(m_new)), which is exactly 1 when the maximum did not move and 0 when
+  // m_old is -inf.
+  const float neg_old = __fmul_rn(-m, s2);
+  const float neg = __fmul_rn(-mn, s2);
+  const float corr = ex2_approx(__fsub_rn(neg, neg_old));
+  float s0 = 0.f, s1 = 0.f, s2a = 0.f, s3 = 0.f;
+#pragma unroll
+  for (int j = 0; j < 32; j += 4) {
+    s0 = __fadd_rn(s0, ex2_approx(__fmaf_rn(x[j], s2, neg)));
+    s1 = __fadd_rn(s1, ex2_approx(__fmaf_rn(x[j + 1], s2, neg)));
+    s2a = __fadd_rn(s2a, ex2_approx(__fmaf_rn(x[j + 2], s2, neg)));
+    s3 = __fadd_rn(s3, ex2_approx(__fmaf_rn(x[j + 3], s2, neg)));
+  }
+  const float gs = __fadd_rn(__fadd_rn(s0, s1), __fadd_rn(s2a, s3));
+  l = __fmaf_rn(l, corr, gs);
+  m = mn;
+}
+
+__device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// Merge this rank's sub-slice partials of one row: chains inside each slice, then the local
+// subtree. Leaves (m_out, l_out) as the rank's partial.
+__device__ __forceinline__ void merge_local(const LogpParams& p, int rp, float s2, float& m_out,
+                                            float& l_out) {
+  float lm[kSlices], ll[kSlices];
+#pragma unroll
+  for (int sl = 0; sl < kSlices; ++sl) {
+    lm[sl] = -CUDART_INF_F;
+    ll[sl] = 0.f;
+  }
+#pragma unroll
+  for (int sl = 0; sl < kSlices; ++sl) {
+    if (sl < p.n_slices_local) {
+      const size_t base = static_cast<size_t>(sl) * p.sub;
+      float m = __ldcg(p.part_m + (base + 0) * p.ldp + rp);
+      float l = __ldcg(p.part_l + (base + 0) * p.ldp + rp);
+      for (int q = 1; q < p.sub; ++q) {
+        const float m2 = __ldcg(p.part_m + (base + q) * p.ldp + rp);
+        const float l2 = __ldcg(p.part_l + (base + q) * p.ldp + rp);
+        merge2(m, l, m2, l2, s2);
+      }
+      lm[sl] = m;
+      ll[sl] = l;
+    }
+  }
+#pragma unroll
+  for (int w = kSlices; w > 1; w >>= 1) {
+    if (w <= p.n_slices_local) {
+#pragma unroll
+      for (int i = 0; i < w / 2; ++i) {
+        float m = lm[2 * i], l = ll[2 * i];
+        merge2(m, l, lm[2 * i + 1], ll[2 * i + 1], s2);
+        lm[i] = m;
+        ll[i] = l;
+      }
+    }
+  }
+  m_out = lm[0];
+  l_out = ll[0];
+}
+
+__device__ __forceinline__ void write_result(const LogpParams& p, int row, float m, float l, float t,
+                                             bool has_t, bool id_ok) {
+  // lse = scale*m + ln(l); logp = scale*t - lse
+  const float lse = __fmaf_rn(lg2_approx(l), kLn2, __fmul_rn(m, p.scale));
+  if (p.lse) p.lse[row] = lse;
+  p.logp[row] = (id_ok && has_t) ? __fsub_rn(__fmul_rn(t, p.scale), lse) : 0.f;
+}
+
+template <int G>
+__global__ void __launch_bounds__(kThreads, 1)
+fused_lmhead_logp_kernel(const __grid_constant__ CUtensorMap tm_h,
+                         const __grid_constant__ CUtensorMap tm_w,
+                         const __grid_constant__ LogpParams p) {
+  using C = Cfg<G>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t tiles_addr = (raw_addr + 1023u) & ~1023u;
+  uint8_t* tiles = smem_raw + (tiles_addr - raw_addr);
+  Control* ctl = reinterpret_cast<Control*>(tiles + C::kTileBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = (G == 2) ? cluster_ctarank() : 0u;
+  const bool leader = (cta_rank == 0);
+  const int pair_id = blockIdx.x / G;
+  const int n_pairs = gridDim.x / G;
+  const int n_items = p.n_mtiles * p.n_chunks;
+  const int num_kb = (p.k + kBK - 1) / kBK;
+  const float s2 = p.scale * kLog2e;
+
+  WaitCtx wctx{&ctl->abort_flag, p.status, p.timeout_ns};
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(smem_u32(&ctl->full[s]), 1);
+      mbar_init(smem_u32(&ctl->empty[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&ctl->tfull[b]), 1);
+      mbar_init(smem_u32(&ctl->tempty[b]), 4 * G);
+    }
+    ctl->abort_flag = 0;
+    ctl->is_last = 0;
+    ctl->n_deferred = 0;
+    fence_mbar_init_cluster();
+  }
+  if (warp == 5) {
+    tmem_alloc<G>(smem_u32(&ctl->tmem_base), 512);
+    tmem_relinquish<G>();
+  }
+  if (warp == 4 && lane == 0) {
+    tma_prefetch_desc(&tm_h);
+    tma_prefetch_desc(&tm_w);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if constexpr (G == 2) {
+    cluster_arrive();
+    cluster_wait();
+  }
+  tc_fence_after_sync();
+  const uint32_t tmem_base = ctl->tmem_base;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int i = pair_id; i < n_items && ok; i += n_pairs) {
+        Item it;
+        decode_item(p, i, it);
+        const int row0 = p.row_begin + it.m_tile * (kBM * G) + static_cast<int>(cta_rank) * kBM;
+        for (int nt = 0; nt < it.n_tiles && ok; ++nt) {
+          const int n0 = it.col_begin + nt * kBN;
+          for (int kb = 0; kb < num_kb; ++kb) {
+            ok = mbar_wait_bounded(smem_u32(&ctl->empty[stage]), phase ^ 1u, wctx,
+                                   kWhereProducerEmpty, stage);
+            if (!ok) break;
+            const uint32_t a_dst = tiles_addr + stage * C::kStageBytes;
+            const uint32_t b_dst = a_dst + C::kABytes;
+            const uint32_t full = smem_u32(&ctl->full[stage]);
+            if constexpr (G == 1) {
+              mbar_arrive_expect_tx(full, C::kTxBytes);
+              tma_load_2d(a_dst, &tm_h, kb * kBK, row0, full);
+              tma_load_2d(b_dst, &tm_w, kb * kBK, n0, full);
+              tma_load_2d(b_dst + 128 * kBK * 2, &tm_w, kb * kBK, n0 + 128, full);
+            } else {
+              if (leader) mbar_arrive_expect_tx(full, C::kTxBytes);
+              const uint32_t full_leader = mapa_u32(full, 0);
+              tma_load_2d_pair(a_dst, &tm_h, kb * kBK, row0, full_leader);
+              tma_load_2d_pair(b_dst, &tm_w, kb * kBK, n0 + static_cast<int>(cta_rank) * C::kBRows,
+                               full_leader);
+            }
+            if (++stage == C::kStages) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = umma_idesc_bf16_f32(kBM * G, kBN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int abuf = 0;
+      uint32_t aphase = 0;
+      bool ok = true;
+      for (int i = pair_id; i < n_items && ok; i += n_pairs) {
+        Item it;
+        decode_item(p, i, it);
+        for (int nt = 0; nt < it.n_tiles && ok; ++nt) {
+          ok = mbar_wait_bounded(smem_u32(&ctl->tempty[abuf]), aphase ^ 1u, wctx,
+                                 kWhereMmaTmemEmpty, abuf);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(abuf * kBN);
+          for (int kb = 0; kb < num_kb; ++kb) {
+            ok = mbar_wait_bounded(smem_u32(&ctl->full[stage]), phase, wctx, kWhereMmaFull, stage);
+            if (!ok) break;
+            tc_fence_after_sync();
+            const uint32_t a_addr = tiles_addr + stage * C::kStageBytes;
+            const uint64_t a_desc = umma_desc_k_sw128(a_addr);
+            const uint64_t b_desc = umma_desc_k_sw128(a_addr + C::kABytes);
+#pragma unroll
+            for (int k = 0; k < kBK / kUmmaK; ++k) {
+              // advancing K by 16 bf16 = 32 bytes = 2 units of the 16-byte address field
+              umma_bf16<G>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc,
+                           (kb > 0 || k > 0) ? 1u : 0u);
+            }
+            umma_commit<G>(smem_u32(&ctl->empty[stage]));
+            if (++stage == C::kStages) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
+          if (!ok) break;
+          umma_commit<G>(smem_u32(&ctl->tfull[abuf]));
+          abuf ^= 1;
+          if (abuf == 0) aphase ^= 1u;
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 0-3)
+    // Control flow rule: every named-barrier call below is reached by all 128 threads; a
+    // failed wait only skips work, and the decision to leave is taken from the shared abort
+    // flag right after a barrier, so it is uniform.
+    const int tid = threadIdx.x;  // 0..127 == TMEM lane == row inside the CTA's 128-row block
+    int abuf = 0;
+    uint32_t aphase = 0;
+    bool ok = true;
+    const uint32_t tempty_leader_base =
+        (G == 2) ? mapa_u32(smem_u32(&ctl->tempty[0]), 0) : smem_u32(&ctl->tempty[0]);
+    for (int i = pair_id; i < n_items; i += n_pairs) {
+      Item it;
+      decode_item(p, i, it);
+      const int blk = it.m_tile * G + static_cast<int>(cta_rank);  // 128-row block in the panel
+      const int rp = blk * kBM + tid;                              // row inside the panel
+      const int row = p.row_begin + rp;                            // global row
+      const bool row_ok = rp < p.rows;
+      long long id = -1;
+      if (row_ok) id = p.ids[row];
+      const bool id_ok = id >= 0 && id < static_cast<long long>(p.v_global);
+      const long long lid = id - p.vocab_offset;  // column inside this rank's shard
+      const bool t_here = id_ok && lid >= it.col_begin && lid < it.col_end;
+      const int tcol_item = t_here ? static_cast<int>(lid) - it.col_begin : -(1 << 30);
+
+      float m = -CUDART_INF_F, l = 0.f, t = 0.f;
+      for (int nt = 0; nt < it.n_tiles; ++nt) {
+        const bool mine = mbar_wait_bounded(smem_u32(&ctl->tfull[abuf]), aphase, wctx,
+                                            kWhereEpiTmemFull, abuf);
+        ok = __all_sync(0xffffffffu, mine) != 0;  // warp-uniform: tcgen05.ld needs convergence
+        if (!ok) break;
+        tc_fence_after_sync();
+        const int valid = min(kBN, it.col_end - (it.col_begin + nt * kBN));
+        const int tcol = tcol_item - nt * kBN;
+        const uint32_t trow = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) +
+                              static_cast<uint32_t>(abuf * kBN);
+        uint32_t va[32], vb[32];
+        tmem_ld_32x32(trow, va);
+        tmem_ld_wait_dep(va);
+#pragma unroll
+        for (int g = 0; g < kBN / 32; g += 2) {
+          __syncwarp();
+          tmem_ld_32x32(trow + (g + 1) * 32, vb);
+          if (g * 32 < valid) fold32(va, g * 32, valid, tcol, s2, m, l, t);
+          __syncwarp();
+          tmem_ld_wait_dep(vb);
+          if (g + 2 < kBN / 32) tmem_ld_32x32(trow + (g + 2) * 32, va);
+          if ((g + 1) * 32 < valid) fold32(vb, (g + 1) * 32, valid, tcol, s2, m, l, t);
+          __syncwarp();
+          if (g + 2 < kBN / 32) tmem_ld_wait_dep(va);
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          if constexpr (G == 2)
+            mbar_arrive_cluster(tempty_leader_base + static_cast<uint32_t>(abuf) * 8u);
+          else
+            mbar_arrive(tempty_leader_base + static_cast<uint32_t>(abuf) * 8u);
+        }
+        abuf ^= 1;
+        if (abuf == 0) aphase ^= 1u;
+      }
+
+      // ---- publish the sub-slice partial, find out whether this block is complete locally
+      if (ok && row_ok) {
+        p.part_m[static_cast<size_t>(it.chunk) * p.ldp + rp] = m;
+        p.part_l[static_cast<size_t>(it.chunk) * p.ldp + rp] = l;
+        if (t_here) p.tgt[rp] = t;
+      }
+      __threadfence();
+      epi_bar();
+      if (ctl->abort_flag) {  // uniform: read after the barrier, set before it
+        ok = false;
+        break;
+      }
+      if (tid == 0) {
+        const unsigned prev = atomicAdd(&p.counters[blk], 1u);
+        const int last = (prev + 1u == static_cast<unsigned>(p.n_chunks)) ? 1 : 0;
+        if (last) p.counters[blk] = 0u;  // self-cleaning for the next launch
+        ctl->is_last = last;
+      }
+      epi_bar();
+      const bool is_last = ctl->is_last != 0;
+      if (is_last) {
+        __threadfence();
+        const bool has_t = id_ok && lid >= 0 && lid < static_cast<long long>(p.v_local);
+        float mm = -CUDART_INF_F, ml = 0.f, mt = 0.f;
+        if (row_ok) {
+          merge_local(p, rp, s2, mm, ml);
+          if (has_t) mt = __ldcg(p.tgt + rp);
+        }
+        if (p.world == 1) {
+          if (row_ok) write_result(p, row, mm, ml, mt, has_t, id_ok);
+        } else {
+          const size_t slot = (static_cast<size_t>(p.epoch & 1u) * p.world + p.rank) * p.ldp + rp;
+          const float4 v = make_float4(mm, ml, mt, has_t ? 1.f : 0.f);
+          if (row_ok) {
+            for (int d = 0; d < p.world; ++d) st_relaxed_sys_f4(p.xbuf[d] + slot, v);
+          }
+          __threadfence_system();
+          epi_bar();
+          if (tid < p.world) {
+            st_release_sys_u32(p.xflag[tid] + static_cast<size_t>(p.rank) * p.n_blocks_max + blk,
+                               p.epoch);
+          }
+          if (tid == 0) {
+            const int n = ctl->n_deferred;
+            if (n < kMaxDeferred) {
+              ctl->deferred[n] = static_cast<uint16_t>(blk);
+              ctl->n_deferred = n + 1;
+            } else {
+              report_failure(wctx, kBadArgument, kWherePeerFlag, blk, n, 0);
+            }
+          }
+        }
+      }
+      epi_bar();  // is_last and the deferred list are reused by the next item
+    }
+
+    // ---- cross-rank finish: top of the tree for the blocks this CTA pushed
+    if (p.world > 1 && ok) {
+      const int n_def = ctl->n_deferred;
+      for (int d = 0; d < n_def; ++d) {
+        const int blk = ctl->deferred[d];
+        if (tid < p.world) {
+          flag_wait_bounded(p.xflag[p.rank] + static_cast<size_t>(tid) * p.n_blocks_max + blk, p.epoch,
+                            wctx, kWherePeerFlag, blk);
+        }
+        epi_bar();
+        if (ctl->abort_flag) break;  // uniform, as above
+        const int rp = blk * kBM + tid;
+        const int row = p.row_begin + rp;
+        if (rp < p.rows) {
+          float lm[kSlices], ll[kSlices];
+          float t = 0.f;
+          bool has_t = false;
+#pragma unroll
+          for (int r = 0; r < kSlices; ++r) {
+            lm[r] = -CUDART_INF_F;
+            ll[r] = 0.f;
+            if (r < p.world) {
+              const size_t slot = (static_cast<size_t>(p.epoch & 1u) * p.world + r) * p.ldp + rp;
+              const float4 v = ld_relaxed_sys_f4(p.xbuf[p.rank] + slot);
+              lm[r] = v.x;
+              ll[r] = v.y;
+              if (v.w != 0.f) {
+                t = v.z;
+                has_t = true;
+              }
+            }
+          }
+#pragma unroll
+          for (int w = kSlices; w > 1; w >>= 1) {
+            if (w <= p.world) {
+#pragma unroll
+              for (int i = 0; i < w / 2; ++i) {
+                float m = lm[2 * i], l = ll[2 * i];
+                merge2(m, l, lm[2 * i + 1], ll[2 * i + 1], s2);
+                lm[i] = m;
+                ll[i] = l;
+              }
+            }
+          }
+          const long long id = p.ids[row];
+          const bool id_ok = id >= 0 && id < static_cast<long long>(p.v_global);
+          write_result(p, row, lm[0], ll[0], t, has_t, id_ok);
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ common exit
+  if (ctl->abort_flag) {
+    if constexpr (G == 2) {
+      // make the peer CTA leave its waits too
+      st_shared_cluster_u32(mapa_u32(smem_u32(&ctl->abort_flag), cta_rank ^ 1u), 1u);
+    }
+    drain_in_flight();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if constexpr (G == 2) {
+    cluster_arrive();
+    cluster_wait();
+  }
+  if (warp == 5) {
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc<G>(tmem_base, 512);
+  }
+}
+
+template <int G>
+int max_ctas(int num_sms) {
+  static int cached[2] = {0, 0};
+  if (cached[G - 1] > 0) return cached[G - 1];
+  using C = Cfg<G>;
+  auto* kern = fused_lmhead_logp_kernel<G>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) !=
+      cudaSuccess)
+    return -1;
+  int n = num_sms;
+  if (G == 2) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(num_sms / 2 * 2));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = C::kSmemBytes;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, kern, &cfg) != cudaSuccess || clusters <= 0) {
+      cudaGetLastError();
+      clusters = num_sms / 2;
+    }
+    n = clusters * 2;
+    if (n > num_sms / 2 * 2) n = num_sms / 2 * 2;
+  }
+  cached[G - 1] = n;
+  return n;
+}
+
+template <int G>
+int launch_panel(const CUtensorMap& tm_h, const CUtensorMap& tm_w, const LogpParams& p, int num_sms,
+                 cudaStream_t stream) {
+  using C = Cfg<G>;
+  int ctas = max_ctas<G>(num_sms);
+  if (ctas <= 0) return -10;
+  const int n_items = p.n_mtiles * p.n_chunks;
+  if (n_items * G < ctas) ctas = n_items * G;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(ctas));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = C::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = G;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, fused_lmhead_logp_kernel<G>, tm_h, tm_w, p);
+  if (e != cudaSuccess) {
+    fprintf(stderr, "[kernel_align_b200] fused_lmhead_logp launch failed: %s\n", cudaGetErrorString(e));
+    return -11;
+  }
+  return 0;
+}
+
+}  // namespace
+}  // namespace ka
+
+extern "C" {
+
+// See fused_lmhead_logp.h for the contract.
+static size_t ka_ws_status_offset(int v_global, int panel_rows) {
+  const int vs = (v_global + ka::kSlices - 1) / ka::kSlices;
+  const int sub = (vs + ka::kSubCols - 1) / ka::kSubCols;
+  const size_t ldp = static_cast<size_t>(panel_rows);
+  const size_t n_chunks = static_cast<size_t>(ka::kSlices) * sub;  // upper bound (world == 1)
+  const size_t n_blocks = ldp / ka::kBM;
+  size_t bytes = 2 * n_chunks * ldp * sizeof(float);  // part_m, part_l
+  bytes += ldp * sizeof(float);                       // tgt
+  bytes += n_blocks * sizeof(unsigned);               // counters
+  return (bytes + 255) / 256 * 256;
+}
+
+size_t ka_lmhead_logp_workspace_bytes(int v_global, int panel_rows) {
+  return ka_ws_status_offset(v_global, panel_rows) + 256;
+}
+
+size_t ka_lmhead_logp_exchange_bytes(int world, int panel_rows) {
+  const size_t ldp = static_cast<size_t>(panel_rows);
+  const size_t n_blocks = ldp / ka::kBM;
+  const size_t xbuf = 2 * static_cast<size_t>(world) * ldp * sizeof(float4);
+  const size_t xflag = static_cast<size_t>(world) * n_blocks * sizeof(unsigned);
+  return xbuf + (xflag + 255) / 256 * 256;
+}
+
+int ka_lmhead_logp_status_offset(int v_global, int panel_rows) {
+  return static_cast<int>(ka_ws_status_offset(v_global, panel_rows));
+}
+
+int ka_lmhead_logp_forward(const void* hidden, const void* weight, const long long* ids, float* logp,
+                           float* lse, void* workspace, size_t workspace_bytes, void* const* peer_exchange,
+                           int m, int k, int v_global, int v_local, int vocab_offset, int world, int rank,
+                           unsigned epoch_base, float scale, int panel_rows, int cta_group, int num_sms,
+                           unsigned long long timeout_ns, void* stream_ptr) {
+  using namespace ka;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  if (m <= 0) return 0;
+  if (k % 8 != 0 || k <= 0) return -1;
+  if (!(world == 1 || world == 2 || world == 4 || world == 8) || rank < 0 || rank >= world) return -2;
+  if (!(scale > 0.f)) return -3;
+  if (cta_group != 1 && cta_group != 2) return -4;
+  if (panel_rows <= 0 || panel_rows % 256 != 0) return -5;
+  if (workspace_bytes < ka_lmhead_logp_workspace_bytes(v_global, panel_rows)) return -6;
+  if (world > 1 && peer_exchange == nullptr) return -7;
+
+  const int vs = (v_global + kSlices - 1) / kSlices;
+  const int sub = (vs + kSubCols - 1) / kSubCols;
+  const int n_slices_local = kSlices / world;
+  if (vocab_offset != rank * n_slices_local * vs) return -8;
+  {
+    const long long hi = static_cast<long long>(rank + 1) * n_slices_local * vs;
+    const long long end = hi < v_global ? hi : v_global;
+    const long long expect = end - vocab_offset > 0 ? end - vocab_offset : 0;
+    if (v_local != expect) return -9;
+  }
+  const size_t ldp = static_cast<size_t>(panel_rows);
+  const size_t n_blocks_max = ldp / kBM;
+  if (n_blocks_max > 65535) return -12;
+
+  LogpParams p = {};
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  const size_t n_chunks_max = static_cast<size_t>(kSlices) * sub;
+  p.part_m = reinterpret_cast<float*>(ws);
+  p.part_l = p.part_m + n_chunks_max * ldp;
+  p.tgt = p.part_l + n_chunks_max * ldp;
+  p.counters = reinterpret_cast<unsigned*>(p.tgt + ldp);
+  p.status = reinterpret_cast<int*>(ws + ka_lmhead_logp_status_offset(v_global, panel_rows));
+  for (int d = 0; d < 8; ++d) {
+    p.xbuf[d] = nullptr;
+    p.xflag[d] = nullptr;
+  }
+  if (world > 1) {
+    const size_t xbuf_bytes = 2 * static_cast<size_t>(world) * ldp * sizeof(float4);
+    for (int d = 0; d < world; ++d) {
+      uint8_t* base = static_cast<uint8_t*>(peer_exchange[d]);
+      if (!base) return -7;
+      p.xbuf[d] = reinterpret_cast<float4*>(base);
+      p.xflag[d] = reinterpret_cast<unsigned*>(base + xbuf_bytes);
+    }
+  }
+  p.ids = ids;
+  p.logp = logp;
+  p.lse = lse;
+  p.m = m;
+  p.k = k;
+  p.v_global = v_global;
+  p.v_local = v_local;
+  p.vocab_offset = vocab_offset;
+  p.vs = vs;
+  p.sub = sub;
+  p.n_slices_local = n_slices_local;
+  p.n_chunks = n_slices_local * sub;
+  p.ldp = static_cast<int>(ldp);
+  p.n_blocks_max = static_cast<int>(n_blocks_max);
+  p.world = world;
+  p.rank = rank;
+  p.scale = scale;
+  p.timeout_ns = timeout_ns;
+  p.cg = p.n_chunks < 8 ? p.n_chunks : 8;
+  {
+    const int pairs = num_sms / cta_group;
+    int mg = pairs / p.cg;
+    if (mg < 1) mg = 1;
+    p.mg = mg;
+  }
+
+  CUtensorMap tm_h, tm_w;
+  int rc = make_tmap_2d_16bit_sw128(&tm_h, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, hidden, static_cast<uint64_t>(m),
+                                    static_cast<uint64_t>(k), static_cast<uint64_t>(k), kBM, kBK);
+  if (rc != 0) return -20 + rc;
+  rc = make_tmap_2d_16bit_sw128(&tm_w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, weight,
+                                static_cast<uint64_t>(v_local > 0 ? v_local : 1), static_cast<uint64_t>(k),
+                                static_cast<uint64_t>(k), 128, kBK);
+  if (rc != 0) return -40 + rc;
+
+  const int rows_per_mtile = kBM * cta_group;
+  unsigned epoch = epoch_base;
+  for (int row_begin = 0; row_begin < m; row_begin += panel_rows) {
+    const int rows = (m - row_begin) < panel_rows ? (m - row_begin) : panel_rows;
+    p.row_begin = row_begin;
+    p.rows = rows;
+    p.n_mtiles = (rows + rows_per_mtile - 1) / rows_per_mtile;
+    p.epoch = epoch++;
+    rc = (cta_group == 1) ? launch_panel<1>(tm_h, tm_w, p, num_sms, stream)
+                          : launch_panel<2>(tm_h, tm_w, p, num_sms, stream);
+    if (rc != 0) return rc;
+  }
+  return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,60 @@
+"""ctypes bindings to the two in-tree native libraries.
+
+``cuda()`` returns the sm_100a kernel library and raises if it is missing: on a GPU host the
+hand-written kernels are the only code path, there is no silent PyTorch fallback.
+``cpu()`` returns the C++ CPU library (oracle for the tests and the CPU device path).
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p, c_float, c_int, c_longlong, c_size_t, c_uint, c_ulonglong, c_void_p
+from functools import lru_cache
+
+from . import _build
+
+
+class NativeLibraryMissing(RuntimeError):
+    pass
+
+
+def _bind(lib, name, restype, argtypes):
+    fn = getattr(lib, name)
+    fn.restype = restype
+    fn.argtypes = argtypes
+    return fn
+
+
+@lru_cache(maxsize=None)
+def cuda() -> ctypes.CDLL:
+    path = _build.build_cuda()
+    if path is None or not path.exists():
+        raise NativeLibraryMissing(
+            "libka_sm100.so is not built; run `python -m kernel_align_b200._build` on a host with nvcc"
+        )
+    lib = ctypes.CDLL(str(path))
+    _bind(lib, "ka_lmhead_logp_workspace_bytes", c_size_t, [c_int, c_int])
+    _bind(lib, "ka_lmhead_logp_status_offset", c_int, [c_int, c_int])
+    _bind(lib, "ka_lmhead_logp_exchange_bytes", c_size_t, [c_int, c_int])
+    _bind(
+        lib,
+        "ka_lmhead_logp_forward",
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p,
+         c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+         c_uint, c_float, c_int, c_int, c_int, c_ulonglong, c_void_p],
+    )
+    return lib
+
+
+@lru_cache(maxsize=None)
+def cpu() -> ctypes.CDLL:
+    path = _build.build_cpu()
+    if path is None or not path.exists():
+        raise NativeLibraryMissing("libka_cpu.so is not built and no C++ compiler is available")
+    return ctypes.CDLL(str(path))
+
+
+def cuda_available() -> bool:
+    import torch
+
+    return torch.cuda.is_available()

@@ -1,0 +1,197 @@
+"""Fused LM-head + per-token log-probability.
+
+``lmhead_logp(hidden, weight, ids)`` returns ``log_softmax(scale * hidden @ weight.T)[ids]``
+without ever materialising the ``[rows, vocab]`` logits. On CUDA it runs the hand-written
+tcgen05/TMA kernel of ``csrc/sm100/fused_lmhead_logp.cu``; on CPU the C++ implementation of
+``csrc/cpu/fused_logp_cpu.cpp``. Both follow the same canonical decomposition of the
+vocabulary (8 slices, 2048-column sub-slices, balanced merge tree), so a row's result does
+not depend on the batch it was computed in, nor on how many GPUs the vocabulary is sharded
+over.
+
+The reference computes the same quantity from materialised logits
+(rl_engine/kernels/sampling.py:91-112, ``SamplerBackend.compute_logp``).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from dataclasses import dataclass, field
+from typing import Optional
+
+import torch
+
+from .. import _native
+
+N_SLICES = 8
+DEFAULT_PANEL_ROWS = 32768
+
+
+def default_timeout_ns() -> int:
+    return int(float(os.environ.get("RL_ENGINE_TIMEOUT_MS", "2000")) * 1e6)
+
+
+def vocab_shard_range(vocab: int, rank: int, world: int) -> tuple[int, int]:
+    """Rows of the LM-head weight that rank ``rank`` of ``world`` holds: whole canonical slices."""
+    if world not in (1, 2, 4, 8):
+        raise ValueError("vocab parallel world size must be 1, 2, 4 or 8")
+    vs = -(-vocab // N_SLICES)
+    per = N_SLICES // world
+    lo = min(vocab, rank * per * vs)
+    hi = min(vocab, (rank + 1) * per * vs)
+    return lo, hi
+
+
+class KernelStatusError(RuntimeError):
+    """A device-side bounded wait gave up; the message carries the status block."""
+
+
+@dataclass
+class _Workspace:
+    buf: torch.Tensor
+    status: torch.Tensor
+    nbytes: int
+    epoch: int = 1
+
+
+_workspaces: dict[tuple, _Workspace] = {}
+
+
+def _get_workspace(device: torch.device, vocab: int, panel_rows: int) -> _Workspace:
+    key = (device.index, vocab, panel_rows)
+    ws = _workspaces.get(key)
+    if ws is None:
+        lib = _native.cuda()
+        nbytes = lib.ka_lmhead_logp_workspace_bytes(vocab, panel_rows)
+        off = lib.ka_lmhead_logp_status_offset(vocab, panel_rows)
+        buf = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+        status = buf[off : off + 32].view(torch.int32)
+        ws = _Workspace(buf=buf, status=status, nbytes=nbytes)
+        _workspaces[key] = ws
+    return ws
+
+
+def workspace_bytes(vocab: int, panel_rows: int = DEFAULT_PANEL_ROWS) -> int:
+    """Scratch the CUDA path holds for a given vocabulary: independent of the row count."""
+    return int(_native.cuda().ka_lmhead_logp_workspace_bytes(vocab, panel_rows))
+
+
+_WHERE = {1: "producer waiting for a free stage", 2: "MMA waiting for operands",
+          3: "MMA waiting for a free accumulator", 4: "epilogue waiting for an accumulator",
+          5: "waiting for a peer rank's flag"}
+
+
+def check_status(ws_status: torch.Tensor) -> None:
+    """Synchronise and raise if the last launches reported a timeout. Clears the status."""
+    st = ws_status.cpu().tolist()
+    if st[0] != 0:
+        ws_status.zero_()
+        raise KernelStatusError(
+            f"fused_lmhead_logp gave up (code {st[0]}) at site {st[1]} "
+            f"({_WHERE.get(st[1], '?')}), block {st[2]}, aux {st[3:6]}"
+        )
+
+
+@dataclass
+class VocabParallel:
+    """Description of a vocabulary-parallel group for :func:`lmhead_logp`.
+
+    ``exchange`` holds, per rank, the address of that rank's symmetric exchange buffer as
+    mapped in this process (see :mod:`kernel_align_b200.parallel.peer`).
+    """
+
+    rank: int
+    world: int
+    exchange_ptrs: list[int] = field(default_factory=list)
+    epoch: int = 1
+    panel_rows: int = DEFAULT_PANEL_ROWS
+
+
+def lmhead_logp(
+    hidden: torch.Tensor,
+    weight: torch.Tensor,
+    ids: torch.Tensor,
+    *,
+    scale: float = 1.0,
+    vocab: Optional[int] = None,
+    group: Optional[VocabParallel] = None,
+    return_lse: bool = False,
+    panel_rows: int = DEFAULT_PANEL_ROWS,
+    cta_group: int = 2,
+    out: Optional[torch.Tensor] = None,
+    check: bool = False,
+):
+    """Per-token log-probabilities of ``ids`` under ``softmax(scale * hidden @ weight.T)``.
+
+    hidden: ``[..., K]`` bf16; weight: ``[V_local, K]`` bf16 (this rank's vocabulary shard,
+    whole canonical slices, see :func:`vocab_shard_range`); ids: ``[...]`` integer, global
+    ids. Ids outside ``[0, vocab)`` give 0. Returns fp32 ``[...]`` (and the log-sum-exp if
+    ``return_lse``).
+    """
+    lead = hidden.shape[:-1]
+    k = hidden.shape[-1]
+    h2 = hidden.reshape(-1, k)
+    m = h2.shape[0]
+    if ids.numel() != m:
+        raise ValueError("ids must have one entry per row of hidden")
+    world = 1 if group is None else group.world
+    rank = 0 if group is None else group.rank
+    v_global = int(vocab) if vocab is not None else int(weight.shape[0])
+    lo, hi = vocab_shard_range(v_global, rank, world)
+    if weight.shape[0] != hi - lo or weight.shape[1] != k:
+        raise ValueError(f"weight shard must be [{hi - lo}, {k}], got {tuple(weight.shape)}")
+
+    if hidden.device.type != "cuda":
+        from . import cpu_ops
+
+        if world != 1:
+            raise ValueError("the CPU path computes the full vocabulary in one process")
+        res = cpu_ops.lmhead_logp_cpu(h2, weight, ids.reshape(-1), scale=scale, return_lse=return_lse)
+        if return_lse:
+            return res[0].reshape(lead), res[1].reshape(lead)
+        return res.reshape(lead)
+
+    if hidden.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
+        raise TypeError("the sm_100a path takes bf16 hidden states and weights")
+    if k % 8 != 0:
+        raise ValueError("hidden size must be a multiple of 8")
+    lib = _native.cuda()
+    h2 = h2.contiguous()
+    w = weight.contiguous()
+    ids64 = ids.reshape(-1).to(torch.int64).contiguous()
+    logp = out.reshape(-1) if out is not None else torch.empty(m, dtype=torch.float32, device=hidden.device)
+    lse = torch.empty(m, dtype=torch.float32, device=hidden.device) if return_lse else None
+    if group is not None:
+        panel_rows = group.panel_rows
+    ws = _get_workspace(hidden.device, v_global, panel_rows)
+    n_panels = -(-m // panel_rows)
+    peer_arr = None
+    if world > 1:
+        peer_arr = (ctypes.c_void_p * world)(*group.exchange_ptrs)
+        epoch = group.epoch
+        group.epoch += n_panels
+    else:
+        epoch = ws.epoch
+        ws.epoch += n_panels
+    props = torch.cuda.get_device_properties(hidden.device)
+    stream = torch.cuda.current_stream(hidden.device).cuda_stream
+    rc = lib.ka_lmhead_logp_forward(
+        h2.data_ptr(), w.data_ptr(), ids64.data_ptr(), logp.data_ptr(),
+        lse.data_ptr() if lse is not None else None,
+        ws.buf.data_ptr(), ws.nbytes, peer_arr,
+        m, k, v_global, hi - lo, lo, world, rank,
+        epoch & 0xFFFFFFFF, float(scale), panel_rows, cta_group, props.multi_processor_count,
+        default_timeout_ns(), stream,
+    )
+    if rc != 0:
+        raise RuntimeError(f"ka_lmhead_logp_forward rejected its arguments (code {rc})")
+    if check:
+        check_status(ws.status)
+    logp = logp.reshape(lead)
+    if return_lse:
+        return logp, lse.reshape(lead)
+    return logp
+
+
+def last_status(device: torch.device, vocab: int, panel_rows: int = DEFAULT_PANEL_ROWS) -> torch.Tensor:
+    """The status block of the workspace for (device, vocab): int32[8], zero when healthy."""
+    return _get_workspace(device, vocab, panel_rows).status

@@ -1,0 +1,321 @@
+#!/usr/bin/env python
+"""Headline benchmark: GRPO per-token log-probability throughput at Llama-3-8B shapes.
+
+    python bench.py --gpus N --steps K --warmup W            (N > 1: launched by torchrun)
+    python bench.py --impl reference ...                     (the unmodified reference)
+
+One step = log-probabilities of G*L target tokens given hidden states [G*L, 4096] (bf16)
+and the LM-head weight [128256, 4096] (bf16), G=256, L=512, synthetic N(0,1) / N(0,0.02)
+data. Own arm: the fused tcgen05 LM-head+logprob kernel, vocabulary sharded over the N
+ranks, partial (max, sum-exp, target) exchanged inside the kernel over peer memory; every
+rank ends with all G*L results. Reference arm: `torch.matmul` (cuBLAS) feeding the
+reference's `SamplerBackend.compute_logp` from baseline/_ref, rows split over the ranks
+(the reference has no distributed code, so data parallelism over rows is the only way to
+use it unmodified on N GPUs).
+
+Prints one JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+VOCAB = 128256
+HIDDEN = 4096
+BASELINE_TOKENS_PER_S = None  # the reference publishes no tokens/s figure
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of this rank's GPU while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines: list[str] = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def init_dist(n_gpus: int):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    if world != n_gpus:
+        raise SystemExit(f"--gpus {n_gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {n_gpus}")
+    return rank, world, local
+
+
+def barrier_sync(world: int):
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(value: float, world: int) -> float:
+    if world == 1:
+        return value
+    t = torch.tensor([value], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def make_inputs(rows: int, v_rows: int, seed: int):
+    gen = torch.Generator(device="cuda").manual_seed(seed)
+    hidden = torch.randn(rows, HIDDEN, device="cuda", generator=gen, dtype=torch.float32).to(torch.bfloat16)
+    weight = torch.empty(v_rows, HIDDEN, device="cuda", dtype=torch.bfloat16)
+    for i in range(0, v_rows, 16384):  # bounded fp32 temporary
+        n = min(16384, v_rows - i)
+        weight[i:i + n] = (torch.randn(n, HIDDEN, device="cuda", generator=gen) * 0.02).to(torch.bfloat16)
+    ids = torch.randint(0, VOCAB, (rows,), device="cuda", generator=gen)
+    return hidden, weight, ids
+
+
+def run_own(args, rank, world, local):
+    sys.path.insert(0, ROOT)
+    from kernel_align_b200.kernels.sampling import SamplerBackend
+    from kernel_align_b200.ops import fused_logp
+
+    rows = args.g * args.seq_len
+    lo, hi = fused_logp.vocab_shard_range(VOCAB, rank, world)
+    hidden, weight, ids = make_inputs(rows, hi - lo, seed=1234)
+    sampler = SamplerBackend()
+    group = None
+    if world > 1:
+        from kernel_align_b200.parallel.peer import vocab_parallel_group
+
+        group = vocab_parallel_group(VOCAB)
+    kw = dict(vocab=VOCAB, group=group)
+    n_panels = -(-rows // fused_logp.DEFAULT_PANEL_ROWS)
+
+    # ---- device-timed kernel throughput
+    for _ in range(args.warmup):
+        out = sampler.fused_logp(hidden, weight, ids, **kw)
+    barrier_sync(world)
+    clocks = ClockSampler(local)
+    clocks.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier_sync(world)
+    e0.record()
+    for _ in range(args.steps):
+        out = sampler.fused_logp(hidden, weight, ids, **kw)
+    e1.record()
+    barrier_sync(world)
+    ms = max_over_ranks(e0.elapsed_time(e1), world) / args.steps
+    clock_info = clocks.stop()
+    fused_logp.check_status(fused_logp.last_status(hidden.device, VOCAB))
+
+    # ---- end to end through the public API: pinned host inputs in, log-probs out, per step
+    h_host = hidden.cpu().pin_memory()
+    ids_host = ids.cpu().pin_memory()
+    out_host = torch.empty(rows, dtype=torch.float32).pin_memory()
+    copy_stream = torch.cuda.Stream()
+    bufs = [(torch.empty_like(hidden), torch.empty_like(ids)) for _ in range(2)]
+    ready = [torch.cuda.Event() for _ in range(2)]
+    done = [torch.cuda.Event() for _ in range(2)]
+
+    def stage(i):
+        b = i % 2
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(done[b])  # the compute that last used this buffer
+            bufs[b][0].copy_(h_host, non_blocking=True)
+            bufs[b][1].copy_(ids_host, non_blocking=True)
+            ready[b].record(copy_stream)
+
+    def e2e_steps(n):
+        stage(0)
+        for i in range(n):
+            b = i % 2
+            if i + 1 < n:
+                stage(i + 1)
+            torch.cuda.current_stream().wait_event(ready[b])
+            res = sampler.fused_logp(bufs[b][0], weight, bufs[b][1], **kw)
+            done[b].record()
+            out_host.copy_(res, non_blocking=True)
+        torch.cuda.synchronize()
+
+    for b in range(2):
+        done[b].record()
+    e2e_steps(max(1, min(2, args.warmup)))
+    barrier_sync(world)
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    e2e_steps(args.steps)
+    t1.record()
+    barrier_sync(world)
+    e2e_ms = max_over_ranks(t0.elapsed_time(t1), world) / args.steps
+    fused_logp.check_status(fused_logp.last_status(hidden.device, VOCAB))
+
+    value = rows / ms * 1e3
+    return {
+        "metric": "grpo_logp_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": (value / BASELINE_TOKENS_PER_S) if BASELINE_TOKENS_PER_S else None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"model": "Llama-3-8B LM head (V=128256, d=4096)", "global_batch": args.g, "seq_len": args.seq_len,
+                   "parallelism": f"vp{world}" if world > 1 else "single",
+                   "l2": "inputs (1 GiB hidden + vocab shard) larger than the 126 MB L2",
+                   "extra_vram_bytes": fused_logp.workspace_bytes(VOCAB)},
+        "clocks": clock_info,
+        "e2e": {"value": rows / e2e_ms * 1e3, "unit": "tokens/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": h_host.numel() * 2 + ids_host.numel() * 8,
+                "d2h_bytes_per_step": out_host.numel() * 4},
+        "gpu_launches": args.steps * n_panels,
+        "impl": "own",
+    }
+
+
+def run_reference(args, rank, world, local):
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "rl_engine")):
+        return {"impl": "reference", "unavailable": "baseline/_ref is missing: the reference is not installed"}
+    sys.path.insert(0, ref_dir)
+    try:
+        from rl_engine.kernels.sampling import SamplerBackend as RefSampler
+    except Exception as e:  # noqa: BLE001
+        return {"impl": "reference", "unavailable": f"import of the reference failed: {type(e).__name__}: {e}"}
+
+    rows = args.g * args.seq_len
+    g_local = args.g // world
+    rows_local = g_local * args.seq_len
+    hidden, weight, ids = make_inputs(rows, VOCAB, seed=1234)
+    hidden = hidden[rank * rows_local:(rank + 1) * rows_local]
+    ids = ids[rank * rows_local:(rank + 1) * rows_local].view(g_local, args.seq_len)
+    sampler = RefSampler().to("cuda")
+
+    def step(h, i):
+        logits = torch.matmul(h, weight.t()).view(g_local, args.seq_len, VOCAB)
+        return sampler.compute_logp(logits, i)
+
+    for _ in range(args.warmup):
+        out = step(hidden, ids)
+    barrier_sync(world)
+    clocks = ClockSampler(local)
+    clocks.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier_sync(world)
+    e0.record()
+    for _ in range(args.steps):
+        out = step(hidden, ids)
+    e1.record()
+    barrier_sync(world)
+    ms = max_over_ranks(e0.elapsed_time(e1), world) / args.steps
+    clock_info = clocks.stop()
+    peak = torch.cuda.max_memory_allocated()
+
+    h_host = hidden.cpu().pin_memory()
+    ids_host = ids.cpu().pin_memory()
+    out_host = torch.empty(g_local, args.seq_len, dtype=out.dtype).pin_memory()
+    barrier_sync(world)
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(args.steps):
+        h_dev = h_host.to("cuda", non_blocking=True)
+        i_dev = ids_host.to("cuda", non_blocking=True)
+        out_host.copy_(step(h_dev, i_dev), non_blocking=True)
+    torch.cuda.synchronize()
+    t1.record()
+    barrier_sync(world)
+    e2e_ms = max_over_ranks(t0.elapsed_time(t1), world) / args.steps
+    value = rows / ms * 1e3
+    return {
+        "metric": "grpo_logp_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"model": "Llama-3-8B LM head (V=128256, d=4096)", "global_batch": args.g, "seq_len": args.seq_len,
+                   "parallelism": f"dp{world}" if world > 1 else "single",
+                   "l2": "inputs and logits larger than the 126 MB L2",
+                   "path": "torch.matmul (cuBLAS) -> rl_engine SamplerBackend.compute_logp",
+                   "peak_allocated_bytes": peak},
+        "clocks": clock_info,
+        "e2e": {"value": rows / e2e_ms * 1e3, "unit": "tokens/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": (h_host.numel() * 2 + ids_host.numel() * 8) * world,
+                "d2h_bytes_per_step": out_host.numel() * out_host.element_size() * world},
+        "gpu_launches": 0,
+        "impl": "reference",
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["own", "reference"], default="own")
+    ap.add_argument("--g", type=int, default=256, help="group size G (rows = G * seq_len)")
+    ap.add_argument("--seq-len", type=int, default=512)
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if not torch.cuda.is_available():
+        line = {"impl": args.impl, "unavailable": "no CUDA device visible"}
+        print(json.dumps(line))
+        return
+    rank, world, local = init_dist(args.gpus)
+    try:
+        line = run_own(args, rank, world, local) if args.impl == "own" else run_reference(args, rank, world, local)
+    finally:
+        pass
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

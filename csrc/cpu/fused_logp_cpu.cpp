@@ -1,0 +1,154 @@
+// CPU implementation of the fused LM-head + log-probability op and of log-prob from
+// materialised logits. Oracle for the CUDA kernels and the code path of the CPU device.
+//
+// Batch invariance: a row's result is a function of that row only. Dot products use a fixed
+// 8-lane accumulation order over K, logits are folded in row chunks of `chunk_rows` (the
+// chunk only bounds the temporary, it never enters the arithmetic), and the vocabulary is
+// decomposed exactly like the CUDA kernel: 8 canonical slices of ceil(V/8) columns,
+// 2048-column sub-slices folded left to right in groups of 32 columns, sub-slices merged
+// left to right, slices merged by a balanced binary tree.
+#include <algorithm>
+#include <cmath>
+#include <cstdint>
+#include <limits>
+#include <thread>
+#include <vector>
+
+namespace {
+
+constexpr int kSlices = 8;
+constexpr int kSubCols = 2048;
+constexpr int kGroup = 32;
+const float kNegInf = -std::numeric_limits<float>::infinity();
+
+inline float dot_fixed(const float* a, const float* b, int k) {
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  int i = 0;
+  for (; i + 8 <= k; i += 8)
+    for (int j = 0; j < 8; ++j) acc[j] += a[i + j] * b[i + j];
+  for (int j = 0; i < k; ++i, ++j) acc[j] += a[i] * b[i];
+  return ((acc[0] + acc[1]) + (acc[2] + acc[3])) + ((acc[4] + acc[5]) + (acc[6] + acc[7]));
+}
+
+struct State {
+  float m = kNegInf;  // running max of the scaled logits
+  float l = 0.f;      // sum of exp(x - m)
+};
+
+inline void fold_group(State& s, const float* x, int n) {
+  float mx = x[0];
+  for (int j = 1; j < n; ++j) mx = std::max(mx, x[j]);
+  const float mn = std::max(s.m, mx);
+  float acc = 0.f;
+  for (int j = 0; j < n; ++j) acc += std::exp(x[j] - mn);
+  const float corr = (s.m == kNegInf) ? 0.f : std::exp(s.m - mn);
+  s.l = s.l * corr + acc;
+  s.m = mn;
+}
+
+inline void merge(State& a, const State& b) {
+  const float mn = std::max(a.m, b.m);
+  const float ca = (a.m == kNegInf) ? 0.f : std::exp(a.m - mn);
+  const float cb = (b.m == kNegInf) ? 0.f : std::exp(b.m - mn);
+  a.l = a.l * ca + b.l * cb;
+  a.m = mn;
+}
+
+// log-sum-exp of one row of scaled logits given through a column accessor
+template <typename LogitAt>
+inline float row_lse(int v, LogitAt&& at) {
+  const int vs = (v + kSlices - 1) / kSlices;
+  State slice[kSlices];
+  float buf[kGroup];
+  for (int sl = 0; sl < kSlices; ++sl) {
+    const int s_begin = std::min(v, sl * vs), s_end = std::min(v, (sl + 1) * vs);
+    State acc;
+    bool first = true;
+    for (int c0 = s_begin; c0 < s_end; c0 += kSubCols) {
+      State sub;
+      const int c1 = std::min(c0 + kSubCols, s_end);
+      for (int g = c0; g < c1; g += kGroup) {
+        const int n = std::min(kGroup, c1 - g);
+        for (int j = 0; j < n; ++j) buf[j] = at(g + j);
+        fold_group(sub, buf, n);
+      }
+      if (first) {
+        acc = sub;
+        first = false;
+      } else {
+        merge(acc, sub);
+      }
+    }
+    slice[sl] = acc;
+  }
+  for (int w = kSlices; w > 1; w >>= 1)
+    for (int i = 0; i < w / 2; ++i) {
+      State a = slice[2 * i];
+      merge(a, slice[2 * i + 1]);
+      slice[i] = a;
+    }
+  return slice[0].m + std::log(slice[0].l);
+}
+
+template <typename F>
+void parallel_rows(int rows, int threads, F&& f) {
+  threads = std::max(1, std::min(threads, rows));
+  if (threads == 1) {
+    f(0, rows);
+    return;
+  }
+  std::vector<std::thread> pool;
+  const int per = (rows + threads - 1) / threads;
+  for (int t = 0; t < threads; ++t) {
+    const int lo = t * per, hi = std::min(rows, lo + per);
+    if (lo < hi) pool.emplace_back([=, &f] { f(lo, hi); });
+  }
+  for (auto& th : pool) th.join();
+}
+
+}  // namespace
+
+// hidden [m, k], weight [v, k], both fp32 row-major; ids [m] int64; logp / lse [m] fp32
+// (lse may be null). `chunk_rows` bounds the logits temporary to chunk_rows * v floats per
+// worker thread. Ids outside [0, v) give logp = 0.
+extern "C" int ka_cpu_lmhead_logp(const float* hidden, const float* weight, const long long* ids, float* logp,
+                                  float* lse, int m, int k, int v, float scale, int chunk_rows, int threads) {
+  if (m <= 0) return 0;
+  if (k <= 0 || v <= 0 || chunk_rows <= 0 || !(scale > 0.f)) return -1;
+  parallel_rows(m, threads, [&](int lo, int hi) {
+    std::vector<float> logits(static_cast<size_t>(chunk_rows) * v);
+    for (int r0 = lo; r0 < hi; r0 += chunk_rows) {
+      const int nr = std::min(chunk_rows, hi - r0);
+      for (int r = 0; r < nr; ++r) {
+        const float* h = hidden + static_cast<size_t>(r0 + r) * k;
+        float* out = logits.data() + static_cast<size_t>(r) * v;
+        for (int c = 0; c < v; ++c) out[c] = dot_fixed(h, weight + static_cast<size_t>(c) * k, k) * scale;
+      }
+      for (int r = 0; r < nr; ++r) {
+        const float* x = logits.data() + static_cast<size_t>(r) * v;
+        const float row_l = row_lse(v, [&](int c) { return x[c]; });
+        if (lse) lse[r0 + r] = row_l;
+        const long long id = ids[r0 + r];
+        logp[r0 + r] = (id >= 0 && id < v) ? x[id] - row_l : 0.f;
+      }
+    }
+  });
+  return 0;
+}
+
+// logits fp32 [rows, v] with row stride in elements.
+extern "C" int ka_cpu_logits_logp(const float* logits, long long row_stride, int rows, int v, const long long* ids,
+                                  float scale, float* logp, float* lse, int threads) {
+  if (rows <= 0) return 0;
+  if (v <= 0 || !(scale > 0.f)) return -1;
+  parallel_rows(rows, threads, [&](int lo, int hi) {
+    for (int r = lo; r < hi; ++r) {
+      const float* x = logits + static_cast<long long>(r) * row_stride;
+      const float row_l = row_lse(v, [&](int c) { return x[c] * scale; });
+      if (lse) lse[r] = row_l;
+      const long long id = ids[r];
+      logp[r] = (id >= 0 && id < v) ? x[id] * scale - row_l : 0.f;
+    }
+  });
+  return 0;
+}

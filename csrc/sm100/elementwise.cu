@@ -1,0 +1,229 @@
+// Memory-bound layer ops of the decoder, each a single pass with 16-byte accesses and fp32
+// math: RMSNorm (with optional fused residual add), rotary embedding, SwiGLU.
+// Every reduction runs in a fixed order inside one CTA, so a row's output depends on that row
+// only (batch invariance). None of these exists in the reference, which only names them
+// (rl_engine/platforms/constants.py:75-80, README feature list).
+#include <cstdint>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "common/ptx.cuh"
+
+namespace ka {
+namespace {
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct alignas(16) Bf16x8 {
+  __nv_bfloat16 v[8];
+};
+
+__device__ __forceinline__ float block_sum_fixed(float v, float* s_warp, int n_warps) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, o));
+  if (lane == 0) s_warp[warp] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int w = 0; w < n_warps; ++w) t = __fadd_rn(t, s_warp[w]);  // same order in every thread
+  __syncthreads();
+  return t;
+}
+
+// y = (x [+ residual]) * rsqrt(mean(x^2) + eps) * w ; if residual_out: residual_out = x + residual
+// One CTA per row, D % 8 == 0.
+__global__ void __launch_bounds__(256)
+rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ residual,
+               const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
+               __nv_bfloat16* __restrict__ residual_out, int rows, int d, float eps) {
+  __shared__ float s_warp[8];
+  const int nvec = d / 8;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const Bf16x8* xp = reinterpret_cast<const Bf16x8*>(x + static_cast<size_t>(row) * d);
+    const Bf16x8* rp = residual ? reinterpret_cast<const Bf16x8*>(residual + static_cast<size_t>(row) * d) : nullptr;
+    Bf16x8* ro = residual_out ? reinterpret_cast<Bf16x8*>(residual_out + static_cast<size_t>(row) * d) : nullptr;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+      Bf16x8 a = xp[i];
+      if (rp) {
+        const Bf16x8 b = rp[i];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          a.v[j] = __float2bfloat16_rn(__fadd_rn(__bfloat162float(a.v[j]), __bfloat162float(b.v[j])));
+        if (ro) ro[i] = a;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float f = __bfloat162float(a.v[j]);
+        ss = __fmaf_rn(f, f, ss);
+      }
+    }
+    const float total = block_sum_fixed(ss, s_warp, blockDim.x >> 5);
+    const float inv = rsqrtf(__fadd_rn(__fdiv_rn(total, static_cast<float>(d)), eps));
+    const Bf16x8* wp = reinterpret_cast<const Bf16x8*>(w);
+    Bf16x8* yp = reinterpret_cast<Bf16x8*>(y + static_cast<size_t>(row) * d);
+    const Bf16x8* src = (rp && ro) ? reinterpret_cast<const Bf16x8*>(ro) : xp;
+    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+      Bf16x8 a = src[i];
+      if (rp && !ro) {
+        const Bf16x8 b = rp[i];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          a.v[j] = __float2bfloat16_rn(__fadd_rn(__bfloat162float(a.v[j]), __bfloat162float(b.v[j])));
+      }
+      const Bf16x8 ww = wp[i];
+      Bf16x8 o;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float n = __fmul_rn(__bfloat162float(a.v[j]), inv);
+        // round the normalised value to bf16 before the weight, as the usual bf16 module does
+        o.v[j] = __float2bfloat16_rn(__fmul_rn(__bfloat162float(__float2bfloat16_rn(n)), __bfloat162float(ww.v[j])));
+      }
+      yp[i] = o;
+    }
+  }
+}
+
+// Rotary embedding, "rotate half" convention: for i < hd/2
+//   out[i]        = x[i] * cos[pos, i] - x[i + hd/2] * sin[pos, i]
+//   out[i + hd/2] = x[i + hd/2] * cos[pos, i] + x[i] * sin[pos, i]
+// x: [tokens, heads, hd] (token stride given), cos/sin: [max_pos, hd/2] fp32, in place.
+__global__ void __launch_bounds__(256)
+rope_kernel(__nv_bfloat16* __restrict__ x, long long token_stride, const long long* __restrict__ positions,
+            const float* __restrict__ cos_t, const float* __restrict__ sin_t, int tokens, int heads, int hd) {
+  const int half = hd / 2;
+  const long long total = static_cast<long long>(tokens) * heads * half;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int j = static_cast<int>(i % half);
+    const long long th = i / half;
+    const int h = static_cast<int>(th % heads);
+    const long long t = th / heads;
+    const long long pos = positions[t];
+    const float c = cos_t[pos * half + j], s = sin_t[pos * half + j];
+    __nv_bfloat16* p = x + t * token_stride + static_cast<long long>(h) * hd;
+    const float a = __bfloat162float(p[j]), b = __bfloat162float(p[j + half]);
+    p[j] = __float2bfloat16_rn(__fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s)));
+    p[j + half] = __float2bfloat16_rn(__fadd_rn(__fmul_rn(b, c), __fmul_rn(a, s)));
+  }
+}
+
+__device__ __forceinline__ float silu_f(float g) {
+  // g * sigmoid(g) with exp through ex2
+  const float e = ex2_approx(__fmul_rn(-g, kLog2e));
+  return __fdiv_rn(g, __fadd_rn(1.f, e));
+}
+
+// out[r, j] = silu(gate[r, j]) * up[r, j]; gate/up are column halves of one [rows, 2f] tensor
+// when up == gate + f (row stride 2f), or separate tensors.
+__global__ void __launch_bounds__(256)
+swiglu_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ up, long long in_stride,
+              __nv_bfloat16* __restrict__ out, int rows, int f) {
+  const int nvec = f / 8;
+  const long long total = static_cast<long long>(rows) * nvec;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / nvec;
+    const int c = static_cast<int>(i % nvec);
+    const Bf16x8 g = reinterpret_cast<const Bf16x8*>(gate + r * in_stride)[c];
+    const Bf16x8 u = reinterpret_cast<const Bf16x8*>(up + r * in_stride)[c];
+    Bf16x8 o;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float a = __bfloat162float(__float2bfloat16_rn(silu_f(__bfloat162float(g.v[j]))));
+      o.v[j] = __float2bfloat16_rn(__fmul_rn(a, __bfloat162float(u.v[j])));
+    }
+    reinterpret_cast<Bf16x8*>(out + r * static_cast<long long>(f))[c] = o;
+  }
+}
+
+// Backward of SwiGLU: d_gate = d_out * up * (sig + g*sig*(1-sig)), d_up = d_out * silu(g).
+__global__ void __launch_bounds__(256)
+swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ up, long long in_stride,
+                  const __nv_bfloat16* __restrict__ d_out, __nv_bfloat16* __restrict__ d_gate,
+                  __nv_bfloat16* __restrict__ d_up, long long dgrad_stride, int rows, int f) {
+  const int nvec = f / 8;
+  const long long total = static_cast<long long>(rows) * nvec;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / nvec;
+    const int c = static_cast<int>(i % nvec);
+    const Bf16x8 g = reinterpret_cast<const Bf16x8*>(gate + r * in_stride)[c];
+    const Bf16x8 u = reinterpret_cast<const Bf16x8*>(up + r * in_stride)[c];
+    const Bf16x8 d = reinterpret_cast<const Bf16x8*>(d_out + r * static_cast<long long>(f))[c];
+    Bf16x8 dg, du;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float gf = __bfloat162float(g.v[j]), uf = __bfloat162float(u.v[j]), df = __bfloat162float(d.v[j]);
+      const float sig = __fdiv_rn(1.f, __fadd_rn(1.f, ex2_approx(__fmul_rn(-gf, kLog2e))));
+      const float dsilu = __fmaf_rn(__fmul_rn(gf, sig), __fsub_rn(1.f, sig), sig);
+      dg.v[j] = __float2bfloat16_rn(__fmul_rn(__fmul_rn(df, uf), dsilu));
+      du.v[j] = __float2bfloat16_rn(__fmul_rn(df, __fmul_rn(gf, sig)));
+    }
+    reinterpret_cast<Bf16x8*>(d_gate + r * dgrad_stride)[c] = dg;
+    reinterpret_cast<Bf16x8*>(d_up + r * dgrad_stride)[c] = du;
+  }
+}
+
+int grid_for(long long work_items, int threads, int num_sms) {
+  long long g = (work_items + threads - 1) / threads;
+  const long long cap = static_cast<long long>(num_sms) * 8;
+  if (g > cap) g = cap;
+  return g < 1 ? 1 : static_cast<int>(g);
+}
+
+}  // namespace
+}  // namespace ka
+
+extern "C" {
+
+int ka_rmsnorm(const void* x, const void* residual, const void* w, void* y, void* residual_out, int rows, int d,
+               float eps, int num_sms, void* stream) {
+  using namespace ka;
+  if (rows <= 0) return 0;
+  if (d % 8 != 0) return -1;
+  const int grid = rows < num_sms * 8 ? rows : num_sms * 8;
+  rmsnorm_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(residual),
+      static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(y), static_cast<__nv_bfloat16*>(residual_out),
+      rows, d, eps);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+int ka_rope(void* x, long long token_stride, const long long* positions, const float* cos_t, const float* sin_t,
+            int tokens, int heads, int hd, int num_sms, void* stream) {
+  using namespace ka;
+  if (tokens <= 0) return 0;
+  if (hd % 2 != 0) return -1;
+  const long long total = static_cast<long long>(tokens) * heads * (hd / 2);
+  rope_kernel<<<grid_for(total, 256, num_sms), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<__nv_bfloat16*>(x), token_stride, positions, cos_t, sin_t, tokens, heads, hd);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+int ka_swiglu(const void* gate, const void* up, long long in_stride, void* out, int rows, int f, int num_sms,
+              void* stream) {
+  using namespace ka;
+  if (rows <= 0) return 0;
+  if (f % 8 != 0 || in_stride % 8 != 0) return -1;
+  const long long total = static_cast<long long>(rows) * (f / 8);
+  swiglu_kernel<<<grid_for(total, 256, num_sms), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(gate), static_cast<const __nv_bfloat16*>(up), in_stride,
+      static_cast<__nv_bfloat16*>(out), rows, f);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+int ka_swiglu_bwd(const void* gate, const void* up, long long in_stride, const void* d_out, void* d_gate, void* d_up,
+                  long long dgrad_stride, int rows, int f, int num_sms, void* stream) {
+  using namespace ka;
+  if (rows <= 0) return 0;
+  if (f % 8 != 0 || in_stride % 8 != 0 || dgrad_stride % 8 != 0) return -1;
+  const long long total = static_cast<long long>(rows) * (f / 8);
+  swiglu_bwd_kernel<<<grid_for(total, 256, num_sms), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(gate), static_cast<const __nv_bfloat16*>(up), in_stride,
+      static_cast<const __nv_bfloat16*>(d_out), static_cast<__nv_bfloat16*>(d_gate), static_cast<__nv_bfloat16*>(d_up),
+      dgrad_stride, rows, f);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+}  // extern "C"

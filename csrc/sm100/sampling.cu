@@ -1,0 +1,587 @@
+// Fused temperature / top-k / top-p token sampling for sm_100a: one CTA per row, one launch
+// per call, the logits row is read once from HBM (later passes hit L2).
+//
+// Semantics (the order the reference gets from FlashInfer's default "top_k_first",
+// rl_engine/kernels/sampling.py:61-64, with the temperature applied once):
+//   1. y = logits / temperature
+//   2. keep the k largest y; ties at the k-th value are kept in increasing token-id order
+//   3. softmax over the survivors, sorted by (y descending, token id ascending); keep token i
+//      while the probability mass of the tokens before it is <= top_p
+//   4. draw u from Philox4x32-10 keyed by (seed, row id, step) and invert the CDF
+// Probability masses are 32.32 fixed-point integers (csrc/common/detmath.h), so every sum is
+// exact and order-free: the token depends only on (row contents, seed, row id, step), not on
+// the batch size, the launch shape or the schedule, and the C++ CPU path reproduces it bit
+// for bit.
+//
+// Two kernels:
+//   sample_topk_kernel     top_k in [1, 1024] (greedy = top_k 1), optional top_p
+//   sample_general_kernel  no top_k (or k > 1024), optional top_p: threshold search by radix
+//                          descent on (count, mass) histograms
+#include <cstdint>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "../common/detmath.h"
+#include "sampling.h"
+
+namespace ka {
+namespace {
+
+constexpr int kThreads = 1024;
+constexpr int kWarps = kThreads / 32;
+constexpr int kCandCap = 4096;
+constexpr int kMaxTopK = 1024;
+
+template <typename T>
+struct Elem;
+template <>
+struct Elem<float> {
+  static constexpr int kVec = 4;
+  static constexpr int kLowBit = 0;
+  __device__ static float to_float(float v) { return v; }
+};
+template <>
+struct Elem<__nv_bfloat16> {
+  static constexpr int kVec = 8;
+  static constexpr int kLowBit = 16;
+  __device__ static float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+};
+template <>
+struct Elem<__half> {
+  static constexpr int kVec = 8;
+  static constexpr int kLowBit = 13;
+  __device__ static float to_float(__half v) { return __half2float(v); }
+};
+
+// Visit every element of a row once: 16-byte vector loads when the row allows it.
+template <typename T, typename F>
+__device__ __forceinline__ void for_each_key(const T* __restrict__ row, int v, bool vec_ok, F&& f) {
+  constexpr int kVec = Elem<T>::kVec;
+  const int tid = threadIdx.x;
+  if (vec_ok) {
+    const int nvec = v / kVec;
+    const uint4* p = reinterpret_cast<const uint4*>(row);
+    for (int i = tid; i < nvec; i += kThreads) {
+      const uint4 raw = p[i];
+      const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+      for (int j = 0; j < kVec; ++j) f(float_to_key(Elem<T>::to_float(e[j])), i * kVec + j);
+    }
+    for (int i = nvec * kVec + tid; i < v; i += kThreads) f(float_to_key(Elem<T>::to_float(row[i])), i);
+  } else {
+    for (int i = tid; i < v; i += kThreads) f(float_to_key(Elem<T>::to_float(row[i])), i);
+  }
+}
+
+__device__ __forceinline__ int block_sum_int(int v, int* s_warp) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();
+  if (lane == 0) s_warp[warp] = v;
+  __syncthreads();
+  int t = (lane < kWarps) ? s_warp[lane] : 0;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+  return t;
+}
+
+// Exclusive prefix sum over the block in thread order; `total` receives the block sum.
+__device__ __forceinline__ unsigned long long block_exscan_u64(unsigned long long v, unsigned long long* s_warp,
+                                                             unsigned long long& total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  unsigned long long inc = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const unsigned long long n = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += n;
+  }
+  __syncthreads();
+  if (lane == 31) s_warp[warp] = inc;
+  __syncthreads();
+  unsigned long long w = (lane < kWarps) ? s_warp[lane] : 0ull;
+  unsigned long long winc = w;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const unsigned long long n = __shfl_up_sync(0xffffffffu, winc, o);
+    if (lane >= o) winc += n;
+  }
+  total = __shfl_sync(0xffffffffu, winc, 31);
+  const unsigned long long warp_off = __shfl_sync(0xffffffffu, winc - w, warp);
+  return warp_off + inc - v;
+}
+
+struct TopkSmem {
+  uint32_t cand_key[kCandCap];
+  uint32_t cand_idx[kCandCap];
+  uint32_t sorted_key[kMaxTopK];
+  uint32_t sorted_idx[kMaxTopK];
+  unsigned long long mass[kMaxTopK];
+  unsigned long long scan[kWarps];
+  int red[kWarps];
+  int count;
+};
+
+// Final step shared by both kernels' oracle definition: survivors sorted by (key desc, id asc)
+// with masses q[i]; apply top-p, draw, return the position picked.
+__device__ __forceinline__ int pick_sorted(const unsigned long long* q, int n, float top_p, uint32_t u24) {
+  unsigned long long z = 0;
+  for (int i = 0; i < n; ++i) z += q[i];
+  int keep = n;
+  unsigned long long zk = z;
+  if (top_p < 1.0f) {
+    const unsigned long long limit = mass_fraction(static_cast<double>(top_p), z);
+    unsigned long long cum = 0;
+    for (int i = 0; i < n; ++i) {
+      if (i > 0 && cum > limit) {
+        keep = i;
+        break;
+      }
+      cum += q[i];
+    }
+    zk = 0;
+    for (int i = 0; i < keep; ++i) zk += q[i];
+  }
+  const unsigned long long target = mass_scale_u24(u24, zk);
+  unsigned long long acc = 0;
+  for (int i = 0; i < keep; ++i) {
+    acc += q[i];
+    if (acc > target) return i;
+  }
+  return keep - 1;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+sample_topk_kernel(const T* __restrict__ logits, long long row_stride, int v, const long long* __restrict__ row_ids,
+                   float inv_temp, int top_k, float top_p, unsigned long long seed, unsigned long long step,
+                   int* __restrict__ out) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  TopkSmem& s = *reinterpret_cast<TopkSmem*>(smem_raw);
+  const int tid = threadIdx.x;
+  const int row = blockIdx.x;
+  const T* rp = logits + static_cast<long long>(row) * row_stride;
+  const bool vec_ok = (reinterpret_cast<uintptr_t>(rp) & 15u) == 0;
+  const int kk = min(min(top_k, kMaxTopK), v);
+
+  // ---- pass 1 (HBM): per-thread maximum
+  uint32_t tmax = 0;
+  for_each_key<T>(rp, v, vec_ok, [&](uint32_t key, int) { tmax = max(tmax, key); });
+
+  // The kk-th largest of the 1024 thread maxima is a lower bound L for the kk-th largest
+  // element of the row: at least kk elements are >= L.
+  uint32_t lower = 0;
+  for (int bit = 31; bit >= Elem<T>::kLowBit; --bit) {
+    const uint32_t cand = lower | (1u << bit);
+    if (__syncthreads_count(tmax >= cand) >= kk) lower = cand;
+  }
+
+  // ---- pass 2 (L2): collect every element >= L
+  if (tid == 0) s.count = 0;
+  __syncthreads();
+  for_each_key<T>(rp, v, vec_ok, [&](uint32_t key, int i) {
+    if (key >= lower) {
+      const int slot = atomicAdd(&s.count, 1);
+      if (slot < kCandCap) {
+        s.cand_key[slot] = key;
+        s.cand_idx[slot] = static_cast<uint32_t>(i);
+      }
+    }
+  });
+  __syncthreads();
+  int n_cand = s.count;
+  __syncthreads();
+
+  if (n_cand > kCandCap) {
+    // ---- rare: more ties / near-ties than the candidate buffer holds. Exact radix select by
+    // counting passes, then an index-ordered pick among the ties at the threshold.
+    uint32_t tau = 0;
+    for (int bit = 31; bit >= 0; --bit) {
+      const uint32_t cand = tau | (1u << bit);
+      int local = 0;
+      for_each_key<T>(rp, v, vec_ok, [&](uint32_t key, int) { local += (key >= cand) ? 1 : 0; });
+      if (block_sum_int(local, s.red) >= kk) tau = cand;
+    }
+    int local_gt = 0;
+    for_each_key<T>(rp, v, vec_ok, [&](uint32_t key, int) { local_gt += (key > tau) ? 1 : 0; });
+    const int n_gt = block_sum_int(local_gt, s.red);
+    const int quota = kk - n_gt;
+    if (tid == 0) s.count = 0;
+    __syncthreads();
+    for_each_key<T>(rp, v, vec_ok, [&](uint32_t key, int i) {
+      if (key > tau) {
+        const int slot = atomicAdd(&s.count, 1);
+        s.cand_key[slot] = key;
+        s.cand_idx[slot] = static_cast<uint32_t>(i);
+      }
+    });
+    __syncthreads();
+    unsigned long long tie_base = 0;
+    constexpr int kPer = 8;
+    for (int base = 0; base < v && tie_base < static_cast<unsigned long long>(quota); base += kThreads * kPer) {
+      const int i0 = base + tid * kPer;
+      int mine = 0;
+      for (int j = 0; j < kPer; ++j) {
+        const int i = i0 + j;
+        if (i < v && float_to_key(Elem<T>::to_float(rp[i])) == tau) ++mine;
+      }
+      unsigned long long total;
+      unsigned long long off = tie_base + block_exscan_u64(static_cast<unsigned long long>(mine), s.scan, total);
+      for (int j = 0; j < kPer; ++j) {
+        const int i = i0 + j;
+        if (i < v && float_to_key(Elem<T>::to_float(rp[i])) == tau) {
+          if (off < static_cast<unsigned long long>(quota)) {
+            s.cand_key[n_gt + off] = tau;
+            s.cand_idx[n_gt + off] = static_cast<uint32_t>(i);
+          }
+          ++off;
+        }
+      }
+      tie_base += total;
+    }
+    __syncthreads();
+    n_cand = kk;
+  }
+
+  // ---- rank sort of the candidates by (key desc, id asc); the first kk are the survivors
+  for (int i = tid; i < n_cand; i += kThreads) {
+    const uint32_t ki = s.cand_key[i], ii = s.cand_idx[i];
+    int rank = 0;
+    for (int j = 0; j < n_cand; ++j) {
+      const uint32_t kj = s.cand_key[j], ij = s.cand_idx[j];
+      rank += (kj > ki || (kj == ki && ij < ii)) ? 1 : 0;
+    }
+    if (rank < kk) {
+      s.sorted_key[rank] = ki;
+      s.sorted_idx[rank] = ii;
+    }
+  }
+  __syncthreads();
+
+  // ---- masses, top-p, draw
+  const float y0 = mul_rn(key_to_float(s.sorted_key[0]), inv_temp);
+  if (tid < kk) {
+    const float y = mul_rn(key_to_float(s.sorted_key[tid]), inv_temp);
+    s.mass[tid] = mass_fixed(exp_det(sub_rn(y, y0)));
+  }
+  __syncthreads();
+  if (tid == 0) {
+    const unsigned long long rid = row_ids ? static_cast<unsigned long long>(row_ids[row])
+                                           : static_cast<unsigned long long>(row);
+    const int pos = pick_sorted(s.mass, kk, top_p, uniform_u24(seed, rid, step));
+    out[row] = static_cast<int>(s.sorted_idx[pos]);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// General kernel: no top-k bound small enough for the candidate list.
+//
+// The kept set is a prefix of the order (key desc, id asc): the first n* elements with
+//   n* = min(k, smallest n with mass(first n) > top_p * Z_k)      (Z_k = mass of the first k)
+// The prefix is located by radix descent over the key bits (11, 11, 10) with exact integer
+// histograms of element counts and fixed-point masses; ties at the threshold key are cut in
+// token-id order. The draw inverts the CDF over the kept set in token-id order.
+// ------------------------------------------------------------------------------------------
+constexpr int kBins = 2048;
+
+struct GeneralSmem {
+  unsigned int cnt[kBins];
+  unsigned long long mass[kBins];
+  unsigned long long scan[kWarps];
+  int red[kWarps];
+  uint32_t max_key;
+  // results of a descent
+  uint32_t prefix;
+  unsigned long long above_cnt;
+  unsigned long long above_mass;
+  int sel_bin;
+  int pick;
+};
+
+// One descent: find key tau and the (count, mass) strictly above it such that the element
+// that crosses `limit` lies among the keys equal to tau. `by_mass` selects the criterion:
+//   by count: first key where count_above + count(key) >  limit  (limit = k - 1)
+//   by mass : first key where mass_above  + mass(key)  >  limit
+template <typename T>
+__device__ void descend(const T* rp, int v, bool vec_ok, float inv_temp, float y_max, bool by_mass,
+                        unsigned long long limit, GeneralSmem& s, uint32_t& tau, unsigned long long& above_cnt,
+                        unsigned long long& above_mass) {
+  const int tid = threadIdx.x;
+  uint32_t prefix = 0;
+  int known_bits = 0;
+  above_cnt = 0;
+  above_mass = 0;
+  const int widths[3] = {11, 11, 10};
+  for (int round = 0; round < 3; ++round) {
+    const int w = widths[round];
+    const int shift = 32 - known_bits - w;
+    for (int b = tid; b < kBins; b += kThreads) {
+      s.cnt[b] = 0;
+      s.mass[b] = 0;
+    }
+    __syncthreads();
+    for_each_key<T>(rp, v, vec_ok, [&](uint32_t key, int) {
+      const bool match = known_bits == 0 || (key >> (32 - known_bits)) == (prefix >> (32 - known_bits));
+      if (match) {
+        const int bin = (key >> shift) & ((1 << w) - 1);
+        atomicAdd(&s.cnt[bin], 1u);
+        const float y = mul_rn(key_to_float(key), inv_temp);
+        atomicAdd(&s.mass[bin], mass_fixed(exp_det(sub_rn(y, y_max))));
+      }
+    });
+    __syncthreads();
+    if (tid == 0) {
+      unsigned long long c = above_cnt, m = above_mass;
+      int sel = 0;
+      for (int b = (1 << w) - 1; b >= 0; --b) {
+        const unsigned long long nc = c + s.cnt[b], nm = m + s.mass[b];
+        const bool crosses = by_mass ? (nm > limit) : (nc > limit);
+        if (crosses || b == 0) {
+          sel = b;
+          break;
+        }
+        c = nc;
+        m = nm;
+      }
+      s.sel_bin = sel;
+      s.above_cnt = c;
+      s.above_mass = m;
+    }
+    __syncthreads();
+    prefix |= static_cast<uint32_t>(s.sel_bin) << shift;
+    above_cnt = s.above_cnt;
+    above_mass = s.above_mass;
+    known_bits += w;
+    __syncthreads();
+  }
+  tau = prefix;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+sample_general_kernel(const T* __restrict__ logits, long long row_stride, int v, const long long* __restrict__ row_ids,
+                      float inv_temp, int top_k, float top_p, unsigned long long seed, unsigned long long step,
+                      int* __restrict__ out) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  GeneralSmem& s = *reinterpret_cast<GeneralSmem*>(smem_raw);
+  const int tid = threadIdx.x;
+  const int row = blockIdx.x;
+  const T* rp = logits + static_cast<long long>(row) * row_stride;
+  const bool vec_ok = (reinterpret_cast<uintptr_t>(rp) & 15u) == 0;
+
+  // ---- row maximum
+  uint32_t tmax = 0;
+  for_each_key<T>(rp, v, vec_ok, [&](uint32_t key, int) { tmax = max(tmax, key); });
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) tmax = max(tmax, __shfl_xor_sync(0xffffffffu, tmax, o));
+  if (tid == 0) s.max_key = 0;
+  __syncthreads();
+  if ((tid & 31) == 0) atomicMax(&s.max_key, tmax);
+  __syncthreads();
+  const float y_max = mul_rn(key_to_float(s.max_key), inv_temp);
+
+  // ---- where the kept prefix ends: (tau, number of ties at tau that are kept)
+  uint32_t tau = 0;                     // threshold key
+  unsigned long long tie_keep = ~0ull;  // ties at tau kept, in id order
+  unsigned long long kept_mass = 0;     // mass of the kept set
+  {
+    // total mass and, if top_k is set, the top-k prefix
+    unsigned long long k_above_cnt = 0, k_above_mass = 0;
+    uint32_t k_tau = 0;
+    unsigned long long k_ties = ~0ull;
+    unsigned long long zk;
+    const bool has_k = top_k > 0 && top_k < v;
+    if (has_k) {
+      descend<T>(rp, v, vec_ok, inv_temp, y_max, false, static_cast<unsigned long long>(top_k - 1), s, k_tau,
+                 k_above_cnt, k_above_mass);
+      k_ties = static_cast<unsigned long long>(top_k) - k_above_cnt;
+      const float y = mul_rn(key_to_float(k_tau), inv_temp);
+      zk = k_above_mass + k_ties * mass_fixed(exp_det(sub_rn(y, y_max)));
+    } else {
+      // everything is kept by the count criterion: Z = total mass
+      unsigned long long local = 0;
+      for_each_key<T>(rp, v, vec_ok, [&](uint32_t key, int) {
+        const float y = mul_rn(key_to_float(key), inv_temp);
+        local += mass_fixed(exp_det(sub_rn(y, y_max)));
+      });
+      unsigned long long total;
+      block_exscan_u64(local, s.scan, total);
+      zk = total;
+    }
+    tau = has_k ? k_tau : 0u;
+    tie_keep = k_ties;
+    kept_mass = zk;
+    if (top_p < 1.0f) {
+      const unsigned long long limit = mass_fraction(static_cast<double>(top_p), zk);
+      uint32_t p_tau;
+      unsigned long long p_above_cnt, p_above_mass;
+      descend<T>(rp, v, vec_ok, inv_temp, y_max, true, limit, s, p_tau, p_above_cnt, p_above_mass);
+      // element i (in sorted order) is kept while the mass before it is <= limit
+      const float y = mul_rn(key_to_float(p_tau), inv_temp);
+      const unsigned long long q = mass_fixed(exp_det(sub_rn(y, y_max)));
+      unsigned long long p_ties;
+      if (p_above_mass > limit) {
+        p_ties = 0;  // cannot happen: the descent stops at the first crossing key
+      } else if (q == 0) {
+        p_ties = ~0ull;
+      } else {
+        p_ties = (limit - p_above_mass) / q + 1;
+      }
+      // the tighter of the two prefixes wins
+      bool p_tighter;
+      if (!has_k) {
+        p_tighter = true;
+      } else if (p_tau != k_tau) {
+        p_tighter = p_tau > k_tau;
+      } else {
+        p_tighter = p_ties < k_ties;
+      }
+      if (p_tighter) {
+        tau = p_tau;
+        tie_keep = p_ties;
+        // the kept mass follows from the number of ties actually present
+        int local = 0;
+        for_each_key<T>(rp, v, vec_ok, [&](uint32_t key, int) { local += (key == p_tau) ? 1 : 0; });
+        const unsigned long long present = static_cast<unsigned long long>(block_sum_int(local, s.red));
+        const unsigned long long used = p_ties < present ? p_ties : present;
+        tie_keep = used;
+        kept_mass = p_above_mass + used * q;
+      }
+    }
+  }
+
+  // ---- draw: invert the CDF over the kept set in token-id order
+  const unsigned long long rid = row_ids ? static_cast<unsigned long long>(row_ids[row])
+                                         : static_cast<unsigned long long>(row);
+  const unsigned long long target = mass_scale_u24(uniform_u24(seed, rid, step), kept_mass);
+  if (tid == 0) s.pick = -1;
+  __syncthreads();
+  constexpr int kPer = 8;
+  unsigned long long mass_base = 0, tie_base = 0;
+  int last_kept = -1;
+  for (int base = 0; base < v; base += kThreads * kPer) {
+    const int i0 = base + tid * kPer;
+    unsigned long long my_mass = 0, my_ties = 0;
+    uint32_t keys[kPer];
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+      const int i = i0 + j;
+      keys[j] = (i < v) ? float_to_key(Elem<T>::to_float(rp[i])) : 0u;
+      if (i < v && keys[j] == tau) ++my_ties;
+    }
+    unsigned long long tie_total;
+    unsigned long long tie_off = tie_base + block_exscan_u64(my_ties, s.scan, tie_total);
+    unsigned long long q[kPer];
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+      const int i = i0 + j;
+      bool kept = false;
+      if (i < v) {
+        if (keys[j] > tau) {
+          kept = true;
+        } else if (keys[j] == tau) {
+          kept = tie_off < tie_keep;
+          ++tie_off;
+        }
+      }
+      q[j] = 0;
+      if (kept) {
+        const float y = mul_rn(key_to_float(keys[j]), inv_temp);
+        q[j] = mass_fixed(exp_det(sub_rn(y, y_max)));
+        last_kept = i;
+      }
+      my_mass += q[j];
+    }
+    unsigned long long mass_total;
+    unsigned long long acc = mass_base + block_exscan_u64(my_mass, s.scan, mass_total);
+    if (acc <= target && acc + my_mass > target) {
+#pragma unroll
+      for (int j = 0; j < kPer; ++j) {
+        acc += q[j];
+        if (q[j] != 0 && acc > target) {
+          s.pick = i0 + j;
+          break;
+        }
+      }
+    }
+    mass_base += mass_total;
+    tie_base += tie_total;
+    __syncthreads();
+    if (s.pick >= 0) break;
+  }
+  // target == kept_mass can only happen when kept_mass is 0 (all masses underflowed):
+  // fall back to the last kept element, or the row maximum position.
+  if (s.pick < 0) {
+    const int cand = last_kept;
+    int best = cand;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) best = max(best, __shfl_xor_sync(0xffffffffu, best, o));
+    __syncthreads();
+    if ((tid & 31) == 0) s.red[tid >> 5] = best;
+    __syncthreads();
+    if (tid == 0) {
+      int b = -1;
+      for (int w = 0; w < kWarps; ++w) b = max(b, s.red[w]);
+      s.pick = b < 0 ? 0 : b;
+    }
+    __syncthreads();
+  }
+  if (tid == 0) out[row] = s.pick;
+}
+
+template <typename T>
+int launch_sampling(const void* logits, long long row_stride, int rows, int v, const long long* row_ids,
+                    float inv_temp, int top_k, float top_p, unsigned long long seed, unsigned long long step,
+                    int* out, cudaStream_t stream) {
+  const T* lp = static_cast<const T*>(logits);
+  cudaError_t e;
+  if (top_k >= 1 && top_k <= kMaxTopK) {
+    static bool configured = false;
+    if (!configured) {
+      e = cudaFuncSetAttribute(sample_topk_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(sizeof(TopkSmem)));
+      if (e != cudaSuccess) return -10;
+      configured = true;
+    }
+    sample_topk_kernel<T><<<rows, kThreads, sizeof(TopkSmem), stream>>>(lp, row_stride, v, row_ids, inv_temp, top_k,
+                                                                         top_p, seed, step, out);
+  } else {
+    static bool configured = false;
+    if (!configured) {
+      e = cudaFuncSetAttribute(sample_general_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(sizeof(GeneralSmem)));
+      if (e != cudaSuccess) return -10;
+      configured = true;
+    }
+    sample_general_kernel<T><<<rows, kThreads, sizeof(GeneralSmem), stream>>>(lp, row_stride, v, row_ids, inv_temp,
+                                                                            top_k, top_p, seed, step, out);
+  }
+  e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -11;
+}
+
+}  // namespace
+}  // namespace ka
+
+extern "C" int ka_sample(const void* logits, int dtype, long long row_stride, int rows, int vocab,
+                         const long long* row_ids, float inv_temperature, int top_k, float top_p,
+                         unsigned long long seed, unsigned long long step, int* out, void* stream) {
+  using namespace ka;
+  if (rows <= 0) return 0;
+  if (vocab <= 0 || !(inv_temperature > 0.f) || !(top_p > 0.f)) return -1;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case KA_DTYPE_F32:
+      return launch_sampling<float>(logits, row_stride, rows, vocab, row_ids, inv_temperature, top_k, top_p, seed,
+                                    step, out, st);
+    case KA_DTYPE_BF16:
+      return launch_sampling<__nv_bfloat16>(logits, row_stride, rows, vocab, row_ids, inv_temperature, top_k, top_p,
+                                            seed, step, out, st);
+    case KA_DTYPE_F16:
+      return launch_sampling<__half>(logits, row_stride, rows, vocab, row_ids, inv_temperature, top_k, top_p, seed,
+                                     step, out, st);
+    default:
+      return -2;
+  }
+}

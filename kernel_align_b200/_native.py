@@ -43,7 +43,30 @@ def cuda() -> ctypes.CDLL:
          c_int, c_int, c_int, c_int, c_int, c_int, c_int,
          c_uint, c_float, c_int, c_int, c_int, c_ulonglong, c_void_p],
     )
+    _bind(
+        lib,
+        "ka_sample",
+        c_int,
+        [c_void_p, c_int, c_longlong, c_int, c_int, c_void_p, c_float, c_int, c_float,
+         c_ulonglong, c_ulonglong, c_void_p, c_void_p],
+    )
+    _bind(
+        lib,
+        "ka_logits_logp",
+        c_int,
+        [c_void_p, c_int, c_longlong, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_int, c_void_p],
+    )
     return lib
+
+
+DTYPE_CODES = {"torch.float32": 0, "torch.bfloat16": 1, "torch.float16": 2}
+
+
+def dtype_code(dtype) -> int:
+    try:
+        return DTYPE_CODES[str(dtype)]
+    except KeyError:
+        raise TypeError(f"unsupported dtype {dtype}; expected float32, bfloat16 or float16") from None
 
 
 @lru_cache(maxsize=None)

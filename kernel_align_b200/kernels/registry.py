@@ -42,7 +42,8 @@ class OpBackend(Enum, metaclass=_LookupMeta):
     SM100_ALLREDUCE = "kernel_align_b200.parallel.collectives.all_reduce_det"
     SM100_GEMM_RS = "kernel_align_b200.parallel.tp_gemm.gemm_reduce_scatter"
     SM100_AG_GEMM = "kernel_align_b200.parallel.tp_gemm.all_gather_gemm"
-    # names the reference exposes; served by the native operators above
+    # names the reference exposes: enum aliases of the native operators above (same value),
+    # so OpBackend["FLASHINFER"] is OpBackend.SM100_FUSED_LOGP
     FLASH_ATTN = "kernel_align_b200.ops.attention.attention"
     FLASHINFER = "kernel_align_b200.ops.fused_logp.lmhead_logp"
     ROCM_AITER = "kernel_align_b200.ops.fused_logp.lmhead_logp"
@@ -94,7 +95,7 @@ class KernelRegistry:
     def dispatch_legacy(self, op_type: str) -> str:
         """The reference's two-way answer (``FLASHINFER`` for log-prob ops, ``FLASH_ATTN``
         otherwise), for callers that compare against those strings."""
-        return OpBackend.FLASHINFER.name if "logp" in op_type else OpBackend.FLASH_ATTN.name
+        return "FLASHINFER" if "logp" in op_type else "FLASH_ATTN"
 
     def override(self, backend: OpBackend, dotted_path: str) -> None:
         """Route ``backend`` to another callable for the rest of the process."""

@@ -1,0 +1,64 @@
+"""Peer memory for the fused compute+collective kernels: one symmetric buffer per rank that
+every other rank of the node can load from and store to over NVLink.
+
+``PeerArena`` wraps ``torch.distributed._symmetric_memory``: every rank allocates the same
+number of bytes, the rendezvous maps all of them into every process, and kernels receive the
+list of base addresses (``ptrs[r]`` is rank ``r``'s buffer as seen from this process). Kernels
+only use plain peer loads/stores on these addresses.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+
+class PeerArena:
+    def __init__(self, nbytes: int, group: Optional[dist.ProcessGroup] = None, device=None):
+        import torch.distributed._symmetric_memory as symm
+
+        if not dist.is_initialized():
+            raise RuntimeError("PeerArena needs an initialised process group")
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank = dist.get_rank(self.group)
+        self.world = dist.get_world_size(self.group)
+        self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.nbytes = (int(nbytes) + 255) // 256 * 256
+        self.buf = symm.empty(self.nbytes, dtype=torch.uint8, device=self.device)
+        self.handle = symm.rendezvous(self.buf, self.group)
+        self.buf.zero_()
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+
+    def zero(self) -> None:
+        """Collectively clear the arena (after an aborted launch left flags half-written)."""
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)
+        self.buf.zero_()
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)
+
+
+_vp_groups: dict = {}
+
+
+def vocab_parallel_group(vocab: int, panel_rows: int = 32768, group: Optional[dist.ProcessGroup] = None):
+    """The :class:`~kernel_align_b200.ops.fused_logp.VocabParallel` description for the
+    current process group, with its exchange arena allocated once and cached."""
+    from ..ops import fused_logp
+    from .. import _native
+
+    g = group if group is not None else dist.group.WORLD
+    key = (id(g), vocab, panel_rows)
+    vp = _vp_groups.get(key)
+    if vp is None:
+        world = dist.get_world_size(g)
+        nbytes = _native.cuda().ka_lmhead_logp_exchange_bytes(world, panel_rows)
+        arena = PeerArena(nbytes, g)
+        vp = fused_logp.VocabParallel(rank=arena.rank, world=world, exchange_ptrs=arena.ptrs, epoch=1,
+                                      panel_rows=panel_rows)
+        vp.arena = arena  # keep the mapping alive
+        _vp_groups[key] = vp
+    return vp

@@ -1,0 +1,80 @@
+"""Infrastructure: logger, device context, registry, executor (the reference's
+rl_engine/tests/test_dispatch.py, with assertions)."""
+import logging
+
+import pytest
+
+from kernel_align_b200.executors.rollout import RolloutExecutor
+from kernel_align_b200.kernels.registry import OpBackend, kernel_registry
+from kernel_align_b200.platforms.constants import constants
+from kernel_align_b200.platforms.device import device_ctx
+from kernel_align_b200.utils.logger import LINE_FORMAT, init_logger, logger
+
+
+class _Capture(logging.Handler):
+    def __init__(self):
+        super().__init__()
+        self.records = []
+
+    def emit(self, record):
+        self.records.append(record.getMessage())
+
+
+def test_logger_once_and_rank(monkeypatch):
+    cap = _Capture()
+    logger.addHandler(cap)
+    try:
+        logger.reset_once_cache()
+        for _ in range(3):
+            logger.info_once("unique message %s", "x")
+        for _ in range(2):
+            logger.warn_once("careful")
+        assert cap.records.count("unique message x") == 1
+        assert cap.records.count("careful") == 1
+        monkeypatch.setenv("RANK", "1")
+        logger.info_on_rank("only on zero", 0)
+        logger.info_on_rank("only on one", 1)
+        assert "only on zero" not in cap.records and "only on one" in cap.records
+    finally:
+        logger.removeHandler(cap)
+    assert init_logger("RL-Engine") is logger
+    assert LINE_FORMAT == "%(levelname)s %(asctime)s [%(name)s]: %(message)s"
+    assert logger.propagate is False
+
+
+def test_constants_surface():
+    names = ["DeviceType", "BackendLib", "PrecisionType", "SamplingMethod", "MemoryFormat", "OperatorFusionLevel",
+             "KernelOptimizationLevel", "LoggingLevel", "ProfilingMode", "DistributedStrategy", "CheckpointFormat",
+             "ActivationFunction"]
+    for n in names:
+        assert hasattr(constants, n)
+    assert constants.DeviceType.CUDA.value == "cuda"
+    assert constants.BackendLib.NATIVE.value == "native"
+    assert constants.DistributedStrategy.HYBRID.value == "hybrid"
+    assert constants.ActivationFunction.SILU.value == "silu"
+
+
+def test_device_and_registry():
+    assert device_ctx.device_type in ("cuda", "cpu")
+    assert device_ctx.is_rocm is False
+    assert device_ctx.rank == 0 or device_ctx.world_size > 1
+    import torch
+
+    want = torch.bfloat16 if device_ctx.device.type == "cuda" else torch.float32
+    assert device_ctx.get_preferred_dtype() == want
+    assert kernel_registry.dispatch("fused_logp") == "SM100_FUSED_LOGP"
+    assert kernel_registry.dispatch("attention") == "SM100_ATTENTION"
+    assert kernel_registry.dispatch("sampling") == "SM100_SAMPLING"
+    assert kernel_registry.dispatch_legacy("fused_logp") == "FLASHINFER"
+    assert kernel_registry.dispatch_legacy("attention") == "FLASH_ATTN"
+    with pytest.raises(ValueError, match="Supported backends"):
+        OpBackend["NOPE"]
+    fn = kernel_registry.resolve(kernel_registry.dispatch("fused_logp"))
+    assert callable(fn)
+    assert kernel_registry.get_op_path(OpBackend.FLASHINFER).endswith("lmhead_logp")
+
+
+def test_executor_flow():
+    result = RolloutExecutor().execute_rollout()
+    assert result["status"] == "success"
+    assert result["kernels"] == ["SM100_FUSED_LOGP", "SM100_ATTENTION"]

@@ -1,0 +1,101 @@
+"""GPU tier: fused LM-head log-prob and log-prob from logits against fp32 PyTorch."""
+import pytest
+import torch
+
+from kernel_align_b200.ops import cpu_ops, fused_logp
+from kernel_align_b200.ops.logits_logp import logits_logp
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref(h, w, ids, scale=1.0):
+    out = torch.empty(h.shape[0], dtype=torch.float32, device=h.device)
+    lse = torch.empty_like(out)
+    for i in range(0, h.shape[0], 1024):
+        lg = (h[i:i + 1024].float() @ w.float().T) * scale
+        lse[i:i + 1024] = torch.logsumexp(lg, -1)
+        out[i:i + 1024] = lg.gather(-1, ids[i:i + 1024, None]).squeeze(-1) - lse[i:i + 1024]
+    return out, lse
+
+
+def _inputs(dev, m, k, v, seed=0):
+    g = torch.Generator(device=dev).manual_seed(seed)
+    h = torch.randn(m, k, device=dev, generator=g).to(torch.bfloat16)
+    w = (torch.randn(v, k, device=dev, generator=g) * 0.02).to(torch.bfloat16)
+    ids = torch.randint(0, v, (m,), device=dev, generator=g)
+    return h, w, ids
+
+
+@pytest.mark.parametrize("cta_group", [1, 2])
+@pytest.mark.parametrize("m,k,v,scale", [(256, 256, 1024, 1.0), (300, 512, 5000, 1 / 0.7), (1000, 1024, 20000, 1.0),
+                                         (130, 4096, 128256, 1.0)])
+def test_fused_logp_matches_fp32_reference(cuda_device, cta_group, m, k, v, scale):
+    h, w, ids = _inputs(cuda_device, m, k, v)
+    out, lse = fused_logp.lmhead_logp(h, w, ids, scale=scale, cta_group=cta_group, return_lse=True, check=True)
+    ref, ref_lse = _ref(h, w, ids, scale)
+    assert (out - ref).abs().max().item() < 2e-3
+    assert (lse - ref_lse).abs().max().item() < 2e-3
+
+
+def test_fused_logp_vs_cpu_library(cuda_device):
+    h, w, ids = _inputs(cuda_device, 256, 256, 1024, seed=3)
+    out = fused_logp.lmhead_logp(h, w, ids, check=True)
+    ref = cpu_ops.lmhead_logp_cpu(h.cpu(), w.cpu(), ids.cpu())
+    assert (out.cpu() - ref).abs().max().item() < 2e-3
+
+
+def test_fused_logp_bitwise_batch_invariant_and_repeatable(cuda_device):
+    h, w, ids = _inputs(cuda_device, 1536, 512, 9000, seed=1)
+    full = fused_logp.lmhead_logp(h, w, ids, check=True)
+    assert torch.equal(full, fused_logp.lmhead_logp(h, w, ids, check=True))
+    for lo, hi in ((0, 1), (5, 133), (700, 1536)):
+        part = fused_logp.lmhead_logp(h[lo:hi], w, ids[lo:hi], check=True)
+        assert torch.equal(part, full[lo:hi])
+    # the row panel size only bounds scratch
+    small = fused_logp.lmhead_logp(h, w, ids, panel_rows=512, check=True)
+    assert torch.equal(small, full)
+    # 1-CTA and 2-CTA tiles issue the same per-row arithmetic
+    assert torch.equal(fused_logp.lmhead_logp(h, w, ids, cta_group=1, check=True), full)
+
+
+def test_fused_logp_ignored_ids_and_3d(cuda_device):
+    h, w, ids = _inputs(cuda_device, 4 * 64, 256, 1024, seed=2)
+    ids = ids.clone()
+    ids[3] = -100
+    out = fused_logp.lmhead_logp(h.view(4, 64, 256), w, ids.view(4, 64), check=True)
+    assert out.shape == (4, 64) and out.view(-1)[3].item() == 0.0
+
+
+def test_fused_logp_scratch_is_constant_in_rows(cuda_device):
+    assert fused_logp.workspace_bytes(128256) < 32 * 2**20
+    h, w, ids = _inputs(cuda_device, 2048, 256, 4096)
+    fused_logp.lmhead_logp(h, w, ids)
+    torch.cuda.synchronize()
+    torch.cuda.reset_peak_memory_stats()
+    base = torch.cuda.memory_allocated()
+    fused_logp.lmhead_logp(h, w, ids)
+    torch.cuda.synchronize()
+    assert torch.cuda.max_memory_allocated() - base < 1 * 2**20  # output + int64 ids only
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_logits_logp(cuda_device, dtype):
+    g = torch.Generator(device=cuda_device).manual_seed(4)
+    logits = (torch.randn(6, 33, 5003, device=cuda_device, generator=g) * 3).to(dtype)
+    ids = torch.randint(0, 5003, (6, 33), device=cuda_device, generator=g)
+    out, lse = logits_logp(logits, ids, scale=1 / 0.7, return_lse=True)
+    ref = torch.log_softmax(logits.float() / 0.7, -1).gather(-1, ids[..., None]).squeeze(-1)
+    assert out.shape == (6, 33)
+    assert (out - ref).abs().max().item() < 1e-4
+    assert (lse - torch.logsumexp(logits.float() / 0.7, -1)).abs().max().item() < 1e-4
+    one = logits_logp(logits[2:3], ids[2:3], scale=1 / 0.7)
+    assert torch.equal(one, out[2:3])
+
+
+def test_logits_logp_llama_vocab(cuda_device):
+    g = torch.Generator(device=cuda_device).manual_seed(5)
+    logits = (torch.randn(64, 128256, device=cuda_device, generator=g) * 2).to(torch.bfloat16)
+    ids = torch.randint(0, 128256, (64,), device=cuda_device, generator=g)
+    out = logits_logp(logits, ids)
+    ref = torch.log_softmax(logits.float(), -1).gather(-1, ids[:, None]).squeeze(-1)
+    assert (out - ref).abs().max().item() < 1e-4

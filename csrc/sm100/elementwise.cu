@@ -59,7 +59,7 @@ rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restr
       }
     }
     const float total = block_sum_fixed(ss, s_warp, blockDim.x >> 5);
-    const float inv = rsqrtf(__fadd_rn(__fdiv_rn(total, static_cast<float>(d)), eps));
+    const float inv = __fdiv_rn(1.f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, static_cast<float>(d)), eps)));
     const Bf16x8* wp = reinterpret_cast<const Bf16x8*>(w);
     Bf16x8* yp = reinterpret_cast<Bf16x8*>(y + static_cast<size_t>(row) * d);
     const Bf16x8* src = (rp && ro) ? reinterpret_cast<const Bf16x8*>(ro) : xp;

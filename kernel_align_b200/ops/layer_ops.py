@@ -1,0 +1,132 @@
+"""RMSNorm (with fused residual add), rotary embedding and SwiGLU.
+
+CUDA: ``csrc/sm100/elementwise.cu`` (bf16 in/out, fp32 math, fixed-order reductions, one pass).
+CPU: ``csrc/cpu/layer_ops_cpu.cpp`` with the same rounding points. The reference only names
+these ops (README feature list, ``ActivationFunction.SILU`` in
+rl_engine/platforms/constants.py:75-80).
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from typing import Optional
+
+import torch
+
+from .. import _native
+
+
+def _sms(t: torch.Tensor) -> int:
+    return torch.cuda.get_device_properties(t.device).multi_processor_count
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _check(rc: int, name: str) -> None:
+    if rc != 0:
+        raise RuntimeError(f"{name} failed ({rc})")
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5, residual: Optional[torch.Tensor] = None):
+    """``y = rmsnorm(x + residual) * weight``. With ``residual`` returns ``(y, x + residual)``."""
+    d = x.shape[-1]
+    x2 = x.reshape(-1, d)
+    rows = x2.shape[0]
+    if x.device.type != "cuda":
+        lib = _native.cpu()
+        xf = x2.float().contiguous()
+        rf = residual.reshape(-1, d).float().contiguous() if residual is not None else None
+        wf = weight.float().contiguous()
+        y = torch.empty_like(xf)
+        ro = torch.empty_like(xf) if residual is not None else None
+        fn = lib.ka_cpu_rmsnorm
+        fn.restype = c_int
+        fn.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float]
+        _check(fn(xf.data_ptr(), rf.data_ptr() if rf is not None else None, wf.data_ptr(), y.data_ptr(),
+                  ro.data_ptr() if ro is not None else None, rows, d, float(eps)), "ka_cpu_rmsnorm")
+        y = y.to(x.dtype).reshape(x.shape)
+        return (y, ro.to(x.dtype).reshape(x.shape)) if residual is not None else y
+    if x.dtype != torch.bfloat16:
+        raise TypeError("the sm_100a rmsnorm takes bf16")
+    x2 = x2.contiguous()
+    r2 = residual.reshape(-1, d).contiguous() if residual is not None else None
+    y = torch.empty_like(x2)
+    ro = torch.empty_like(x2) if residual is not None else None
+    lib = _native.cuda()
+    fn = lib.ka_rmsnorm
+    fn.restype = c_int
+    fn.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p]
+    _check(fn(x2.data_ptr(), r2.data_ptr() if r2 is not None else None, weight.contiguous().data_ptr(), y.data_ptr(),
+              ro.data_ptr() if ro is not None else None, rows, d, float(eps), _sms(x), _stream(x)), "ka_rmsnorm")
+    y = y.reshape(x.shape)
+    return (y, ro.reshape(x.shape)) if residual is not None else y
+
+
+def rope_tables(max_pos: int, head_dim: int, theta: float = 500000.0, device="cpu"):
+    """``cos``/``sin`` tables ``[max_pos, head_dim/2]`` fp32, computed in float64 on the host so
+    that every device sees the same values."""
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float64) / head_dim))
+    ang = torch.arange(max_pos, dtype=torch.float64)[:, None] * inv[None, :]
+    return ang.cos().float().to(device), ang.sin().float().to(device)
+
+
+def rope_(x: torch.Tensor, positions: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """Rotate ``x`` ``[tokens, heads, head_dim]`` in place ("rotate half" convention)."""
+    tokens, heads, hd = x.shape
+    pos = positions.reshape(-1).to(torch.int64).contiguous()
+    if x.device.type != "cuda":
+        lib = _native.cpu()
+        xf = x.float().contiguous()
+        fn = lib.ka_cpu_rope
+        fn.restype = c_int
+        fn.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int]
+        _check(fn(xf.data_ptr(), pos.data_ptr(), cos.contiguous().data_ptr(), sin.contiguous().data_ptr(), tokens,
+                  heads, hd), "ka_cpu_rope")
+        x.copy_(xf.to(x.dtype))
+        return x
+    if x.dtype != torch.bfloat16 or x.stride(2) != 1 or x.stride(1) != hd:
+        raise ValueError("rope_ takes bf16 [tokens, heads, head_dim] with contiguous heads")
+    lib = _native.cuda()
+    fn = lib.ka_rope
+    fn.restype = c_int
+    fn.argtypes = [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+    _check(fn(x.data_ptr(), x.stride(0), pos.data_ptr(), cos.data_ptr(), sin.data_ptr(), tokens, heads, hd, _sms(x),
+              _stream(x)), "ka_rope")
+    return x
+
+
+def swiglu(gate_up: torch.Tensor, up: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``silu(gate) * up``. Either one ``[..., 2F]`` tensor holding ``[gate | up]`` or two ``[..., F]``."""
+    if up is None:
+        f = gate_up.shape[-1] // 2
+        g2 = gate_up.reshape(-1, 2 * f)
+        gate_v, up_v, stride = g2[:, :f], g2[:, f:], 2 * f
+        lead = gate_up.shape[:-1]
+    else:
+        f = gate_up.shape[-1]
+        gate_v, up_v, stride = gate_up.reshape(-1, f).contiguous(), up.reshape(-1, f).contiguous(), f
+        lead = gate_up.shape[:-1]
+    rows = gate_v.shape[0]
+    if gate_up.device.type != "cuda":
+        lib = _native.cpu()
+        gf, uf = gate_v.float().contiguous(), up_v.float().contiguous()
+        out = torch.empty_like(gf)
+        fn = lib.ka_cpu_swiglu
+        fn.restype = c_int
+        fn.argtypes = [c_void_p, c_void_p, c_void_p, c_longlong]
+        _check(fn(gf.data_ptr(), uf.data_ptr(), out.data_ptr(), gf.numel()), "ka_cpu_swiglu")
+        return out.to(gate_up.dtype).reshape(*lead, f)
+    if gate_up.dtype != torch.bfloat16:
+        raise TypeError("the sm_100a swiglu takes bf16")
+    if up is None and not gate_up.is_contiguous():
+        return swiglu(gate_up.contiguous())
+    out = torch.empty(rows, f, dtype=torch.bfloat16, device=gate_up.device)
+    lib = _native.cuda()
+    fn = lib.ka_swiglu
+    fn.restype = c_int
+    fn.argtypes = [c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p]
+    _check(fn(gate_v.data_ptr(), up_v.data_ptr(), stride, out.data_ptr(), rows, f, _sms(out), _stream(out)),
+           "ka_swiglu")
+    return out.reshape(*lead, f)

@@ -1,0 +1,2 @@
+"""SwiGLU entry point (see :mod:`kernel_align_b200.ops.layer_ops`)."""
+from .layer_ops import swiglu  # noqa: F401

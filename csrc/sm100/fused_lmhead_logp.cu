@@ -762,3 +762,76 @@ int ka_lmhead_logp_forward(const void* hidden, const void* weight, const long lo
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------
+// Allocation-free entry point (see fused_lmhead_logp_noalloc.h for who needs it and the rules).
+// ------------------------------------------------------------------------------------------
+#include <mutex>
+
+#include "fused_lmhead_logp_noalloc.h"
+
+// The kernel's scratch for callers that cannot allocate: partials, target logits, counters
+// and status for one panel of KA_NOALLOC_PANEL_ROWS rows at up to KA_NOALLOC_MAX_VOCAB
+// columns. In host code this name is only a handle for cudaGetSymbolAddress, never a pointer.
+static __device__ __align__(256) unsigned char ka_noalloc_scratch[KA_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_noalloc_mutex;
+void* g_noalloc_ptr[kMaxDevices] = {};
+
+// Device address of the scratch array on the current device, resolved once per device.
+void* noalloc_scratch_for_current_device() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, ka_noalloc_scratch);
+    if (e != cudaSuccess) {
+      fprintf(stderr, "[kernel_align_b200] cudaGetSymbolAddress(ka_noalloc_scratch) failed on device %d: %s\n", dev,
+              cudaGetErrorString(e));
+      return nullptr;
+    }
+    g_noalloc_ptr[dev] = p;
+  }
+  return g_noalloc_ptr[dev];
+}
+}  // namespace
+
+extern "C" int ka_lmhead_logp_forward_noalloc(const void* hidden, const void* weight, const long long* ids,
+                                              float* logp, float* lse, int m, int k, int vocab, float scale,
+                                              int cta_group, int num_sms, unsigned long long timeout_ns,
+                                              void* stream) {
+  if (vocab <= 0 || vocab > KA_NOALLOC_MAX_VOCAB ||
+      ka_lmhead_logp_workspace_bytes(vocab, KA_NOALLOC_PANEL_ROWS) > static_cast<size_t>(KA_NOALLOC_SCRATCH_BYTES)) {
+    fprintf(stderr,
+            "[kernel_align_b200] ka_lmhead_logp_forward_noalloc: vocab %d is outside the built-in scratch "
+            "(max %d); use ka_lmhead_logp_forward with a caller-provided workspace\n",
+            vocab, KA_NOALLOC_MAX_VOCAB);
+    return -30;
+  }
+  void* scratch = noalloc_scratch_for_current_device();
+  if (scratch == nullptr) return -31;
+  // Counters and status must start at zero; a call that was aborted may have left them dirty.
+  const size_t status_off = static_cast<size_t>(ka_lmhead_logp_status_offset(vocab, KA_NOALLOC_PANEL_ROWS));
+  const size_t counters_bytes = (KA_NOALLOC_PANEL_ROWS / ka::kBM) * sizeof(unsigned);
+  const size_t clear_from = (status_off - counters_bytes) / 256 * 256;  // rounded down into the tgt tail, which is
+                                                                        // rewritten before it is read
+  if (cudaMemsetAsync(static_cast<unsigned char*>(scratch) + clear_from, 0, status_off + 256 - clear_from,
+                      static_cast<cudaStream_t>(stream)) != cudaSuccess)
+    return -32;
+  return ka_lmhead_logp_forward(hidden, weight, ids, logp, lse, scratch, KA_NOALLOC_SCRATCH_BYTES, nullptr, m, k,
+                                vocab, vocab, 0, 1, 0, 1u, scale, KA_NOALLOC_PANEL_ROWS, cta_group, num_sms,
+                                timeout_ns, stream);
+}
+
+extern "C" int ka_lmhead_logp_noalloc_status(int vocab, int* host_out) {
+  if (vocab <= 0 || vocab > KA_NOALLOC_MAX_VOCAB) return -30;
+  void* scratch = noalloc_scratch_for_current_device();
+  if (scratch == nullptr) return -31;
+  const size_t status_off = static_cast<size_t>(ka_lmhead_logp_status_offset(vocab, KA_NOALLOC_PANEL_ROWS));
+  const cudaError_t e = cudaMemcpy(host_out, static_cast<unsigned char*>(scratch) + status_off,
+                                   ka::kStatusWords * sizeof(int), cudaMemcpyDeviceToHost);
+  return e == cudaSuccess ? 0 : -34;
+}

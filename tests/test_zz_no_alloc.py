@@ -1,0 +1,79 @@
+"""The allocation-free C entry point of the fused LM-head log-prob kernel.
+
+Some hosts of this library cannot create device memory: the serving engine next to them has
+reserved the GPU's memory for its own pool, or their loop must not run into the device-wide
+synchronisation an allocation implies. ``ka_lmhead_logp_forward_noalloc`` keeps the kernel's
+scratch in a fixed device array inside the library instead. This test drives it through the
+exported C symbol only (inputs and outputs are ordinary tensors, as they would be the
+caller's own buffers) and checks it against the regular entry point, twice in a row, because
+the second call runs on scratch the first one left behind.
+
+The file sorts last on purpose: a failure here cannot hide the result of any other test.
+"""
+import ctypes
+from ctypes import c_float, c_int, c_ulonglong, c_void_p
+
+import pytest
+import torch
+
+from kernel_align_b200 import _native
+from kernel_align_b200.ops import fused_logp
+
+pytestmark = pytest.mark.gpu
+
+MAX_VOCAB = 262144
+
+
+def _entry():
+    lib = _native.cuda()
+    fn = lib.ka_lmhead_logp_forward_noalloc
+    fn.restype = c_int
+    fn.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_int,
+                   c_ulonglong, c_void_p]
+    st = lib.ka_lmhead_logp_noalloc_status
+    st.restype = c_int
+    st.argtypes = [c_int, c_void_p]
+    return fn, st
+
+
+def _call(fn, h, w, ids, logp, lse, scale=1.0):
+    props = torch.cuda.get_device_properties(h.device)
+    return fn(h.data_ptr(), w.data_ptr(), ids.data_ptr(), logp.data_ptr(), lse.data_ptr(), h.shape[0], h.shape[1],
+              w.shape[0], scale, 2, props.multi_processor_count, 2_000_000_000,
+              torch.cuda.current_stream().cuda_stream)
+
+
+def test_noalloc_entry_matches_regular_entry_twice(cuda_device):
+    fn, status = _entry()
+    g = torch.Generator(device=cuda_device).manual_seed(21)
+    for call, (m, k, v) in enumerate([(9000, 512, 20011), (700, 256, 4096)]):
+        h = torch.randn(m, k, device=cuda_device, generator=g).to(torch.bfloat16)
+        w = (torch.randn(v, k, device=cuda_device, generator=g) * 0.02).to(torch.bfloat16)
+        ids = torch.randint(0, v, (m,), device=cuda_device, generator=g)
+        want, want_lse = fused_logp.lmhead_logp(h, w, ids, scale=1.3, return_lse=True, check=True)
+        logp = torch.full((m,), float("nan"), device=cuda_device)
+        lse = torch.full((m,), float("nan"), device=cuda_device)
+        torch.cuda.synchronize()
+        before = torch.cuda.memory_allocated()
+        rc = _call(fn, h, w, ids, logp, lse, scale=1.3)
+        torch.cuda.synchronize()
+        assert rc == 0, f"call {call}: rc {rc}"
+        assert torch.cuda.memory_allocated() == before
+        host = (ctypes.c_int * 8)()
+        assert status(v, host) == 0 and list(host)[0] == 0, list(host)
+        assert (logp - want).abs().max().item() < 2e-3
+        assert (lse - want_lse).abs().max().item() < 2e-3
+        # same tiles, same merge order: the two entry points agree bit for bit
+        assert torch.equal(logp, want)
+
+
+def test_noalloc_entry_rejects_oversized_vocab(cuda_device):
+    fn, _ = _entry()
+    h = torch.zeros(8, 64, device=cuda_device, dtype=torch.bfloat16)
+    ids = torch.zeros(8, device=cuda_device, dtype=torch.int64)
+    out = torch.zeros(8, device=cuda_device)
+    props = torch.cuda.get_device_properties(cuda_device)
+    # the size check comes first: the (deliberately tiny) weight pointer is never read
+    rc = fn(h.data_ptr(), h.data_ptr(), ids.data_ptr(), out.data_ptr(), out.data_ptr(), 8, 64, MAX_VOCAB + 1, 1.0, 2,
+            props.multi_processor_count, 2_000_000_000, torch.cuda.current_stream().cuda_stream)
+    assert rc == -30

@@ -1,0 +1,37 @@
+"""Multi-GPU tier: child processes under torchrun, one rank per GPU (skipped with < 2 GPUs)."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _run_worker(script, nproc, timeout=600, extra_env=None):
+    env = dict(os.environ)
+    env.setdefault("MASTER_ADDR", "127.0.0.1")
+    env.update(extra_env or {})
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(29500 + nproc), os.path.join(HERE, "workers", script)]
+    proc = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
+    lines = [l for l in proc.stdout.splitlines() if l.startswith("RESULT ")]
+    assert proc.returncode == 0 and lines, proc.stdout[-3000:] + proc.stderr[-3000:]
+    return json.loads(lines[-1][len("RESULT "):])
+
+
+def _world_sizes():
+    n = torch.cuda.device_count() if torch.cuda.is_available() else 0
+    return [w for w in (2, 4, 8) if w <= n]
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_vocab_parallel_logp_bitwise_equals_single_gpu(world):
+    if world not in _world_sizes():
+        pytest.skip(f"needs {world} GPUs")
+    res = _run_worker("vp_logp_worker.py", world)
+    assert res["all_ranks_ok"], res
+    assert res["small_err"] < 2e-3 and res["llama_err"] < 2e-3

@@ -1,0 +1,73 @@
+#!/usr/bin/env python
+"""Small, self-terminating workloads for profiler captures: one operator, a few launches.
+
+    python benchmarks/profile_case.py --op fused_logp --rows 4736
+    ncu --set full --clock-control none -k regex:fused_lmhead -s 2 -c 1 -o out \
+        python benchmarks/profile_case.py --op fused_logp --rows 4736
+
+Inputs are larger than the 126 MB L2 where the operator streams memory, but stay within a
+few GB so that a multi-pass capture ends within a minute.
+"""
+from __future__ import annotations
+
+import argparse
+
+import torch
+
+from _common import ROOT  # noqa: F401  (puts the repository root on sys.path)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--op", required=True,
+                    choices=["fused_logp", "logits_logp", "sampling", "rmsnorm", "swiglu", "gemm", "attention",
+                             "grpo_loss"])
+    ap.add_argument("--rows", type=int, default=4736)
+    ap.add_argument("--vocab", type=int, default=128256)
+    ap.add_argument("--hidden", type=int, default=4096)
+    ap.add_argument("--launches", type=int, default=3)
+    args = ap.parse_args()
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(0)
+    if args.op == "fused_logp":
+        from kernel_align_b200.ops.fused_logp import lmhead_logp
+
+        h = torch.randn(args.rows, args.hidden, device=dev, generator=g).to(torch.bfloat16)
+        w = torch.empty(args.vocab, args.hidden, device=dev, dtype=torch.bfloat16)
+        for i in range(0, args.vocab, 16384):
+            n = min(16384, args.vocab - i)
+            w[i:i + n] = (torch.randn(n, args.hidden, device=dev, generator=g) * 0.02).to(torch.bfloat16)
+        ids = torch.randint(0, args.vocab, (args.rows,), device=dev, generator=g)
+        fn = lambda: lmhead_logp(h, w, ids)  # noqa: E731
+    elif args.op == "logits_logp":
+        from kernel_align_b200.ops.logits_logp import logits_logp
+
+        x = (torch.randn(args.rows, args.vocab, device=dev, generator=g) * 2).to(torch.bfloat16)
+        ids = torch.randint(0, args.vocab, (args.rows,), device=dev, generator=g)
+        fn = lambda: logits_logp(x, ids)  # noqa: E731
+    elif args.op == "sampling":
+        from kernel_align_b200.ops.sampling import sample
+
+        x = (torch.randn(args.rows, args.vocab, device=dev, generator=g) * 2).to(torch.bfloat16)
+        fn = lambda: sample(x, top_k=50, top_p=0.9, temperature=0.7, seed=1, step=0)  # noqa: E731
+    elif args.op == "rmsnorm":
+        from kernel_align_b200.ops.layer_ops import rmsnorm
+
+        x = torch.randn(args.rows, args.hidden, device=dev, generator=g).to(torch.bfloat16)
+        w = torch.ones(args.hidden, device=dev, dtype=torch.bfloat16)
+        fn = lambda: rmsnorm(x, w, 1e-5, x)  # noqa: E731
+    elif args.op == "swiglu":
+        from kernel_align_b200.ops.layer_ops import swiglu
+
+        x = torch.randn(args.rows, 2 * 14336, device=dev, generator=g).to(torch.bfloat16)
+        fn = lambda: swiglu(x)  # noqa: E731
+    else:
+        raise SystemExit(f"--op {args.op}: no profile case defined yet")
+    for _ in range(args.launches):
+        out = fn()
+    torch.cuda.synchronize()
+    print("done", tuple(out.shape) if hasattr(out, "shape") else "")
+
+
+if __name__ == "__main__":
+    main()

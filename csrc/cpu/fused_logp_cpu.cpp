@@ -5,7 +5,7 @@
 // 8-lane accumulation order over K, logits are folded in row chunks of `chunk_rows` (the
 // chunk only bounds the temporary, it never enters the arithmetic), and the vocabulary is
 // decomposed exactly like the CUDA kernel: 8 canonical slices of ceil(V/8) columns,
-// 2048-column sub-slices folded left to right in groups of 32 columns, sub-slices merged
+// 1792-column sub-slices folded left to right in groups of 32 columns, sub-slices merged
 // left to right, slices merged by a balanced binary tree.
 #include <algorithm>
 #include <cmath>
@@ -17,7 +17,7 @@
 namespace {
 
 constexpr int kSlices = 8;
-constexpr int kSubCols = 2048;
+constexpr int kSubCols = 1792;
 constexpr int kGroup = 32;
 const float kNegInf = -std::numeric_limits<float>::infinity();
 

@@ -9,7 +9,7 @@
 //
 // Reproducibility contract (per row, bitwise):
 //   * the global vocabulary is cut into 8 canonical slices of ceil(V/8) columns, each slice
-//     into sub-slices of 2048 columns, each sub-slice into 256-column MMA tiles;
+//     into sub-slices of 1792 columns, each sub-slice into 256-column MMA tiles;
 //   * one thread owns one row of one sub-slice and folds its tiles left to right;
 //   * sub-slices of a slice are merged left to right, the 8 slices by a balanced binary
 //     tree. A rank that holds 8/N contiguous slices evaluates a whole subtree locally and the
@@ -27,6 +27,7 @@
 #include <cfloat>
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 #include <cuda_bf16.h>
 #include <math_constants.h>
 
@@ -42,7 +43,7 @@ constexpr int kBM = 128;         // rows per CTA (TMEM lanes)
 constexpr int kBN = 256;         // columns per MMA tile
 constexpr int kBK = 64;          // bf16 elements per 128-byte swizzled row
 constexpr int kUmmaK = 16;       // K per tcgen05.mma of kind::f16
-constexpr int kSubCols = 2048;   // columns per canonical sub-slice (8 tiles)
+constexpr int kSubCols = 1792;   // columns per canonical sub-slice (7 tiles)
 constexpr int kSlices = 8;       // canonical slices of the global vocabulary
 constexpr int kThreads = 192;    // warps 0-3 epilogue, 4 TMA producer, 5 MMA issuer
 constexpr int kMaxDeferred = 512;
@@ -101,9 +102,14 @@ __device__ __forceinline__ void decode_item(const LogpParams& p, int i, Item& it
   const int m_local = r2 / cg_sz;
   const int c_local = r2 - m_local * cg_sz;
   it.m_tile = g * p.mg + m_local;
-  it.chunk = h * p.cg + c_local;
-  const int sl = it.chunk / p.sub;
-  const int q = it.chunk - sl * p.sub;
+  // Schedule position -> (slice, sub-slice): sub-slice major, so that the sub-slices that run
+  // side by side have the same position inside their slices and therefore the same number of
+  // tiles; CTAs that share W tiles through L2 then stay in step. The partials are stored
+  // slice major (chunk = slice * sub + sub-slice), which is what the merge walks.
+  const int sched = h * p.cg + c_local;
+  const int q = sched / p.n_slices_local;
+  const int sl = sched - q * p.n_slices_local;
+  it.chunk = sl * p.sub + q;
   const int slice_begin = sl * p.vs;
   const int slice_end = min(slice_begin + p.vs, p.v_local);
   it.col_begin = slice_begin + q * kSubCols;
@@ -729,7 +735,14 @@ int ka_lmhead_logp_forward(const void* hidden, const void* weight, const long lo
   p.rank = rank;
   p.scale = scale;
   p.timeout_ns = timeout_ns;
-  p.cg = p.n_chunks < 8 ? p.n_chunks : 8;
+  // Sub-slices that run side by side (cg) x row tiles that run side by side (mg) ~ CTA pairs.
+  // KA_LOGP_CG overrides the default split for tuning.
+  int cg_pref = 8;
+  if (const char* e = getenv("KA_LOGP_CG")) {
+    const int v = atoi(e);
+    if (v >= 1 && v <= 64) cg_pref = v;
+  }
+  p.cg = p.n_chunks < cg_pref ? p.n_chunks : cg_pref;
   {
     const int pairs = num_sms / cta_group;
     int mg = pairs / p.cg;

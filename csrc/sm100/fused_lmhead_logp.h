@@ -22,7 +22,7 @@ struct LogpParams {
   int v_global, v_local, vocab_offset;
   int row_begin, rows;   // panel processed by this launch
   int vs;                // canonical slice width = ceil(V / 8)
-  int sub;               // sub-slices per slice = ceil(vs / 2048)
+  int sub;               // sub-slices per slice = ceil(vs / 1792)
   int n_slices_local;    // 8 / world
   int n_chunks;          // n_slices_local * sub
   int ldp;               // panel leading dimension (rows, multiple of 256)

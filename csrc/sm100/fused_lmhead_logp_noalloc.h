@@ -31,7 +31,7 @@
 
 #define KA_NOALLOC_MAX_VOCAB 262144
 #define KA_NOALLOC_PANEL_ROWS 8192
-#define KA_NOALLOC_SCRATCH_BYTES 8421888
+#define KA_NOALLOC_SCRATCH_BYTES 9994752
 
 extern "C" {
 

@@ -4,7 +4,7 @@
 without ever materialising the ``[rows, vocab]`` logits. On CUDA it runs the hand-written
 tcgen05/TMA kernel of ``csrc/sm100/fused_lmhead_logp.cu``; on CPU the C++ implementation of
 ``csrc/cpu/fused_logp_cpu.cpp``. Both follow the same canonical decomposition of the
-vocabulary (8 slices, 2048-column sub-slices, balanced merge tree), so a row's result does
+vocabulary (8 slices, 1792-column sub-slices, balanced merge tree), so a row's result does
 not depend on the batch it was computed in, nor on how many GPUs the vocabulary is sharded
 over.
 

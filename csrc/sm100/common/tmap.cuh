@@ -34,6 +34,16 @@ inline int make_tmap_2d_16bit_sw128(CUtensorMap* map, CUtensorMapDataType dt, co
                                     uint32_t box_rows, uint32_t box_cols) {
   EncodeTiledFn fn = get_encode_tiled();
   if (!fn) return -1;
+  // The encode call is a driver entry point and needs the tensor's context current on this
+  // thread. A host thread that has not touched CUDA yet (an autograd worker, for one) has
+  // none: bind the device the tensor lives on.
+  {
+    cudaPointerAttributes at;
+    if (cudaPointerGetAttributes(&at, base) == cudaSuccess && at.type == cudaMemoryTypeDevice)
+      cudaSetDevice(at.device);
+    else
+      cudaGetLastError();
+  }
   if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0 || (row_stride_elems * 2) % 16 != 0) return -2;
   cuuint64_t gdim[2] = {cols, rows};
   cuuint64_t gstride[1] = {row_stride_elems * 2};

@@ -1,0 +1,527 @@
+// Batch-invariant bf16 GEMM for sm_100a: persistent CTA pairs, TMA operand ring,
+// tcgen05.mma (cta_group::2, M=256 N=256 K=16) into double-buffered TMEM accumulators, and an
+// epilogue that either stores the tile or emits fp32 K-slice partials for the tensor-parallel
+// reduce-scatter (see gemm.h). Operands may be K-major or MN-major (the latter serves the
+// backward GEMMs without transposes).
+//
+// The reference has no GEMM of its own; its registry only names backends
+// (rl_engine/kernels/registry.py:20-30).
+#include <cstdint>
+#include <cstdio>
+#include <cstdlib>
+#include <cuda_bf16.h>
+
+#include "common/bounded_wait.cuh"
+#include "common/ptx.cuh"
+#include "common/tmap.cuh"
+#include "gemm.h"
+
+namespace ka {
+namespace {
+
+constexpr int kG = 2;              // CTAs per tile
+constexpr int kBM = 128;           // rows per CTA
+constexpr int kBN = 256;           // columns per tile
+constexpr int kBK = 64;            // K per stage
+constexpr int kUmmaK = 16;
+constexpr int kThreads = 192;      // warps 0-3 epilogue, 4 producer, 5 MMA
+constexpr int kStages = 6;
+constexpr int kABytes = kBM * kBK * 2;            // 16 KiB
+constexpr int kBBytes = (kBN / kG) * kBK * 2;     // 16 KiB
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kTxBytes = kStageBytes * kG;
+constexpr int kTileBytes = kStages * kStageBytes;
+constexpr int kSmemBytes = kTileBytes + 1024 + 1024;
+constexpr int kGroupM = 8;         // row tiles that share a column tile in the schedule
+
+struct Control {
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  uint64_t tfull[2];
+  uint64_t tempty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+enum Where : int { kWProducer = 11, kWMmaFull = 12, kWMmaTmem = 13, kWEpi = 14, kWReduceFlag = 15, kWGatherFlag = 16 };
+
+// MN-major operand tile written by TMA as 64-element (128 B) wide boxes of 64 K-rows each:
+// 16-byte chunks along MN are contiguous (swizzled), 8 K-rows form a 1024 B group (SBO), the
+// next 64 MN elements start one box (8 KiB) further (LBO).
+__device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(8192 >> 4) << 16;
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+
+struct Unit {
+  int m_blk, n_blk, slice;
+};
+
+__device__ __forceinline__ void decode_unit(const GemmParams& p, int tiles_m, int tiles_n, int u, Unit& out) {
+  const int t = u / p.k_slices;
+  out.slice = u - t * p.k_slices;
+  const int per_group = kGroupM * tiles_n;
+  const int g = t / per_group;
+  const int gm = min(kGroupM, tiles_m - g * kGroupM);
+  const int r = t - g * per_group;
+  out.n_blk = r / gm;
+  out.m_blk = g * kGroupM + (r - out.n_blk * gm);
+  // all-gather mode: start with the row tiles whose source is this rank, they need no wait
+  if (p.a_gather) out.m_blk = (out.m_blk + (p.rank * p.a_rows_per_rank) / (kBM * kG)) % tiles_m;
+}
+
+__device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld_wait_dep(uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.wait::ld.sync.aligned;"
+      : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]),
+        "+r"(v[7]), "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]),
+        "+r"(v[14]), "+r"(v[15]), "+r"(v[16]), "+r"(v[17]), "+r"(v[18]), "+r"(v[19]),
+        "+r"(v[20]), "+r"(v[21]), "+r"(v[22]), "+r"(v[23]), "+r"(v[24]), "+r"(v[25]),
+        "+r"(v[26]), "+r"(v[27]), "+r"(v[28]), "+r"(v[29]), "+r"(v[30]), "+r"(v[31])
+      :
+      : "memory");
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// Store 32 consecutive accumulator columns of one row.
+__device__ __forceinline__ void store_group(const GemmParams& p, const uint32_t (&v)[32], long long row, int col,
+                                            int slice_global) {
+  if (col >= p.n) return;
+  const bool full = col + 32 <= p.n;
+  if (p.epilogue == kEpiStoreBf16) {
+    __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.c) + row * p.ldc + col;
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+      if (full || col + j + 8 <= p.n) {
+        uint4 o;
+        o.x = pack_bf16(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
+        o.y = pack_bf16(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+        o.z = pack_bf16(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]));
+        o.w = pack_bf16(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
+        *reinterpret_cast<uint4*>(dst + j) = o;
+      }
+    }
+  } else {
+    float* dst;
+    if (p.epilogue == kEpiStoreF32) {
+      dst = static_cast<float*>(p.c) + row * p.ldc + col;
+    } else {
+      const int owner = static_cast<int>(row / p.rows_per_rank);
+      const long long lr = row - static_cast<long long>(owner) * p.rows_per_rank;
+      dst = p.stage[owner] + (static_cast<long long>(slice_global) * p.rows_per_rank + lr) * p.n + col;
+    }
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+      if (full || col + j + 4 <= p.n) {
+        *reinterpret_cast<uint4*>(dst + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ float4 ld_f4_sys(const float* p) {
+  return ld_relaxed_sys_f4(reinterpret_cast<const float4*>(p));
+}
+__device__ __forceinline__ float4 add4(float4 a, float4 b) {
+  return make_float4(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y), __fadd_rn(a.z, b.z), __fadd_rn(a.w, b.w));
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                 const __grid_constant__ GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t tiles_addr = (raw_addr + 1023u) & ~1023u;
+  uint8_t* tiles = smem_raw + (tiles_addr - raw_addr);
+  Control* ctl = reinterpret_cast<Control*>(tiles + kTileBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = cluster_ctarank();
+  const bool leader = cta_rank == 0;
+  const int pair_id = blockIdx.x / kG;
+  const int n_pairs = gridDim.x / kG;
+  const int tiles_m = (p.m + kBM * kG - 1) / (kBM * kG);
+  const int tiles_n = (p.n + kBN - 1) / kBN;
+  const int n_units = tiles_m * tiles_n * p.k_slices;
+  const int k_per_slice = p.k / p.k_slices;
+  const int num_kb = (k_per_slice + kBK - 1) / kBK;
+
+  WaitCtx wctx{&ctl->abort_flag, p.status, p.timeout_ns};
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(smem_u32(&ctl->full[s]), 1);
+      mbar_init(smem_u32(&ctl->empty[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&ctl->tfull[b]), 1);
+      mbar_init(smem_u32(&ctl->tempty[b]), 4 * kG);
+    }
+    ctl->abort_flag = 0;
+    fence_mbar_init_cluster();
+  }
+  if (warp == 5) {
+    tmem_alloc<kG>(smem_u32(&ctl->tmem_base), 512);
+    tmem_relinquish<kG>();
+  }
+  if (warp == 4 && lane == 0) {
+    tma_prefetch_desc(&tm_a);
+    tma_prefetch_desc(&tm_b);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_arrive();
+  cluster_wait();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = ctl->tmem_base;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int u = pair_id; u < n_units && ok; u += n_pairs) {
+        Unit un;
+        decode_unit(p, tiles_m, tiles_n, u, un);
+        const int row0 = un.m_blk * (kBM * kG) + static_cast<int>(cta_rank) * kBM;
+        const int col0 = un.n_blk * kBN + static_cast<int>(cta_rank) * (kBN / kG);
+        const int kbase = un.slice * k_per_slice;
+        if (p.a_gather) {
+          // rows of another rank become readable when that rank's push has been flagged
+          const int src = row0 / p.a_rows_per_rank;
+          const int blk = (row0 - src * p.a_rows_per_rank) / kBM;
+          const int blocks = p.a_rows_per_rank / kBM;
+          if (row0 < p.m)
+            ok = flag_wait_bounded(p.a_flags[p.rank] + static_cast<size_t>(src) * blocks + blk, p.epoch, wctx,
+                                   kWGatherFlag, src * 65536 + blk);
+          if (!ok) break;
+        }
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = mbar_wait_bounded(smem_u32(&ctl->empty[stage]), phase ^ 1u, wctx, kWProducer, stage);
+          if (!ok) break;
+          const uint32_t a_dst = tiles_addr + stage * kStageBytes;
+          const uint32_t b_dst = a_dst + kABytes;
+          const uint32_t full = smem_u32(&ctl->full[stage]);
+          if (leader) mbar_arrive_expect_tx(full, kTxBytes);
+          const uint32_t full_leader = mapa_u32(full, 0);
+          const int k0 = kbase + kb * kBK;
+          if (p.a_major == 0) {
+            tma_load_2d_pair(a_dst, &tm_a, k0, row0, full_leader);
+          } else {
+            tma_load_2d_pair(a_dst, &tm_a, row0, k0, full_leader);
+            tma_load_2d_pair(a_dst + 8192, &tm_a, row0 + 64, k0, full_leader);
+          }
+          if (p.b_major == 0) {
+            tma_load_2d_pair(b_dst, &tm_b, k0, col0, full_leader);
+          } else {
+            tma_load_2d_pair(b_dst, &tm_b, col0, k0, full_leader);
+            tma_load_2d_pair(b_dst + 8192, &tm_b, col0 + 64, k0, full_leader);
+          }
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0 && leader) {
+      const uint32_t idesc = umma_idesc_bf16_f32(kBM * kG, kBN) | (static_cast<uint32_t>(p.a_major) << 15) |
+                             (static_cast<uint32_t>(p.b_major) << 16);
+      const uint32_t a_step = p.a_major == 0 ? 2u : 128u;  // descriptor units (16 B) per K=16
+      const uint32_t b_step = p.b_major == 0 ? 2u : 128u;
+      int stage = 0;
+      uint32_t phase = 0;
+      int abuf = 0;
+      uint32_t aphase = 0;
+      bool ok = true;
+      for (int u = pair_id; u < n_units && ok; u += n_pairs) {
+        ok = mbar_wait_bounded(smem_u32(&ctl->tempty[abuf]), aphase ^ 1u, wctx, kWMmaTmem, abuf);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(abuf * kBN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = mbar_wait_bounded(smem_u32(&ctl->full[stage]), phase, wctx, kWMmaFull, stage);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t a_addr = tiles_addr + stage * kStageBytes;
+          const uint64_t a_desc = p.a_major == 0 ? umma_desc_k_sw128(a_addr) : umma_desc_mn_sw128(a_addr);
+          const uint64_t b_desc =
+              p.b_major == 0 ? umma_desc_k_sw128(a_addr + kABytes) : umma_desc_mn_sw128(a_addr + kABytes);
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k) {
+            umma_bf16<kG>(d_tmem, a_desc + a_step * k, b_desc + b_step * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit<kG>(smem_u32(&ctl->empty[stage]));
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        umma_commit<kG>(smem_u32(&ctl->tfull[abuf]));
+        abuf ^= 1;
+        if (abuf == 0) aphase ^= 1u;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 0-3)
+    // Every named barrier below is reached by all 128 threads; leaving is decided from the
+    // shared abort flag right after a barrier.
+    const int tid = threadIdx.x;
+    bool ok = true;
+
+    if (p.a_gather) {
+      // ---- all-gather: push this rank's rows of A into every peer's gather buffer, one
+      // 128-row block at a time, then raise the block's flag on that peer.
+      const int blocks = p.a_rows_per_rank / kBM;
+      const int vec_per_row = p.k / 8;  // 16-byte vectors
+      const uint4* src = static_cast<const uint4*>(p.a_local);
+      for (int blk = blockIdx.x; blk < blocks; blk += gridDim.x) {
+        const long long v0 = static_cast<long long>(blk) * kBM * vec_per_row;
+        const long long nv = static_cast<long long>(kBM) * vec_per_row;
+        for (int d = 0; d < p.world; ++d) {
+          const int dst_rank = (p.rank + d) % p.world;  // start with the local copy
+          uint4* dst = static_cast<uint4*>(p.a_bufs[dst_rank]) +
+                       static_cast<long long>(p.rank) * p.a_rows_per_rank * vec_per_row + v0;
+          for (long long i = tid; i < nv; i += 128) dst[i] = src[v0 + i];
+        }
+        __threadfence_system();
+        epi_bar();
+        if (tid < p.world)
+          st_release_sys_u32(p.a_flags[tid] + static_cast<size_t>(p.rank) * blocks + blk, p.epoch);
+      }
+    }
+
+    int abuf = 0;
+    uint32_t aphase = 0;
+    const uint32_t tempty_leader = mapa_u32(smem_u32(&ctl->tempty[0]), 0);
+    for (int u = pair_id; u < n_units; u += n_pairs) {
+      Unit un;
+      decode_unit(p, tiles_m, tiles_n, u, un);
+      const long long row = static_cast<long long>(un.m_blk) * (kBM * kG) + cta_rank * kBM + tid;
+      const bool mine = mbar_wait_bounded(smem_u32(&ctl->tfull[abuf]), aphase, wctx, kWEpi, abuf);
+      ok = __all_sync(0xffffffffu, mine) != 0;
+      if (ok) {
+        tc_fence_after_sync();
+        const uint32_t trow = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + static_cast<uint32_t>(abuf * kBN);
+        const int slice_global = p.slice_base + un.slice;
+        uint32_t va[32], vb[32];
+        tmem_ld_32x32(trow, va);
+        tmem_ld_wait_dep(va);
+#pragma unroll
+        for (int g = 0; g < kBN / 32; g += 2) {
+          __syncwarp();
+          tmem_ld_32x32(trow + (g + 1) * 32, vb);
+          if (row < p.m) store_group(p, va, row, un.n_blk * kBN + g * 32, slice_global);
+          __syncwarp();
+          tmem_ld_wait_dep(vb);
+          if (g + 2 < kBN / 32) tmem_ld_32x32(trow + (g + 2) * 32, va);
+          if (row < p.m) store_group(p, vb, row, un.n_blk * kBN + (g + 1) * 32, slice_global);
+          __syncwarp();
+          if (g + 2 < kBN / 32) tmem_ld_wait_dep(va);
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(tempty_leader + static_cast<uint32_t>(abuf) * 8u);
+        abuf ^= 1;
+        if (abuf == 0) aphase ^= 1u;
+      }
+      if (p.epilogue == kEpiPartialF32) {
+        // publish: this CTA's 128 rows x 256 columns of slice `slice_global` are in place
+        __threadfence_system();
+        epi_bar();
+        if (ctl->abort_flag) {
+          ok = false;
+          break;
+        }
+        if (tid == 0) {
+          const long long row0 = static_cast<long long>(un.m_blk) * (kBM * kG) + cta_rank * kBM;
+          if (row0 < p.m) {
+            const int owner = static_cast<int>(row0 / p.rows_per_rank);
+            const int rblk = static_cast<int>((row0 - static_cast<long long>(owner) * p.rows_per_rank) / kBM);
+            const int rblks = p.rows_per_rank / kBM;
+            st_release_sys_u32(p.flags[owner] + (static_cast<size_t>(p.slice_base + un.slice) * rblks + rblk) * tiles_n +
+                                   un.n_blk,
+                               p.epoch);
+          }
+        }
+      } else if (!ok) {
+        break;
+      }
+    }
+
+    if (p.epilogue == kEpiPartialF32 && ok) {
+      // ---- reduce-scatter tail: the rows this rank owns, slices combined by a balanced tree
+      const int rblks = p.rows_per_rank / kBM;
+      const int items = rblks * tiles_n;
+      const int rows_valid = min(p.rows_per_rank, p.m - p.rank * p.rows_per_rank);
+      for (int it = blockIdx.x; it < items; it += gridDim.x) {
+        const int rblk = it / tiles_n, nb = it - rblk * tiles_n;
+        if (tid < p.total_slices)
+          flag_wait_bounded(p.flags[p.rank] + (static_cast<size_t>(tid) * rblks + rblk) * tiles_n + nb, p.epoch, wctx,
+                            kWReduceFlag, it);
+        epi_bar();
+        if (ctl->abort_flag) break;
+        const int ncols = min(kBN, p.n - nb * kBN);
+        const int vec_per_row = ncols / 4;
+        const size_t slice_stride = static_cast<size_t>(p.rows_per_rank) * p.n;
+        for (int i = tid; i < kBM * vec_per_row; i += 128) {
+          const int r = i / vec_per_row, c4 = i - r * vec_per_row;
+          const int lr = rblk * kBM + r;
+          if (lr >= rows_valid) continue;
+          const size_t off = static_cast<size_t>(lr) * p.n + nb * kBN + c4 * 4;
+          const float* base = p.stage[p.rank] + off;
+          float4 s[8];
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+            s[q] = q < p.total_slices ? ld_f4_sys(base + q * slice_stride) : make_float4(0.f, 0.f, 0.f, 0.f);
+          const float4 t01 = add4(s[0], s[1]), t23 = add4(s[2], s[3]), t45 = add4(s[4], s[5]), t67 = add4(s[6], s[7]);
+          float4 acc = add4(add4(t01, t23), add4(t45, t67));
+          __nv_bfloat16* outp = static_cast<__nv_bfloat16*>(p.out) + off;
+          if (p.residual) {
+            // residual add in bf16 arithmetic order: round the GEMM result first, as a separate
+            // bf16 linear + add would
+            const __nv_bfloat16* rp = static_cast<const __nv_bfloat16*>(p.residual) + off;
+            const uint2 rr = *reinterpret_cast<const uint2*>(rp);
+            const __nv_bfloat162 r01 = *reinterpret_cast<const __nv_bfloat162*>(&rr.x);
+            const __nv_bfloat162 r23 = *reinterpret_cast<const __nv_bfloat162*>(&rr.y);
+            acc.x = __fadd_rn(__bfloat162float(__float2bfloat16_rn(acc.x)), __bfloat162float(r01.x));
+            acc.y = __fadd_rn(__bfloat162float(__float2bfloat16_rn(acc.y)), __bfloat162float(r01.y));
+            acc.z = __fadd_rn(__bfloat162float(__float2bfloat16_rn(acc.z)), __bfloat162float(r23.x));
+            acc.w = __fadd_rn(__bfloat162float(__float2bfloat16_rn(acc.w)), __bfloat162float(r23.y));
+          }
+          uint2 o;
+          o.x = pack_bf16(acc.x, acc.y);
+          o.y = pack_bf16(acc.z, acc.w);
+          *reinterpret_cast<uint2*>(outp) = o;
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ common exit
+  if (ctl->abort_flag) {
+    st_shared_cluster_u32(mapa_u32(smem_u32(&ctl->abort_flag), cta_rank ^ 1u), 1u);
+    drain_in_flight();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_arrive();
+  cluster_wait();
+  if (warp == 5) {
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc<kG>(tmem_base, 512);
+  }
+}
+
+int max_ctas(int num_sms) {
+  static int cached = 0;
+  if (cached > 0) return cached;
+  if (cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+    return -1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(num_sms / 2 * 2));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = kSmemBytes;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int clusters = 0;
+  if (cudaOccupancyMaxActiveClusters(&clusters, gemm_bf16_kernel, &cfg) != cudaSuccess || clusters <= 0) {
+    cudaGetLastError();
+    clusters = num_sms / 2;
+  }
+  int n = clusters * 2;
+  if (n > num_sms / 2 * 2) n = num_sms / 2 * 2;
+  cached = n;
+  return n;
+}
+
+}  // namespace
+
+// Shared by the plain entry point and the tensor-parallel ones (tp_gemm.cu): build the
+// tensor maps for the operand layouts in `p` and launch.
+int gemm_launch(const void* a, long long lda, const void* b, long long ldb, const GemmParams& p, int num_sms,
+                bool full_grid, cudaStream_t stream) {
+  if (p.m <= 0 || p.n <= 0 || p.k <= 0) return 0;
+  if (p.k % 8 != 0 || p.n % 8 != 0 || lda % 8 != 0 || ldb % 8 != 0) return -1;
+  if (p.k_slices < 1 || p.k % p.k_slices != 0 || (p.k_slices > 1 && (p.k / p.k_slices) % kBK != 0)) return -2;
+  if (p.a_major == 1 && p.m % 8 != 0) return -3;
+  CUtensorMap tm_a, tm_b;
+  int rc;
+  if (p.a_major == 0)
+    rc = make_tmap_2d_16bit_sw128(&tm_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, a, p.m, p.k, lda, kBM, kBK);
+  else
+    rc = make_tmap_2d_16bit_sw128(&tm_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, a, p.k, p.m, lda, kBK, 64);
+  if (rc != 0) return -20 + rc;
+  if (p.b_major == 0)
+    rc = make_tmap_2d_16bit_sw128(&tm_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, b, p.n, p.k, ldb, kBN / kG, kBK);
+  else
+    rc = make_tmap_2d_16bit_sw128(&tm_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, b, p.k, p.n, ldb, kBK, 64);
+  if (rc != 0) return -40 + rc;
+  int ctas = max_ctas(num_sms);
+  if (ctas <= 0) return -10;
+  const int tiles_m = (p.m + kBM * kG - 1) / (kBM * kG), tiles_n = (p.n + kBN - 1) / kBN;
+  const int units = tiles_m * tiles_n * p.k_slices;
+  if (!full_grid && units * kG < ctas) ctas = units * kG;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(ctas));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = kG;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_bf16_kernel, tm_a, tm_b, p);
+  if (e != cudaSuccess) {
+    fprintf(stderr, "[kernel_align_b200] gemm launch failed: %s\n", cudaGetErrorString(e));
+    return -11;
+  }
+  return 0;
+}
+
+}  // namespace ka
+
+extern "C" int ka_gemm_bf16(const void* a, long long lda, int a_major, const void* b, long long ldb, int b_major,
+                            void* c, long long ldc, int out_f32, int m, int n, int k, int* status, int num_sms,
+                            unsigned long long timeout_ns, void* stream) {
+  ka::GemmParams p = {};
+  p.m = m;
+  p.n = n;
+  p.k = k;
+  p.a_major = a_major ? 1 : 0;
+  p.b_major = b_major ? 1 : 0;
+  p.epilogue = out_f32 ? ka::kEpiStoreF32 : ka::kEpiStoreBf16;
+  p.c = c;
+  p.ldc = ldc;
+  p.k_slices = 1;
+  p.total_slices = 1;
+  p.world = 1;
+  p.status = status;
+  p.timeout_ns = timeout_ns;
+  return ka::gemm_launch(a, lda, b, ldb, p, num_sms, false, static_cast<cudaStream_t>(stream));
+}

@@ -1,0 +1,94 @@
+"""Batch-invariant bf16 GEMM on tcgen05 (``csrc/sm100/gemm.cu``).
+
+``gemm_bi(a, b)`` computes ``a @ b.T`` for ``a [M, K]`` and ``b [N, K]`` (the layout of a
+``torch.nn.Linear`` weight). ``trans_a`` / ``trans_b`` select the other storage orders so the
+backward GEMMs need no transpose pass:
+
+    y  = gemm_bi(x, w)                                  # [M, K] x [N, K]^T
+    dx = gemm_bi(dy, w, trans_b=True)                   # dy [M, N] times w stored as [N(=K'), K(=N')]
+    dw = gemm_bi(dy, x, trans_a=True, trans_b=True)     # dy^T x, both stored token-major
+
+A row of the result depends only on that row of ``a`` (fixed tiles, fixed K order, no split-K),
+so the output is bitwise identical for any batch size. ``Linear`` is the autograd wrapper.
+"""
+from __future__ import annotations
+
+from ctypes import c_int, c_longlong, c_ulonglong, c_void_p
+
+import torch
+
+from .. import _native
+from .fused_logp import default_timeout_ns
+
+_status: dict[int, torch.Tensor] = {}
+
+
+def status_buffer(device: torch.device) -> torch.Tensor:
+    """Per-device int32[8] block the GEMM kernels report bounded-wait failures into."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _status:
+        _status[idx] = torch.zeros(8, dtype=torch.int32, device=device)
+    return _status[idx]
+
+
+def check_status(device: torch.device) -> None:
+    st = status_buffer(device).cpu().tolist()
+    if st[0] != 0:
+        status_buffer(device).zero_()
+        raise RuntimeError(f"gemm kernel gave up: code {st[0]} at site {st[1]}, block {st[2]}, aux {st[3:6]}")
+
+
+def _fn():
+    lib = _native.cuda()
+    fn = lib.ka_gemm_bf16
+    fn.restype = c_int
+    fn.argtypes = [c_void_p, c_longlong, c_int, c_void_p, c_longlong, c_int, c_void_p, c_longlong, c_int, c_int, c_int,
+                   c_int, c_void_p, c_int, c_ulonglong, c_void_p]
+    return fn
+
+
+def gemm_bi(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bool = False,
+            out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """``op(a) @ op(b).T`` with ``op(a) = a.T if trans_a`` (a stored ``[K, M]``) and
+    ``op(b) = b.T if trans_b`` (b stored ``[K, N]``). 2-D bf16 inputs, row-major."""
+    if a.device.type != "cuda":
+        af = a.float().t() if trans_a else a.float()
+        bf = b.float().t() if trans_b else b.float()
+        return (af @ bf.t()).to(out_dtype)
+    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
+        raise TypeError("gemm_bi takes bf16 operands")
+    a = a if a.stride(-1) == 1 else a.contiguous()
+    b = b if b.stride(-1) == 1 else b.contiguous()
+    k, m = (a.shape[0], a.shape[1]) if trans_a else (a.shape[1], a.shape[0])
+    kb, n = (b.shape[0], b.shape[1]) if trans_b else (b.shape[1], b.shape[0])
+    if k != kb:
+        raise ValueError(f"inner dimensions differ: {k} vs {kb}")
+    out = torch.empty(m, n, dtype=out_dtype, device=a.device)
+    props = torch.cuda.get_device_properties(a.device)
+    rc = _fn()(a.data_ptr(), a.stride(0), int(trans_a), b.data_ptr(), b.stride(0), int(trans_b), out.data_ptr(),
+               out.stride(0), int(out_dtype == torch.float32), m, n, k, status_buffer(a.device).data_ptr(),
+               props.multi_processor_count, default_timeout_ns(), torch.cuda.current_stream(a.device).cuda_stream)
+    if rc != 0:
+        raise RuntimeError(f"ka_gemm_bf16 rejected its arguments (code {rc})")
+    return out
+
+
+class _LinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w):
+        ctx.save_for_backward(x, w)
+        return gemm_bi(x.reshape(-1, x.shape[-1]), w).reshape(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1]).contiguous()
+        x2 = x.reshape(-1, x.shape[-1])
+        dx = gemm_bi(dy2, w, trans_b=True).reshape(x.shape) if ctx.needs_input_grad[0] else None
+        dw = gemm_bi(dy2, x2, trans_a=True, trans_b=True) if ctx.needs_input_grad[1] else None
+        return dx, dw
+
+
+def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``x @ w.T`` with autograd through the same kernel."""
+    return _LinearFn.apply(x, w)

@@ -64,17 +64,19 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
   }
 }
 
-// Wait until a 32-bit flag in global memory (possibly written by another GPU) equals
-// `expected`, reading it with acquire semantics at system scope.
+// Wait until a 32-bit epoch flag in global memory (possibly written by another GPU) has
+// reached `expected`, reading it with acquire semantics at system scope. Epochs only grow, and
+// a writer may already be one call ahead, so "reached" means seen - expected >= 0 in wrapping
+// arithmetic.
 __device__ __forceinline__ bool flag_wait_bounded(const uint32_t* flag, uint32_t expected,
                                                   const WaitCtx& ctx, int where, int aux0) {
   uint32_t seen = ld_acquire_sys_u32(flag);
-  if (seen == expected) return true;
+  if (static_cast<int32_t>(seen - expected) >= 0) return true;
   const uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
   for (;;) {
     seen = ld_acquire_sys_u32(flag);
-    if (seen == expected) return true;
+    if (static_cast<int32_t>(seen - expected) >= 0) return true;
     if ((++spins & 15u) == 0u) {
       if (*ctx.abort_flag) return false;
       if (globaltimer_ns() - t0 > ctx.timeout_ns) {

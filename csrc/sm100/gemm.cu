@@ -372,6 +372,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       const int rows_valid = min(p.rows_per_rank, p.m - p.rank * p.rows_per_rank);
       for (int it = blockIdx.x; it < items; it += gridDim.x) {
         const int rblk = it / tiles_n, nb = it - rblk * tiles_n;
+        if (rblk * kBM >= rows_valid) continue;  // block past the end of the matrix: nobody writes it
         if (tid < p.total_slices)
           flag_wait_bounded(p.flags[p.rank] + (static_cast<size_t>(tid) * rblks + rblk) * tiles_n + nb, p.epoch, wctx,
                             kWReduceFlag, it);

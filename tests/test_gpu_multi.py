@@ -35,3 +35,12 @@ def test_vocab_parallel_logp_bitwise_equals_single_gpu(world):
     res = _run_worker("vp_logp_worker.py", world)
     assert res["all_ranks_ok"], res
     assert res["small_err"] < 2e-3 and res["llama_err"] < 2e-3
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_tp_gemm_fused_collectives_bitwise_equal_single_gpu(world):
+    if world not in _world_sizes():
+        pytest.skip(f"needs {world} GPUs")
+    res = _run_worker("tp_gemm_worker.py", world)
+    assert res["all_ranks_ok"], res
+    assert res["rs_small_err"] < 0.02 and res["rs_llama_err"] < 0.02

@@ -1,0 +1,121 @@
+"""CPU multi-rank tier: gloo ranks on this host exercise the host-side logic of the
+deterministic collectives and of failure detection (no GPU involved)."""
+import os
+import sys
+import time
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _init(rank, world, port, timeout_s=30):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    import datetime
+
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=timeout_s))
+
+
+def _allreduce_worker(rank, world, port, out_dir):
+    _init(rank, world, port)
+    from kernel_align_b200.parallel.collectives import all_reduce_det, tree_sum
+
+    g = torch.Generator().manual_seed(100 + rank)
+    x = torch.randn(1000, generator=g) * (10.0 ** (rank - 1))
+    mine = x.clone()
+    all_reduce_det(mine)
+    parts = [torch.randn(1000, generator=torch.Generator().manual_seed(100 + r)) * (10.0 ** (r - 1))
+             for r in range(world)]
+    want = tree_sum(parts)
+    torch.save({"ok": bool(torch.equal(mine, want)), "val": mine}, os.path.join(out_dir, f"r{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_all_reduce_det_gloo_fixed_tree_order(tmp_path, world):
+    port = 29700 + world
+    mp.spawn(_allreduce_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    outs = [torch.load(tmp_path / f"r{r}.pt") for r in range(world)]
+    assert all(o["ok"] for o in outs)
+    for o in outs[1:]:
+        assert torch.equal(o["val"], outs[0]["val"])  # every rank holds the same bits
+
+
+def _failure_worker(rank, world, port, out_dir):
+    _init(rank, world, port, timeout_s=20)
+    from kernel_align_b200.parallel.collectives import all_reduce_det
+    from kernel_align_b200.parallel.health import PeerLost, PeerMonitor
+
+    mon = PeerMonitor(timeout_s=2.0)
+    x = torch.ones(16)
+    mon.check(0)
+    all_reduce_det(x)  # step 0: everyone takes part
+    leaver = world - 1
+    if rank == leaver:
+        # leave between steps, with nothing in flight; rank `leaver - 1` simply stops
+        # answering instead (no announcement): both must be noticed
+        mon.announce_leave()
+        open(os.path.join(out_dir, f"r{rank}.left"), "w").close()
+        time.sleep(6)  # keep the process (and its sockets) alive while the others look
+        return
+    t0 = time.time()
+    try:
+        mon.check(1)
+        outcome = "completed"
+    except PeerLost as e:
+        outcome = f"PeerLost:{e.rank}"
+    with open(os.path.join(out_dir, f"r{rank}.txt"), "w") as f:
+        f.write(f"{outcome} {time.time() - t0:.1f}")
+    time.sleep(1)
+
+
+def test_missing_rank_is_detected_on_the_host(tmp_path):
+    world = 4
+    mp.spawn(_failure_worker, args=(world, 29720, str(tmp_path)), nprocs=world, join=True)
+    assert (tmp_path / f"r{world - 1}.left").exists()
+    for r in range(world - 1):
+        outcome, secs = (tmp_path / f"r{r}.txt").read_text().split()
+        assert outcome == f"PeerLost:{world - 1}", outcome
+        assert float(secs) < 5
+
+
+def _silent_worker(rank, world, port, out_dir):
+    _init(rank, world, port, timeout_s=20)
+    from kernel_align_b200.parallel.health import PeerLost, PeerMonitor
+
+    mon = PeerMonitor(timeout_s=1.0)
+    mon.check(0)
+    if rank == 1:
+        time.sleep(4)  # hangs on the host: never reaches step 1 in time, says nothing
+        return
+    t0 = time.time()
+    try:
+        mon.check(1)
+        outcome = "completed"
+    except PeerLost as e:
+        outcome = f"PeerLost:{e.rank}"
+    with open(os.path.join(out_dir, f"r{rank}.txt"), "w") as f:
+        f.write(f"{outcome} {time.time() - t0:.1f}")
+    time.sleep(4)
+
+
+def test_silent_rank_times_out_on_the_host(tmp_path):
+    mp.spawn(_silent_worker, args=(2, 29730, str(tmp_path)), nprocs=2, join=True)
+    outcome, secs = (tmp_path / "r0.txt").read_text().split()
+    assert outcome == "PeerLost:1" and 0.5 < float(secs) < 4
+
+
+def test_tree_sum_order():
+    from kernel_align_b200.parallel.collectives import tree_sum
+
+    parts = [torch.tensor([1e8]), torch.tensor([1.0]), torch.tensor([-1e8]), torch.tensor([1.0])]
+    # ((1e8 + 1) + (-1e8 + 1)) in fp32: 1e8 + 1 rounds to 1e8
+    assert tree_sum(parts).item() == ((torch.tensor(1e8) + 1.0) + (torch.tensor(-1e8) + 1.0)).item()
+    with pytest.raises(ValueError):
+        tree_sum(parts[:3])

@@ -44,3 +44,11 @@ def test_tp_gemm_fused_collectives_bitwise_equal_single_gpu(world):
     res = _run_worker("tp_gemm_worker.py", world)
     assert res["all_ranks_ok"], res
     assert res["rs_small_err"] < 0.02 and res["rs_llama_err"] < 0.02
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_deterministic_all_reduce_and_grad_buckets(world):
+    if world not in _world_sizes():
+        pytest.skip(f"needs {world} GPUs")
+    res = _run_worker("allreduce_worker.py", world)
+    assert res["all_ranks_ok"], res

@@ -1,0 +1,66 @@
+"""Batch-invariant attention (causal or full, grouped KV heads, head_dim 128 on CUDA).
+
+CUDA: ``csrc/sm100/attention.cu`` (TMA + tcgen05, fixed 128-wide KV tiles in increasing
+order). CPU: ``csrc/cpu/attention_cpu.cpp``. The reference routes the op type "attention" to a
+backend name only (rl_engine/kernels/registry.py:41-55).
+"""
+from __future__ import annotations
+
+import math
+from ctypes import c_float, c_int, c_longlong, c_ulonglong, c_void_p
+from typing import Optional
+
+import torch
+
+from .. import _native
+from .fused_logp import default_timeout_ns
+from .gemm import status_buffer
+
+
+def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool = True,
+              scale: Optional[float] = None, return_lse: bool = False):
+    """q ``[B, L, Hq, D]``, k / v ``[B, L, Hkv, D]`` -> ``[B, L, Hq, D]``.
+
+    Inputs may be strided views of a fused projection as long as heads are contiguous
+    (``stride(-1) == 1``, ``stride(-2) == D``) and the batch stride is ``L`` tokens.
+    """
+    b, l, hq, d = q.shape
+    hkv = k.shape[2]
+    sc = float(scale) if scale is not None else 1.0 / math.sqrt(d)
+    if q.device.type != "cuda":
+        lib = _native.cpu()
+        qf, kf, vf = (t.float().contiguous() for t in (q, k, v))
+        out = torch.empty_like(qf)
+        lse = torch.empty(b, hq, l, dtype=torch.float32) if return_lse else None
+        fn = lib.ka_cpu_attention
+        fn.restype = c_int
+        fn.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
+                       c_int]
+        rc = fn(qf.data_ptr(), kf.data_ptr(), vf.data_ptr(), out.data_ptr(), lse.data_ptr() if return_lse else None,
+                b, l, hq, hkv, d, sc, int(causal))
+        if rc != 0:
+            raise RuntimeError(f"ka_cpu_attention failed ({rc})")
+        out = out.to(q.dtype)
+        return (out, lse) if return_lse else out
+    if d != 128 or q.dtype != torch.bfloat16:
+        raise ValueError("the sm_100a attention kernel takes bf16 with head_dim 128")
+
+    def tok_view(t, heads):
+        ok = t.stride(3) == 1 and t.stride(2) == d and t.stride(0) == l * t.stride(1) and t.stride(1) % 8 == 0 \
+            and t.data_ptr() % 16 == 0
+        return t if ok else t.contiguous()
+
+    q, k, v = tok_view(q, hq), tok_view(k, hkv), tok_view(v, hkv)
+    out = torch.empty(b, l, hq, d, dtype=torch.bfloat16, device=q.device)
+    lse = torch.empty(b, hq, l, dtype=torch.float32, device=q.device) if return_lse else None
+    lib = _native.cuda()
+    fn = lib.ka_attention_fwd
+    fn.restype = c_int
+    fn.argtypes = [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p,
+                   c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_ulonglong, c_void_p]
+    rc = fn(q.data_ptr(), q.stride(1), k.data_ptr(), k.stride(1), v.data_ptr(), v.stride(1), out.data_ptr(),
+            out.stride(1), lse.data_ptr() if lse is not None else None, b, l, hq, hkv, d, sc, int(causal),
+            status_buffer(q.device).data_ptr(), default_timeout_ns(), torch.cuda.current_stream(q.device).cuda_stream)
+    if rc != 0:
+        raise RuntimeError(f"ka_attention_fwd rejected its arguments (code {rc})")
+    return (out, lse) if return_lse else out

@@ -94,12 +94,39 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   return *reinterpret_cast<const uint32_t*>(&h);
 }
 
+struct RowCtx {
+  float neg_lse2;  // -lse * log2(e)
+  float gs;        // upstream gradient * scale
+  long long tgt;   // target column inside this shard (or out of range)
+};
+
 // Store 32 consecutive accumulator columns of one row.
 __device__ __forceinline__ void store_group(const GemmParams& p, const uint32_t (&v)[32], long long row, int col,
-                                            int slice_global) {
+                                            int slice_global, const RowCtx& rc) {
   if (col >= p.n) return;
   const bool full = col + 32 <= p.n;
-  if (p.epilogue == kEpiStoreBf16) {
+  if (p.epilogue == kEpiLogitsGrad) {
+    const float s2 = p.scale * 1.4426950408889634f;
+    __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.c) + row * p.ldc + col;
+    float d[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const float pr = ex2_approx(__fmaf_rn(__uint_as_float(v[j]), s2, rc.neg_lse2));
+      const float one = (col + j == rc.tgt) ? 1.f : 0.f;
+      d[j] = __fmul_rn(rc.gs, __fsub_rn(one, pr));
+    }
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+      if (full || col + j + 8 <= p.n) {
+        uint4 o;
+        o.x = pack_bf16(d[j], d[j + 1]);
+        o.y = pack_bf16(d[j + 2], d[j + 3]);
+        o.z = pack_bf16(d[j + 4], d[j + 5]);
+        o.w = pack_bf16(d[j + 6], d[j + 7]);
+        *reinterpret_cast<uint4*>(dst + j) = o;
+      }
+    }
+  } else if (p.epilogue == kEpiStoreBf16) {
     __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.c) + row * p.ldc + col;
 #pragma unroll
     for (int j = 0; j < 32; j += 8) {
@@ -320,6 +347,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         tc_fence_after_sync();
         const uint32_t trow = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + static_cast<uint32_t>(abuf * kBN);
         const int slice_global = p.slice_base + un.slice;
+        RowCtx rc = {0.f, 0.f, -1};
+        if (p.epilogue == kEpiLogitsGrad && row < p.m) {
+          rc.neg_lse2 = __fmul_rn(-p.row_lse[row], 1.4426950408889634f);
+          rc.gs = __fmul_rn(p.row_g[row], p.scale);
+          rc.tgt = p.row_ids[row] - p.col_offset;
+        }
         uint32_t va[32], vb[32];
         tmem_ld_32x32(trow, va);
         tmem_ld_wait_dep(va);
@@ -327,11 +360,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         for (int g = 0; g < kBN / 32; g += 2) {
           __syncwarp();
           tmem_ld_32x32(trow + (g + 1) * 32, vb);
-          if (row < p.m) store_group(p, va, row, un.n_blk * kBN + g * 32, slice_global);
+          if (row < p.m) store_group(p, va, row, un.n_blk * kBN + g * 32, slice_global, rc);
           __syncwarp();
           tmem_ld_wait_dep(vb);
           if (g + 2 < kBN / 32) tmem_ld_32x32(trow + (g + 2) * 32, va);
-          if (row < p.m) store_group(p, vb, row, un.n_blk * kBN + (g + 1) * 32, slice_global);
+          if (row < p.m) store_group(p, vb, row, un.n_blk * kBN + (g + 1) * 32, slice_global, rc);
           __syncwarp();
           if (g + 2 < kBN / 32) tmem_ld_wait_dep(va);
         }
@@ -525,4 +558,28 @@ extern "C" int ka_gemm_bf16(const void* a, long long lda, int a_major, const voi
   p.status = status;
   p.timeout_ns = timeout_ns;
   return ka::gemm_launch(a, lda, b, ldb, p, num_sms, false, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int ka_lmhead_logits_grad(const void* hidden, const void* weight, const long long* ids, const float* lse,
+                                     const float* g, void* d_logits, long long ldd, int m, int n, int k, float scale,
+                                     int col_offset, int* status, int num_sms, unsigned long long timeout_ns,
+                                     void* stream) {
+  ka::GemmParams p = {};
+  p.m = m;
+  p.n = n;
+  p.k = k;
+  p.epilogue = ka::kEpiLogitsGrad;
+  p.c = d_logits;
+  p.ldc = ldd;
+  p.k_slices = 1;
+  p.total_slices = 1;
+  p.world = 1;
+  p.row_lse = lse;
+  p.row_g = g;
+  p.row_ids = ids;
+  p.scale = scale;
+  p.col_offset = col_offset;
+  p.status = status;
+  p.timeout_ns = timeout_ns;
+  return ka::gemm_launch(hidden, k, weight, k, p, num_sms, false, static_cast<cudaStream_t>(stream));
 }

@@ -22,7 +22,8 @@ namespace ka {
 enum GemmEpilogue : int {
   kEpiStoreBf16 = 0,    // C bf16 [M, N]
   kEpiStoreF32 = 1,     // C fp32 [M, N]
-  kEpiPartialF32 = 2    // fp32 partial per K slice, pushed to the row owner's staging buffer
+  kEpiPartialF32 = 2,   // fp32 partial per K slice, pushed to the row owner's staging buffer
+  kEpiLogitsGrad = 3    // C bf16 = g[row] * scale * (onehot(ids[row]) - exp(scale * acc - lse[row]))
 };
 
 struct GemmParams {
@@ -49,6 +50,12 @@ struct GemmParams {
   const void* a_local;    // this rank's rows [a_rows_per_rank, k] to push to every peer
   void* a_bufs[8];        // per destination rank: its gather buffer
   unsigned* a_flags[8];   // per destination rank: [world][row blocks of 128]
+  // --- kEpiLogitsGrad: gradient of the log-prob w.r.t. the logits, from recomputed logits
+  const float* row_lse;       // [m] log-sum-exp of the scaled logits (natural log)
+  const float* row_g;         // [m] upstream gradient of logp
+  const long long* row_ids;   // [m] global target ids
+  float scale;
+  int col_offset;             // global index of column 0 (vocabulary shard offset)
   int* status;
   unsigned long long timeout_ns;
 };
@@ -65,6 +72,12 @@ extern "C" {
 
 // Plain GEMM: c = op(a) op(b)^T. out_f32 selects fp32 output. All leading dimensions in
 // elements; m, n, k multiples of 8. Returns 0 or a negative code.
+// d_logits[m, n] (bf16) for logp = scale * logits[ids] - logsumexp(scale * logits), with the
+// logits recomputed as hidden[m, k] x weight[n, k]^T inside the kernel.
+int ka_lmhead_logits_grad(const void* hidden, const void* weight, const long long* ids, const float* lse,
+                          const float* g, void* d_logits, long long ldd, int m, int n, int k, float scale,
+                          int col_offset, int* status, int num_sms, unsigned long long timeout_ns, void* stream);
+
 int ka_gemm_bf16(const void* a, long long lda, int a_major, const void* b, long long ldb, int b_major, void* c,
                  long long ldc, int out_f32, int m, int n, int k, int* status, int num_sms,
                  unsigned long long timeout_ns, void* stream);

@@ -106,7 +106,7 @@ class VocabParallel:
     panel_rows: int = DEFAULT_PANEL_ROWS
 
 
-def lmhead_logp(
+def _lmhead_logp_forward(
     hidden: torch.Tensor,
     weight: torch.Tensor,
     ids: torch.Tensor,
@@ -195,3 +195,96 @@ def lmhead_logp(
 def last_status(device: torch.device, vocab: int, panel_rows: int = DEFAULT_PANEL_ROWS) -> torch.Tensor:
     """The status block of the workspace for (device, vocab): int32[8], zero when healthy."""
     return _get_workspace(device, vocab, panel_rows).status
+
+
+_GRAD_PANEL_BYTES = 8 << 30
+
+
+class _LmheadLogpFn(torch.autograd.Function):
+    """Differentiable fused log-prob. Backward recomputes the logits tile by tile inside the
+    GEMM kernel (``kEpiLogitsGrad`` epilogue of ``csrc/sm100/gemm.cu``), writes
+    ``d_logits = g * scale * (onehot - softmax)`` as bf16 for a panel of rows, and feeds it to
+    the two backward GEMMs: ``d_hidden = d_logits @ W`` and ``d_W = d_logits^T @ hidden``."""
+
+    @staticmethod
+    def forward(ctx, hidden, weight, ids, scale, vocab, group, panel_rows, cta_group):
+        logp, lse = _lmhead_logp_forward(hidden, weight, ids, scale=scale, vocab=vocab, group=group,
+                                         return_lse=True, panel_rows=panel_rows, cta_group=cta_group)
+        ctx.save_for_backward(hidden, weight, ids, lse)
+        ctx.scale, ctx.vocab, ctx.group = scale, vocab, group
+        return logp
+
+    @staticmethod
+    def backward(ctx, g):
+        from . import gemm as _gemm
+
+        hidden, weight, ids, lse = ctx.saved_tensors
+        if hidden.device.type != "cuda":
+            raise RuntimeError("backward of the fused log-prob runs on CUDA only; use PyTorch ops on CPU")
+        k = hidden.shape[-1]
+        h2 = hidden.reshape(-1, k).contiguous()
+        m = h2.shape[0]
+        v_global = int(ctx.vocab) if ctx.vocab is not None else int(weight.shape[0])
+        world = 1 if ctx.group is None else ctx.group.world
+        rank = 0 if ctx.group is None else ctx.group.rank
+        lo, hi = vocab_shard_range(v_global, rank, world)
+        v_local = hi - lo
+        ids64 = ids.reshape(-1).to(torch.int64).contiguous()
+        valid = (ids64 >= 0) & (ids64 < v_global)
+        g32 = (g.reshape(-1).float() * valid).contiguous()
+        lse32 = lse.reshape(-1).float().contiguous()
+        w = weight.contiguous()
+        lib = _native.cuda()
+        fn = lib.ka_lmhead_logits_grad
+        fn.restype = ctypes.c_int
+        fn.argtypes = [ctypes.c_void_p] * 6 + [ctypes.c_longlong, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                               ctypes.c_float, ctypes.c_int, ctypes.c_void_p, ctypes.c_int,
+                                               ctypes.c_ulonglong, ctypes.c_void_p]
+        props = torch.cuda.get_device_properties(h2.device)
+        stream = torch.cuda.current_stream(h2.device).cuda_stream
+        rows_per_panel = max(256, min(m, (_GRAD_PANEL_BYTES // max(1, v_local * 2)) // 256 * 256))
+        need_dh, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        d_hidden = torch.empty_like(h2) if need_dh else None
+        d_weight = None
+        multi = rows_per_panel < m
+        for r0 in range(0, m, rows_per_panel):
+            r1 = min(m, r0 + rows_per_panel)
+            d_logits = torch.empty(r1 - r0, v_local, dtype=torch.bfloat16, device=h2.device)
+            rc = fn(h2[r0:r1].data_ptr(), w.data_ptr(), ids64[r0:r1].data_ptr(), lse32[r0:r1].data_ptr(),
+                    g32[r0:r1].data_ptr(), d_logits.data_ptr(), v_local, r1 - r0, v_local, k, float(ctx.scale), lo,
+                    _gemm.status_buffer(h2.device).data_ptr(), props.multi_processor_count, default_timeout_ns(),
+                    stream)
+            if rc != 0:
+                raise RuntimeError(f"ka_lmhead_logits_grad rejected its arguments (code {rc})")
+            if need_dh:
+                d_hidden[r0:r1] = _gemm.gemm_bi(d_logits, w, trans_b=True)
+            if need_dw:
+                part = _gemm.gemm_bi(d_logits, h2[r0:r1], trans_a=True, trans_b=True,
+                                     out_dtype=torch.float32 if multi else torch.bfloat16)
+                d_weight = part if d_weight is None else d_weight.add_(part)
+            del d_logits
+        if need_dh and world > 1:
+            from ..parallel.collectives import all_reduce_det
+
+            all_reduce_det(d_hidden, getattr(ctx.group, "process_group", None))
+        if need_dw and d_weight.dtype != weight.dtype:
+            d_weight = d_weight.to(weight.dtype)
+        return (d_hidden.reshape(hidden.shape) if need_dh else None), d_weight, None, None, None, None, None, None
+
+
+def lmhead_logp(hidden: torch.Tensor, weight: torch.Tensor, ids: torch.Tensor, *, scale: float = 1.0,
+                vocab: Optional[int] = None, group: Optional[VocabParallel] = None, return_lse: bool = False,
+                panel_rows: int = DEFAULT_PANEL_ROWS, cta_group: int = 2, out: Optional[torch.Tensor] = None,
+                check: bool = False):
+    """Per-token log-probabilities of ``ids`` under ``softmax(scale * hidden @ weight.T)``.
+
+    hidden: ``[..., K]`` bf16; weight: ``[V_local, K]`` bf16 (this rank's vocabulary shard,
+    whole canonical slices, see :func:`vocab_shard_range`); ids: ``[...]`` integer, global
+    ids. Ids outside ``[0, vocab)`` give 0. Returns fp32 ``[...]`` (and the log-sum-exp if
+    ``return_lse``). Differentiable with respect to ``hidden`` and ``weight`` on CUDA.
+    """
+    needs_grad = torch.is_grad_enabled() and (hidden.requires_grad or weight.requires_grad)
+    if needs_grad and hidden.device.type == "cuda" and not return_lse and out is None:
+        return _LmheadLogpFn.apply(hidden, weight, ids, float(scale), vocab, group, panel_rows, cta_group)
+    return _lmhead_logp_forward(hidden, weight, ids, scale=scale, vocab=vocab, group=group, return_lse=return_lse,
+                                panel_rows=panel_rows, cta_group=cta_group, out=out, check=check)

@@ -99,3 +99,30 @@ def test_logits_logp_llama_vocab(cuda_device):
     out = logits_logp(logits, ids)
     ref = torch.log_softmax(logits.float(), -1).gather(-1, ids[:, None]).squeeze(-1)
     assert (out - ref).abs().max().item() < 1e-4
+
+
+def test_fused_logp_backward_matches_autograd(cuda_device):
+    from kernel_align_b200.ops import gemm
+
+    m, k, v = 600, 512, 9000
+    h, w, ids = _inputs(cuda_device, m, k, v, seed=11)
+    ids = ids.clone()
+    ids[5] = -100
+    g = torch.randn(m, device=cuda_device, generator=torch.Generator(device=cuda_device).manual_seed(12))
+    hq, wq = h.clone().requires_grad_(), w.clone().requires_grad_()
+    out = fused_logp.lmhead_logp(hq, wq, ids, scale=1 / 0.7)
+    out.backward(g)
+    gemm.check_status(cuda_device)
+    hr, wr = h.float().requires_grad_(), w.float().requires_grad_()
+    lg = (hr @ wr.t()) / 0.7
+    ref = torch.log_softmax(lg, -1).gather(-1, ids.clamp(min=0)[:, None]).squeeze(-1)
+    ref = ref * (ids >= 0)
+    ref.backward(g)
+    assert (out - ref.detach()).abs().max().item() < 2e-3
+    assert (hq.grad.float() - hr.grad).abs().max().item() <= 0.02 * hr.grad.abs().max().item()
+    assert (wq.grad.float() - wr.grad).abs().max().item() <= 0.02 * wr.grad.abs().max().item()
+    assert hq.grad[5].abs().max().item() == 0
+    # repeatable bit for bit
+    h2, w2 = h.clone().requires_grad_(), w.clone().requires_grad_()
+    fused_logp.lmhead_logp(h2, w2, ids, scale=1 / 0.7).backward(g)
+    assert torch.equal(h2.grad, hq.grad) and torch.equal(w2.grad, wq.grad)

@@ -165,6 +165,80 @@ swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* _
   }
 }
 
+// Backward of y = bf16(bf16(x * inv) * w): one CTA per chunk of kRmsChunk rows (fixed, so the
+// order in which rows enter d_w does not depend on the grid), threads own columns.
+//   dx = inv * (dy*w - n * mean(dy*w*n)),  n = x * inv;   dw_partial[chunk] = sum_rows dy * n
+constexpr int kRmsChunk = 128;
+
+__global__ void __launch_bounds__(256)
+rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                   const __nv_bfloat16* __restrict__ dy, __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_part,
+                   int rows, int d, float eps) {
+  __shared__ float s_warp[8];
+  const int chunk = blockIdx.x;
+  const int r0 = chunk * kRmsChunk, r1 = min(rows, r0 + kRmsChunk);
+  const int nvec = d / 8;
+  // each thread owns the vectors threadIdx.x, threadIdx.x + 256, ... (at most 4 for d <= 8192)
+  float dw_acc[4][8];
+#pragma unroll
+  for (int a = 0; a < 4; ++a)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dw_acc[a][j] = 0.f;
+  for (int row = r0; row < r1; ++row) {
+    const Bf16x8* xp = reinterpret_cast<const Bf16x8*>(x + static_cast<size_t>(row) * d);
+    const Bf16x8* gp = reinterpret_cast<const Bf16x8*>(dy + static_cast<size_t>(row) * d);
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < nvec; i += 256) {
+      const Bf16x8 a = xp[i];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float f = __bfloat162float(a.v[j]);
+        ss = __fmaf_rn(f, f, ss);
+      }
+    }
+    const float total = block_sum_fixed(ss, s_warp, 8);
+    const float inv = __fdiv_rn(1.f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, static_cast<float>(d)), eps)));
+    float dot = 0.f;
+    for (int i = threadIdx.x; i < nvec; i += 256) {
+      const Bf16x8 a = xp[i], g = gp[i], ww = reinterpret_cast<const Bf16x8*>(w)[i];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float n = __fmul_rn(__bfloat162float(a.v[j]), inv);
+        dot = __fmaf_rn(__fmul_rn(__bfloat162float(g.v[j]), __bfloat162float(ww.v[j])), n, dot);
+      }
+    }
+    const float mean_dot = __fdiv_rn(block_sum_fixed(dot, s_warp, 8), static_cast<float>(d));
+    int slot = 0;
+    for (int i = threadIdx.x; i < nvec; i += 256, ++slot) {
+      const Bf16x8 a = xp[i], g = gp[i], ww = reinterpret_cast<const Bf16x8*>(w)[i];
+      Bf16x8 o;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float n = __fmul_rn(__bfloat162float(a.v[j]), inv);
+        const float gw = __fmul_rn(__bfloat162float(g.v[j]), __bfloat162float(ww.v[j]));
+        o.v[j] = __float2bfloat16_rn(__fmul_rn(inv, __fsub_rn(gw, __fmul_rn(n, mean_dot))));
+        if (slot < 4) dw_acc[slot][j] = __fmaf_rn(__bfloat162float(g.v[j]), n, dw_acc[slot][j]);
+      }
+      reinterpret_cast<Bf16x8*>(dx + static_cast<size_t>(row) * d)[i] = o;
+    }
+  }
+  int slot = 0;
+  for (int i = threadIdx.x; i < nvec && slot < 4; i += 256, ++slot) {
+    float* dst = dw_part + static_cast<size_t>(chunk) * d + i * 8;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dst[j] = dw_acc[slot][j];
+  }
+}
+
+// d_w[c] = sum over chunks (in index order) of dw_part[chunk][c]
+__global__ void rmsnorm_dw_kernel(const float* __restrict__ dw_part, __nv_bfloat16* __restrict__ dw, int chunks, int d) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= d) return;
+  float acc = 0.f;
+  for (int k = 0; k < chunks; ++k) acc = __fadd_rn(acc, dw_part[static_cast<size_t>(k) * d + c]);
+  dw[c] = __float2bfloat16_rn(acc);
+}
+
 int grid_for(long long work_items, int threads, int num_sms) {
   long long g = (work_items + threads - 1) / threads;
   const long long cap = static_cast<long long>(num_sms) * 8;
@@ -223,6 +297,22 @@ int ka_swiglu_bwd(const void* gate, const void* up, long long in_stride, const v
       static_cast<const __nv_bfloat16*>(gate), static_cast<const __nv_bfloat16*>(up), in_stride,
       static_cast<const __nv_bfloat16*>(d_out), static_cast<__nv_bfloat16*>(d_gate), static_cast<__nv_bfloat16*>(d_up),
       dgrad_stride, rows, f);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// x, dy: [rows, d] bf16; dx: [rows, d] bf16; dw: [d] bf16; dw_part: scratch of
+// ceil(rows / 128) * d floats. d % 8 == 0 and d <= 8192.
+int ka_rmsnorm_bwd(const void* x, const void* w, const void* dy, void* dx, void* dw, float* dw_part, int rows, int d,
+                   float eps, void* stream) {
+  using namespace ka;
+  if (rows <= 0) return 0;
+  if (d % 8 != 0 || d > 8192) return -1;
+  const int chunks = (rows + kRmsChunk - 1) / kRmsChunk;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  rmsnorm_bwd_kernel<<<chunks, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
+                                             static_cast<const __nv_bfloat16*>(dy), static_cast<__nv_bfloat16*>(dx),
+                                             dw_part, rows, d, eps);
+  rmsnorm_dw_kernel<<<(d + 255) / 256, 256, 0, st>>>(dw_part, static_cast<__nv_bfloat16*>(dw), chunks, d);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

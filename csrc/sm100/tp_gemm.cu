@@ -43,12 +43,14 @@ size_t ka_gemm_rs_exchange_bytes(int m, int n, int world) {
 
 int ka_gemm_rs_rows_per_rank(int m, int world) { return rows_per_rank_of(m, world); }
 
-// a: [m, k_local] bf16 (this rank's K shard = 8/world canonical slices), b: [n, k_local] bf16,
+// a: [m, k_local] bf16 (this rank's K shard = 8/world canonical slices), b: [n, k_local] bf16
+// (b_major = 0) or [k_local, n] (b_major = 1),
 // out: [rows_per_rank, n] bf16 (this rank's rows of the reduced result), residual: same shape
 // or null. exchange[r]: rank r's symmetric buffer as mapped here. Must be zero-initialised
 // once; `epoch` must grow by one per call on a given buffer.
-int ka_gemm_reduce_scatter(const void* a, long long lda, const void* b, long long ldb, void* out, const void* residual,
-                           void* const* exchange, int m, int n, int k_local, int world, int rank, unsigned epoch,
+int ka_gemm_reduce_scatter(const void* a, long long lda, const void* b, long long ldb, int b_major, void* out,
+                           const void* residual, void* const* exchange, int m, int n, int k_local, int world, int rank,
+                           unsigned epoch,
                            int* status, int num_sms, unsigned long long timeout_ns, void* stream) {
   if (!(world == 1 || world == 2 || world == 4 || world == 8) || rank < 0 || rank >= world) return -50;
   if (n % 8 != 0) return -51;
@@ -57,7 +59,7 @@ int ka_gemm_reduce_scatter(const void* a, long long lda, const void* b, long lon
   p.n = n;
   p.k = k_local;
   p.a_major = 0;
-  p.b_major = 0;
+  p.b_major = b_major ? 1 : 0;
   p.epilogue = ka::kEpiPartialF32;
   p.k_slices = kSlices / world;
   p.slice_base = rank * p.k_slices;
@@ -91,9 +93,10 @@ size_t ka_ag_gemm_exchange_bytes(int rows_per_rank, int k, int world) {
   return 2 * buf + 2 * flags;
 }
 
-// a_local: [rows_per_rank, k] bf16 (rows_per_rank multiple of 128), b: [n_local, k] bf16,
+// a_local: [rows_per_rank, k] bf16 (rows_per_rank multiple of 128), b: [n_local, k] bf16
+// (b_major = 0) or [k, n_local] (b_major = 1),
 // c: [world * rows_per_rank, n_local] bf16 = all_gather(a_local) @ b^T.
-int ka_all_gather_gemm(const void* a_local, const void* b, long long ldb, void* c, long long ldc,
+int ka_all_gather_gemm(const void* a_local, const void* b, long long ldb, int b_major, void* c, long long ldc,
                        void* const* exchange, int rows_per_rank, int n_local, int k, int world, int rank,
                        unsigned epoch, int* status, int num_sms, unsigned long long timeout_ns, void* stream) {
   if (world < 1 || world > 8 || rank < 0 || rank >= world) return -50;
@@ -103,7 +106,7 @@ int ka_all_gather_gemm(const void* a_local, const void* b, long long ldb, void* 
   p.n = n_local;
   p.k = k;
   p.a_major = 0;
-  p.b_major = 0;
+  p.b_major = b_major ? 1 : 0;
   p.epilogue = ka::kEpiStoreBf16;
   p.c = c;
   p.ldc = ldc;

@@ -64,3 +64,60 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool
     if rc != 0:
         raise RuntimeError(f"ka_attention_fwd rejected its arguments (code {rc})")
     return (out, lse) if return_lse else out
+
+
+def _attention_backward_math(q, k, v, out, d_out, lse, causal, scale):
+    """Gradient of attention from saved (q, k, v, out, lse), one (batch, kv head) block at a time
+    in fp32. Deterministic (plain matmuls, fixed order); a fused tcgen05 backward kernel is
+    the planned replacement for this interim path."""
+    b, l, hq, d = q.shape
+    hkv = k.shape[2]
+    g = hq // hkv
+    dq = torch.empty_like(q)
+    dk = torch.empty_like(k)
+    dv = torch.empty_like(v)
+    mask = torch.ones(l, l, device=q.device, dtype=torch.bool).triu(1) if causal else None
+    for bi in range(b):
+        qf = q[bi].float().permute(1, 0, 2)                       # [hq, l, d]
+        kf = k[bi].float().permute(1, 0, 2)                       # [hkv, l, d]
+        vf = v[bi].float().permute(1, 0, 2)
+        of = out[bi].float().permute(1, 0, 2)
+        dof = d_out[bi].float().permute(1, 0, 2)
+        kx = kf.repeat_interleave(g, 0)
+        vx = vf.repeat_interleave(g, 0)
+        s = torch.matmul(qf, kx.transpose(1, 2)) * scale           # [hq, l, l]
+        p = torch.exp(s - lse[bi][:, :, None])
+        if mask is not None:
+            p = p.masked_fill(mask, 0.0)
+        delta = (dof * of).sum(-1, keepdim=True)
+        dp = torch.matmul(dof, vx.transpose(1, 2))
+        ds = p * (dp - delta) * scale
+        dq[bi] = torch.matmul(ds, kx).permute(1, 0, 2).to(q.dtype)
+        dkx = torch.matmul(ds.transpose(1, 2), qf)                 # [hq, l, d]
+        dvx = torch.matmul(p.transpose(1, 2), dof)
+        dk[bi] = dkx.view(hkv, g, l, d).sum(1).permute(1, 0, 2).to(k.dtype)
+        dv[bi] = dvx.view(hkv, g, l, d).sum(1).permute(1, 0, 2).to(v.dtype)
+    return dq, dk, dv
+
+
+class _AttentionFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, causal, scale):
+        out, lse = attention(q, k, v, causal=causal, scale=scale, return_lse=True)
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.causal, ctx.scale = causal, scale
+        return out
+
+    @staticmethod
+    def backward(ctx, d_out):
+        q, k, v, out, lse = ctx.saved_tensors
+        dq, dk, dv = _attention_backward_math(q, k, v, out, d_out, lse, ctx.causal, ctx.scale)
+        return dq, dk, dv, None, None
+
+
+def attention_fn(q, k, v, *, causal: bool = True, scale: Optional[float] = None):
+    """Differentiable attention: forward on the tcgen05 kernel."""
+    sc = float(scale) if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    if not torch.is_grad_enabled() or not (q.requires_grad or k.requires_grad or v.requires_grad):
+        return attention(q, k, v, causal=causal, scale=sc)
+    return _AttentionFn.apply(q, k, v, causal, sc)

@@ -130,3 +130,87 @@ def swiglu(gate_up: torch.Tensor, up: Optional[torch.Tensor] = None) -> torch.Te
     _check(fn(gate_v.data_ptr(), up_v.data_ptr(), stride, out.data_ptr(), rows, f, _sms(out), _stream(out)),
            "ka_swiglu")
     return out.reshape(*lead, f)
+
+
+# --------------------------------------------------------------------------------------------
+# Differentiable wrappers (CUDA): forward and backward both run the hand-written kernels.
+# --------------------------------------------------------------------------------------------
+class _RMSNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, eps):
+        ctx.save_for_backward(x, weight)
+        ctx.eps = eps
+        return rmsnorm(x, weight, eps)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight = ctx.saved_tensors
+        d = x.shape[-1]
+        x2 = x.reshape(-1, d).contiguous()
+        dy2 = dy.reshape(-1, d).contiguous()
+        rows = x2.shape[0]
+        dx = torch.empty_like(x2)
+        dw = torch.empty_like(weight)
+        part = torch.empty((rows + 127) // 128, d, dtype=torch.float32, device=x.device)
+        fn = _native.cuda().ka_rmsnorm_bwd
+        fn.restype = c_int
+        fn.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p]
+        _check(fn(x2.data_ptr(), weight.contiguous().data_ptr(), dy2.data_ptr(), dx.data_ptr(), dw.data_ptr(),
+                  part.data_ptr(), rows, d, float(ctx.eps), _stream(x)), "ka_rmsnorm_bwd")
+        return dx.reshape(x.shape), dw, None
+
+
+def rmsnorm_fn(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
+    """Differentiable RMSNorm (no fused residual; add the residual with ``+`` before it)."""
+    if x.device.type != "cuda" or not (x.requires_grad or weight.requires_grad) or not torch.is_grad_enabled():
+        return rmsnorm(x, weight, eps)
+    return _RMSNormFn.apply(x, weight, eps)
+
+
+class _RopeFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, positions, cos, sin):
+        ctx.save_for_backward(positions, cos, sin)
+        out = x.clone() if not x.is_contiguous() else x.clone()
+        return rope_(out, positions, cos, sin)
+
+    @staticmethod
+    def backward(ctx, dy):
+        positions, cos, sin = ctx.saved_tensors
+        # the transpose of a rotation is the rotation by the opposite angle
+        return rope_(dy.contiguous().clone(), positions, cos, -sin), None, None, None
+
+
+def rope_fn(x: torch.Tensor, positions: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """Out-of-place, differentiable rotary embedding of ``x`` ``[tokens, heads, head_dim]``."""
+    return _RopeFn.apply(x, positions, cos, sin)
+
+
+class _SwigluFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gate_up):
+        ctx.save_for_backward(gate_up)
+        return swiglu(gate_up)
+
+    @staticmethod
+    def backward(ctx, d_out):
+        (gate_up,) = ctx.saved_tensors
+        f = gate_up.shape[-1] // 2
+        gu = gate_up.reshape(-1, 2 * f)
+        d2 = d_out.reshape(-1, f).contiguous()
+        rows = gu.shape[0]
+        grad = torch.empty_like(gu)
+        fn = _native.cuda().ka_swiglu_bwd
+        fn.restype = c_int
+        fn.argtypes = [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int,
+                       c_void_p]
+        _check(fn(gu.data_ptr(), gu.data_ptr() + 2 * f, 2 * f, d2.data_ptr(), grad.data_ptr(),
+                  grad.data_ptr() + 2 * f, 2 * f, rows, f, _sms(gu), _stream(gu)), "ka_swiglu_bwd")
+        return grad.reshape(gate_up.shape)
+
+
+def swiglu_fn(gate_up: torch.Tensor) -> torch.Tensor:
+    """Differentiable SwiGLU on a contiguous ``[..., 2F]`` tensor holding ``[gate | up]``."""
+    if gate_up.device.type != "cuda" or not gate_up.requires_grad or not torch.is_grad_enabled():
+        return swiglu(gate_up)
+    return _SwigluFn.apply(gate_up.contiguous())

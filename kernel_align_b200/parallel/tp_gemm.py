@@ -70,21 +70,25 @@ def _lib():
     lib.ka_ag_gemm_exchange_bytes.restype = c_size_t
     lib.ka_ag_gemm_exchange_bytes.argtypes = [c_int, c_int, c_int]
     lib.ka_gemm_reduce_scatter.restype = c_int
-    lib.ka_gemm_reduce_scatter.argtypes = [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p,
-                                           c_int, c_int, c_int, c_int, c_int, c_uint, c_void_p, c_int, c_ulonglong,
-                                           c_void_p]
+    lib.ka_gemm_reduce_scatter.argtypes = [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p,
+                                           c_void_p, c_int, c_int, c_int, c_int, c_int, c_uint, c_void_p, c_int,
+                                           c_ulonglong, c_void_p]
     lib.ka_all_gather_gemm.restype = c_int
-    lib.ka_all_gather_gemm.argtypes = [c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_int,
-                                       c_int, c_int, c_int, c_uint, c_void_p, c_int, c_ulonglong, c_void_p]
+    lib.ka_all_gather_gemm.argtypes = [c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_longlong, c_void_p, c_int,
+                                       c_int, c_int, c_int, c_int, c_uint, c_void_p, c_int, c_ulonglong, c_void_p]
     return lib
 
 
 def gemm_reduce_scatter(x: torch.Tensor, w_shard: torch.Tensor, ctx: TPContext,
-                        residual: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Rows ``[rank * M/world, (rank + 1) * M/world)`` of ``concat_k(x) @ concat_k(w).T`` (+ residual)."""
+                        residual: Optional[torch.Tensor] = None, trans_b: bool = False,
+                        keep_padding: bool = False) -> torch.Tensor:
+    """Rows ``[rank * M/world, (rank + 1) * M/world)`` of ``concat_k(x) @ concat_k(w).T`` (+ residual).
+
+    ``w_shard`` is ``[N, K_local]``, or ``[K_local, N]`` with ``trans_b``. ``keep_padding`` returns
+    all ``rows_per_rank`` rows (a multiple of 128) instead of cutting at the end of the matrix."""
     lib = _lib()
     m, k_local = x.shape
-    n = w_shard.shape[0]
+    n = w_shard.shape[1] if trans_b else w_shard.shape[0]
     if k_local % (8 // ctx.world * 64) != 0:
         raise ValueError("the K shard must split into whole 64-wide blocks per canonical slice")
     x = x.contiguous()
@@ -101,21 +105,30 @@ def gemm_reduce_scatter(x: torch.Tensor, w_shard: torch.Tensor, ctx: TPContext,
             res = torch.cat([res, res.new_zeros(rpr - res.shape[0], n)])
     ptrs = (c_void_p * ctx.world)(*arena.ptrs)
     props = torch.cuda.get_device_properties(x.device)
-    rc = lib.ka_gemm_reduce_scatter(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(),
+    rc = lib.ka_gemm_reduce_scatter(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), int(trans_b), out.data_ptr(),
                                     res.data_ptr() if res is not None else None, ptrs, m, n, k_local, ctx.world,
                                     ctx.rank, epoch & 0xFFFFFFFF, status_buffer(x.device).data_ptr(),
                                     props.multi_processor_count, default_timeout_ns(),
                                     torch.cuda.current_stream(x.device).cuda_stream)
     if rc != 0:
         raise RuntimeError(f"ka_gemm_reduce_scatter rejected its arguments (code {rc})")
-    return out[:rows_valid]
+    return out if keep_padding else out[:rows_valid]
 
 
-def all_gather_gemm(x_local: torch.Tensor, w_shard: torch.Tensor, ctx: TPContext) -> torch.Tensor:
-    """``all_gather(x_local, dim=0) @ w_shard.T``; ``x_local`` rows must be a multiple of 128."""
+def rows_per_rank(m: int, world: int) -> int:
+    """Rows of a reduce-scattered ``[m, n]`` result that each rank owns (multiple of 128)."""
+    return int(_lib().ka_gemm_rs_rows_per_rank(m, world))
+
+
+def all_gather_gemm(x_local: torch.Tensor, w_shard: torch.Tensor, ctx: TPContext, trans_b: bool = False,
+                    return_gathered: bool = False):
+    """``all_gather(x_local, dim=0) @ w_shard.T``; ``x_local`` rows must be a multiple of 128.
+
+    ``w_shard`` is ``[N_local, K]``, or ``[K, N_local]`` with ``trans_b``. With ``return_gathered``
+    also returns a copy of the gathered activations ``[world * rows, K]``."""
     lib = _lib()
     rows, k = x_local.shape
-    n_local = w_shard.shape[0]
+    n_local = w_shard.shape[1] if trans_b else w_shard.shape[0]
     if rows % 128 != 0:
         raise ValueError("rows per rank must be a multiple of 128")
     x = x_local.contiguous()
@@ -125,10 +138,15 @@ def all_gather_gemm(x_local: torch.Tensor, w_shard: torch.Tensor, ctx: TPContext
     out = torch.empty(ctx.world * rows, n_local, dtype=torch.bfloat16, device=x.device)
     ptrs = (c_void_p * ctx.world)(*arena.ptrs)
     props = torch.cuda.get_device_properties(x.device)
-    rc = lib.ka_all_gather_gemm(x.data_ptr(), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), ptrs, rows,
+    rc = lib.ka_all_gather_gemm(x.data_ptr(), w.data_ptr(), w.stride(0), int(trans_b), out.data_ptr(), out.stride(0), ptrs, rows,
                                 n_local, k, ctx.world, ctx.rank, epoch & 0xFFFFFFFF,
                                 status_buffer(x.device).data_ptr(), props.multi_processor_count,
                                 default_timeout_ns(), torch.cuda.current_stream(x.device).cuda_stream)
     if rc != 0:
         raise RuntimeError(f"ka_all_gather_gemm rejected its arguments (code {rc})")
+    if return_gathered:
+        nb = (ctx.world * rows * k * 2 + 255) // 256 * 256
+        gen = epoch & 1
+        gathered = arena.buf[gen * nb: gen * nb + ctx.world * rows * k * 2].view(torch.bfloat16).view(ctx.world * rows, k)
+        return out, gathered.clone()
     return out

@@ -52,3 +52,11 @@ def test_deterministic_all_reduce_and_grad_buckets(world):
         pytest.skip(f"needs {world} GPUs")
     res = _run_worker("allreduce_worker.py", world)
     assert res["all_ranks_ok"], res
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_tp_decoder_layer_bitwise_equals_single_gpu(world):
+    if world not in _world_sizes():
+        pytest.skip(f"needs {world} GPUs")
+    res = _run_worker("tp_layer_worker.py", world)
+    assert res["all_ranks_ok"], res

@@ -19,7 +19,9 @@ def _run_worker(script, nproc, timeout=600, extra_env=None):
            "--master-addr", "127.0.0.1", "--master-port", str(29500 + nproc), os.path.join(HERE, "workers", script)]
     proc = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
     lines = [l for l in proc.stdout.splitlines() if l.startswith("RESULT ")]
-    assert proc.returncode == 0 and lines, proc.stdout[-3000:] + proc.stderr[-3000:]
+    if proc.returncode != 0 or not lines:
+        err = [l for l in proc.stderr.splitlines() if "Error" in l or "error" in l or "rejected" in l]
+        raise AssertionError("worker failed: " + " | ".join(err[-12:]) + "\n" + proc.stdout[-1500:])
     return json.loads(lines[-1][len("RESULT "):])
 
 

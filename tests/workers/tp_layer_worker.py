@@ -30,7 +30,9 @@ def main():
     dev = torch.device("cuda", local)
     tp, solo = TPContext(), solo_context(dev)
     res = {}
-    cases = {"tiny": (LlamaConfig.tiny(), [(1, 256), (8, 256)]), "llama8b": (LlamaConfig.llama3_8b(), [(1, 512), (8, 512)])}
+    tiny = LlamaConfig(vocab_size=2048, hidden=1024, n_layers=2, n_heads=16, n_kv_heads=8, head_dim=128, ffn=4096,
+                       max_pos=1024)
+    cases = {"tiny": (tiny, [(1, 256), (8, 256)]), "llama8b": (LlamaConfig.llama3_8b(), [(1, 512), (8, 512)])}
     for name, (cfg, shapes) in cases.items():
         layer_tp = DecoderLayer(cfg, tp, seed=5, device=dev)
         layer_1 = DecoderLayer(cfg, solo, seed=5, device=dev)

@@ -1,0 +1,103 @@
+"""GRPO training step on the native operators.
+
+One step = rollout (``generate``: G completions per prompt with the fused sampler, their
+log-probabilities recorded) -> rewards -> group-normalised advantages -> policy forward with
+autograd through the native kernels -> fused LM-head log-prob -> clipped-ratio loss ->
+backward -> deterministic gradient all-reduce over the data-parallel ranks (overlapped with
+backward, :class:`GradReducer`) -> fused AdamW. Every kernel on that path reduces in a fixed
+order, so the loss of a step is bitwise reproducible run to run.
+
+The reference has no trainer; its README lists GRPO as the target workload.
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..kernels.sampling import SamplerBackend
+from ..ops.decode import FusedAdamW
+from ..ops.fused_logp import lmhead_logp
+from ..ops.grpo_loss import group_advantages, grpo_loss
+from ..utils.logger import logger
+from .generation import generate
+
+
+class GRPOTrainer:
+    def __init__(self, model, reward_fn: Callable[[torch.Tensor, torch.Tensor], torch.Tensor], *,
+                 group_size: int = 8, max_new_tokens: int = 16, temperature: float = 1.0, top_k: Optional[int] = None,
+                 top_p: Optional[float] = None, eps_clip: float = 0.2, beta: float = 0.0, lr: float = 1e-6,
+                 weight_decay: float = 0.0, seed: int = 0, data_parallel: bool = False,
+                 bucket_bytes: int = 64 << 20):
+        self.model = model
+        self.reward_fn = reward_fn
+        self.group_size, self.max_new_tokens = group_size, max_new_tokens
+        self.temperature, self.top_k, self.top_p = temperature, top_k, top_p
+        self.eps_clip, self.beta = eps_clip, beta
+        self.sampler = SamplerBackend(seed=seed)
+        self.step_index = 0
+        self.dp = data_parallel and dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1
+        self.dp_rank = dist.get_rank() if self.dp else 0
+        self.reducer = None
+        if self.dp:
+            from ..parallel.collectives import GradReducer
+
+            self.reducer = GradReducer(model.parameters(), bucket_bytes=bucket_bytes, average=True)
+        self.optimizer = FusedAdamW(model.parameters(), lr=lr, weight_decay=weight_decay)
+
+    # ------------------------------------------------------------------ phases
+    def rollout(self, prompts: torch.Tensor) -> dict:
+        """``prompts [P, Lp]`` of this rank -> sequences, sampled-token log-probs, rewards, advantages."""
+        p = prompts.shape[0]
+        out = generate(self.model, prompts, sampler=self.sampler, max_new_tokens=self.max_new_tokens,
+                       temperature=self.temperature, top_k=self.top_k, top_p=self.top_p, group_size=self.group_size,
+                       row_id_offset=self.dp_rank * p * self.group_size)
+        rewards = self.reward_fn(prompts.repeat_interleave(self.group_size, 0), out["new_tokens"]).float()
+        out["rewards"] = rewards
+        out["advantages"] = group_advantages(rewards, self.group_size)
+        return out
+
+    def policy_logp(self, sequences: torch.Tensor, prompt_len: int) -> torch.Tensor:
+        """Log-probability of every generated token under the current policy, with autograd."""
+        inputs, targets = sequences[:, :-1], sequences[:, 1:]
+        hidden = self.model.hidden_states(inputs)
+        tokens = inputs.numel()
+        logp = lmhead_logp(hidden[:tokens], self.model.lm_head, targets.reshape(-1),
+                           scale=1.0 / self.temperature if self.temperature > 0 else 1.0)
+        return logp.view(inputs.shape)[:, prompt_len - 1:]
+
+    def train_step(self, prompts: torch.Tensor) -> dict:
+        prompt_len = prompts.shape[1]
+        roll = self.rollout(prompts)
+        if self.reducer is not None:
+            self.reducer.zero_grad()
+        else:
+            self.optimizer.zero_grad(set_to_none=True)
+        logp_new = self.policy_logp(roll["sequences"], prompt_len)
+        loss, stats = grpo_loss(logp_new, roll["logp"], roll["advantages"], eps_low=self.eps_clip, beta=self.beta,
+                                logp_ref=roll["logp"] if self.beta > 0 else None, return_stats=True)
+        loss.backward()
+        if self.reducer is not None:
+            self.reducer.finish()
+        self.optimizer.step()
+        self.step_index += 1
+        tokens = roll["new_tokens"].numel()
+        return {"loss": loss.detach(), "clip_fraction": stats[1], "tokens": tokens,
+                "reward_mean": roll["rewards"].mean(), "step": self.step_index}
+
+    # ------------------------------------------------------------------ checkpoint / resume
+    def save(self, path: str) -> str:
+        from ..utils.checkpoint import save_checkpoint
+
+        world = dist.get_world_size() if self.dp else 1
+        return save_checkpoint(path, self.model, self.optimizer, self.sampler, self.step_index, rank=self.dp_rank,
+                               world=world)
+
+    def load(self, path: str) -> None:
+        from ..utils.checkpoint import load_checkpoint
+
+        world = dist.get_world_size() if self.dp else 1
+        info = load_checkpoint(path, self.model, self.optimizer, self.sampler, rank=self.dp_rank, world=world)
+        self.step_index = info["step"]
+        logger.info_on_rank(f"resumed from {path} at step {self.step_index}")

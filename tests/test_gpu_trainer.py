@@ -1,0 +1,84 @@
+"""GPU tier: generation, the GRPO step and checkpoint / resume on one GPU (tiny model)."""
+import pytest
+import torch
+
+from kernel_align_b200.executors.generation import generate
+from kernel_align_b200.executors.rollout import RolloutExecutor
+from kernel_align_b200.executors.trainer import GRPOTrainer
+from kernel_align_b200.kernels.sampling import SamplerBackend
+from kernel_align_b200.models.llama import LlamaConfig, LlamaModel
+from kernel_align_b200.ops import gemm
+from kernel_align_b200.ops.decode import attention_decode
+
+pytestmark = pytest.mark.gpu
+
+
+def _model(dev, seed=1):
+    return LlamaModel(LlamaConfig.tiny(n_layers=2), seed=seed, device=dev)
+
+
+def test_decode_attention_matches_math(cuda_device):
+    g = torch.Generator(device=cuda_device).manual_seed(0)
+    q = torch.randn(3, 8, 128, device=cuda_device, generator=g).to(torch.bfloat16)
+    ck = torch.randn(3, 200, 2, 128, device=cuda_device, generator=g).to(torch.bfloat16)
+    cv = torch.randn(3, 200, 2, 128, device=cuda_device, generator=g).to(torch.bfloat16)
+    lens = torch.tensor([1, 77, 200], dtype=torch.int32, device=cuda_device)
+    out = attention_decode(q, ck, cv, lens)
+    ref = attention_decode(q.cpu(), ck.cpu(), cv.cpu(), lens.cpu())
+    assert (out.cpu().float() - ref.float()).abs().max().item() < 0.03
+    assert torch.equal(attention_decode(q[1:2], ck[1:2], cv[1:2], lens[1:2]), out[1:2])
+
+
+def test_generation_is_seeded_batch_invariant_and_consistent_with_prefill(cuda_device):
+    model = _model(cuda_device)
+    prompts = torch.randint(0, model.cfg.vocab_size, (3, 16), device=cuda_device,
+                            generator=torch.Generator(device=cuda_device).manual_seed(3))
+    out = generate(model, prompts, sampler=SamplerBackend(seed=5), max_new_tokens=8, temperature=0.8, top_k=50,
+                   top_p=0.95, group_size=2)
+    again = generate(model, prompts, sampler=SamplerBackend(seed=5), max_new_tokens=8, temperature=0.8, top_k=50,
+                     top_p=0.95, group_size=2)
+    gemm.check_status(cuda_device)
+    assert out["sequences"].shape == (6, 24)
+    assert torch.equal(out["sequences"], again["sequences"]) and torch.equal(out["logp"], again["logp"])
+    other = generate(model, prompts, sampler=SamplerBackend(seed=6), max_new_tokens=8, temperature=0.8, top_k=50,
+                     top_p=0.95, group_size=2)
+    assert not torch.equal(out["sequences"], other["sequences"])
+    # the log-prob recorded during decoding agrees with a fresh full forward over the sequence
+    from kernel_align_b200.ops.fused_logp import lmhead_logp
+
+    seq = out["sequences"]
+    with torch.no_grad():
+        hidden = model.hidden_states(seq[:, :-1])
+        lp = lmhead_logp(hidden[: seq[:, :-1].numel()], model.lm_head, seq[:, 1:].reshape(-1), scale=1 / 0.8)
+    lp = lp.view(6, -1)[:, 15:]
+    assert (lp - out["logp"]).abs().max().item() < 0.08
+    # executor entry point with a model attached
+    res = RolloutExecutor({"max_new_tokens": 4, "top_k": 20}, model=model, sampler=SamplerBackend(seed=1)) \
+        .execute_rollout(prompts)
+    assert res["status"] == "success" and res["sequences"].shape == (3, 20)
+
+
+def _reward(prompts, new_tokens):
+    return (new_tokens % 7 == 0).float().mean(1) + 0.1 * (new_tokens[:, 0] % 3).float()
+
+
+def test_grpo_step_is_bitwise_repeatable_and_resumable(cuda_device, tmp_path):
+    prompts = torch.randint(0, 2048, (4, 16), device=cuda_device,
+                            generator=torch.Generator(device=cuda_device).manual_seed(9))
+
+    def fresh():
+        return GRPOTrainer(_model(cuda_device, seed=2), _reward, group_size=4, max_new_tokens=8, temperature=1.0,
+                           top_k=50, lr=1e-4, seed=3)
+
+    a, b = fresh(), fresh()
+    la = [a.train_step(prompts)["loss"].item() for _ in range(3)]
+    lb0 = b.train_step(prompts)["loss"].item()
+    ckpt = b.save(str(tmp_path / "ckpt.pt"))
+    c = fresh()
+    c.load(ckpt)
+    lc = [c.train_step(prompts)["loss"].item() for _ in range(2)]
+    gemm.check_status(cuda_device)
+    assert all(torch.isfinite(torch.tensor(la)))
+    assert lb0 == la[0]                       # run-to-run bitwise equal loss
+    assert lc == la[1:]                       # resume reproduces the uninterrupted run
+    assert la[0] != la[1] or la[1] != la[2]   # the policy actually moved

@@ -1,0 +1,113 @@
+#!/usr/bin/env python
+"""Per-operator device timings on one GPU, each against the library baseline and its roofline.
+
+Rooflines use the measured peaks of this pod when MEASURED_PEAKS.json is present
+(copy bandwidth and cuBLAS bf16 throughput), else the fallback figures 6.65 TB/s / 1.59 PFLOP/s.
+CUDA events, >= 3 warm-ups, median of 10, L2 flushed between iterations for the memory-bound ops.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+import torch.nn.functional as F
+from tabulate import tabulate
+
+from _common import ROOT, time_cuda, write_json
+from kernel_align_b200.ops import gemm
+from kernel_align_b200.ops.attention import attention
+from kernel_align_b200.ops.layer_ops import rmsnorm, swiglu
+from kernel_align_b200.ops.logits_logp import logits_logp
+from kernel_align_b200.ops.sampling import sample
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return p["hbm_gbs"], p["bf16_tflops"], p.get("bf16_tflops_sustained", p["bf16_tflops"]), "of measured"
+    return 6650.0, 1590.0, 1400.0, "of fallback"
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--json-out", default=None)
+    ap.add_argument("--reference-sampler", action="store_true",
+                    help="also time the reference's SamplerBackend.sample from baseline/_ref (FlashInfer JIT)")
+    args = ap.parse_args()
+    dev = torch.device("cuda")
+    hbm, tf_burst, tf_sus, tag = peaks()
+    g = torch.Generator(device=dev).manual_seed(0)
+    rows, out = [], []
+
+    def rec(name, ms, base_ms, frac, note):
+        rows.append([name, f"{ms * 1e3:.1f} us", f"{base_ms * 1e3:.1f} us" if base_ms else "-",
+                     f"{base_ms / ms:.2f}x" if base_ms else "-", f"{frac:.2f} {tag}", note])
+        out.append({"op": name, "ms": ms, "baseline_ms": base_ms, "roofline_fraction": frac, "note": note})
+
+    # GEMM, Llama-3-8B layer shapes at 8192 tokens
+    for name, (m, n, k) in {"gemm qkv 8192x6144x4096": (8192, 6144, 4096), "gemm gate_up 8192x28672x4096": (8192, 28672, 4096),
+                            "gemm down 8192x4096x14336": (8192, 4096, 14336), "gemm 8192^3": (8192, 8192, 8192)}.items():
+        a = torch.randn(m, k, device=dev, generator=g).to(torch.bfloat16)
+        b = (torch.randn(n, k, device=dev, generator=g) * 0.02).to(torch.bfloat16)
+        t = time_cuda(lambda: gemm.gemm_bi(a, b), flush_l2=False)
+        tb = time_cuda(lambda: a @ b.t(), flush_l2=False)
+        tfl = 2.0 * m * n * k / t / 1e9
+        rec(name, t, tb, tfl / tf_burst, f"{tfl:.0f} TFLOP/s vs cuBLAS {2.0 * m * n * k / tb / 1e9:.0f}")
+        del a, b
+    # attention, B=16 L=512 and B=4 L=4096, 32q/8kv heads
+    for b_, l in ((16, 512), (4, 4096)):
+        q = torch.randn(b_, l, 32, 128, device=dev, generator=g).to(torch.bfloat16)
+        k = torch.randn(b_, l, 8, 128, device=dev, generator=g).to(torch.bfloat16)
+        v = torch.randn(b_, l, 8, 128, device=dev, generator=g).to(torch.bfloat16)
+        t = time_cuda(lambda: attention(q, k, v), flush_l2=False)
+        qs, ks, vs = (x.permute(0, 2, 1, 3) for x in (q, k, v))
+        tb = time_cuda(lambda: F.scaled_dot_product_attention(qs, ks, vs, is_causal=True, enable_gqa=True), flush_l2=False)
+        flops = 4.0 * b_ * 32 * l * l * 128 / 2
+        rec(f"attention fwd B={b_} L={l}", t, tb, flops / t / 1e9 / tf_burst,
+            f"{flops / t / 1e9:.0f} TFLOP/s (causal) vs torch SDPA {flops / tb / 1e9:.0f}")
+    # memory-bound ops
+    x = torch.randn(32768, 4096, device=dev, generator=g).to(torch.bfloat16)
+    w = torch.ones(4096, device=dev, dtype=torch.bfloat16)
+    t = time_cuda(lambda: rmsnorm(x, w, 1e-5, x))
+    tb = time_cuda(lambda: F.rms_norm((x + x).float(), (4096,), w.float(), 1e-5).to(torch.bfloat16))
+    by = x.numel() * 2 * 4
+    rec("rmsnorm+residual 32768x4096", t, tb, by / t / 1e6 / hbm, f"{by / t / 1e6:.0f} GB/s")
+    gu = torch.randn(8192, 2 * 14336, device=dev, generator=g).to(torch.bfloat16)
+    t = time_cuda(lambda: swiglu(gu))
+    tb = time_cuda(lambda: F.silu(gu[:, :14336]) * gu[:, 14336:])
+    by = gu.numel() * 2 * 1.5
+    rec("swiglu 8192x14336", t, tb, by / t / 1e6 / hbm, f"{by / t / 1e6:.0f} GB/s")
+    del x, gu
+    lg = (torch.randn(16384, 128256, device=dev, generator=g) * 2).to(torch.bfloat16)
+    ids = torch.randint(0, 128256, (16384,), device=dev, generator=g)
+    t = time_cuda(lambda: logits_logp(lg, ids), iters=5)
+    tb = time_cuda(lambda: torch.log_softmax(lg, -1).gather(-1, ids[:, None]), iters=5)
+    by = lg.numel() * 2
+    rec("logits_logp 16384x128256", t, tb, by / t / 1e6 / hbm, f"{by / t / 1e6:.0f} GB/s")
+    del lg
+    for gsz in (64, 256):
+        lgs = (torch.randn(gsz, 128256, device=dev, generator=g) * 2).to(torch.bfloat16)
+        t = time_cuda(lambda: sample(lgs, top_k=50, top_p=0.9, temperature=0.7, seed=1, step=0))
+        tb = None
+        if args.reference_sampler:
+            import sys
+            sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
+            try:
+                from rl_engine.kernels.sampling import SamplerBackend as RefSampler
+                ref = RefSampler()
+                tb = time_cuda(lambda: ref.sample(lgs, top_k=50, top_p=0.9, temperature=0.7), warmup=5)
+            except Exception as e:  # noqa: BLE001
+                print("reference sampler unavailable:", type(e).__name__, str(e)[:200])
+        by = lgs.numel() * 2
+        rec(f"sampling G={gsz} V=128256 k=50 p=0.9", t, tb, by / t / 1e6 / hbm, f"{by / t / 1e6:.0f} GB/s of logits")
+    print(tabulate(rows, headers=["op", "ours", "baseline", "speedup", "roofline", "note"], tablefmt="github"))
+    write_json(args.json_out, {"device": torch.cuda.get_device_name(), "peaks": {"hbm_gbs": hbm, "bf16_tflops": tf_burst,
+                                                                                 "bf16_tflops_sustained": tf_sus}, "results": out})
+
+
+if __name__ == "__main__":
+    main()

@@ -61,6 +61,20 @@ def main():
 
         x = torch.randn(args.rows, 2 * 14336, device=dev, generator=g).to(torch.bfloat16)
         fn = lambda: swiglu(x)  # noqa: E731
+    elif args.op == "attention":
+        from kernel_align_b200.ops.attention import attention
+
+        b_, l = 4, args.rows if args.rows <= 8192 else 4096
+        q = torch.randn(b_, l, 32, 128, device=dev, generator=g).to(torch.bfloat16)
+        k = torch.randn(b_, l, 8, 128, device=dev, generator=g).to(torch.bfloat16)
+        v = torch.randn(b_, l, 8, 128, device=dev, generator=g).to(torch.bfloat16)
+        fn = lambda: attention(q, k, v)  # noqa: E731
+    elif args.op == "gemm":
+        from kernel_align_b200.ops.gemm import gemm_bi
+
+        a = torch.randn(8192, args.hidden, device=dev, generator=g).to(torch.bfloat16)
+        b = (torch.randn(28672, args.hidden, device=dev, generator=g) * 0.02).to(torch.bfloat16)
+        fn = lambda: gemm_bi(a, b)  # noqa: E731
     else:
         raise SystemExit(f"--op {args.op}: no profile case defined yet")
     for _ in range(args.launches):

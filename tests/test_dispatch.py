@@ -78,3 +78,23 @@ def test_executor_flow():
     result = RolloutExecutor().execute_rollout()
     assert result["status"] == "success"
     assert result["kernels"] == ["SM100_FUSED_LOGP", "SM100_ATTENTION"]
+
+
+def test_every_registered_operator_resolves_to_code():
+    for backend in OpBackend:
+        fn = kernel_registry.resolve(backend)
+        assert callable(fn), backend
+    for op_type, want in {"fused_logp": "lmhead_logp", "logits_logp": "logits_logp", "sampling": "sample",
+                          "attention": "attention", "rmsnorm": "rmsnorm", "rope": "rope_", "swiglu": "swiglu",
+                          "gemm": "gemm_bi", "gemm_reduce_scatter": "gemm_reduce_scatter",
+                          "all_gather_gemm": "all_gather_gemm", "all_reduce": "all_reduce_det",
+                          "grpo_loss": "grpo_loss"}.items():
+        assert kernel_registry.resolve(kernel_registry.dispatch(op_type)).__name__ == want, op_type
+
+
+def test_packages_are_real_packages():
+    import importlib
+
+    for sub in ("utils", "platforms", "kernels", "executors", "ops", "parallel", "models"):
+        mod = importlib.import_module(f"kernel_align_b200.{sub}")
+        assert mod.__file__ and mod.__file__.endswith("__init__.py")

@@ -39,18 +39,24 @@ template <>
 struct Elem<float> {
   static constexpr int kVec = 4;
   static constexpr int kLowBit = 0;
+  static constexpr bool kPacked = false;
+  static constexpr uint32_t kInf2 = 0;
   __device__ static float to_float(float v) { return v; }
 };
 template <>
 struct Elem<__nv_bfloat16> {
   static constexpr int kVec = 8;
   static constexpr int kLowBit = 16;
+  static constexpr bool kPacked = true;
+  static constexpr uint32_t kInf2 = 0x7F807F80u;  // +inf bit pattern, twice
   __device__ static float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
 };
 template <>
 struct Elem<__half> {
   static constexpr int kVec = 8;
   static constexpr int kLowBit = 13;
+  static constexpr bool kPacked = true;
+  static constexpr uint32_t kInf2 = 0x7C007C00u;
   __device__ static float to_float(__half v) { return __half2float(v); }
 };
 
@@ -62,15 +68,15 @@ __device__ __forceinline__ void for_each_key(const T* __restrict__ row, int v, b
   if (vec_ok) {
     const int nvec = v / kVec;
     const uint4* p = reinterpret_cast<const uint4*>(row);
-    for (int i = tid; i < nvec; i += kThreads) {
+    for (int i = tid; i < nvec; i += blockDim.x) {
       const uint4 raw = p[i];
       const T* e = reinterpret_cast<const T*>(&raw);
 #pragma unroll
       for (int j = 0; j < kVec; ++j) f(float_to_key(Elem<T>::to_float(e[j])), i * kVec + j);
     }
-    for (int i = nvec * kVec + tid; i < v; i += kThreads) f(float_to_key(Elem<T>::to_float(row[i])), i);
+    for (int i = nvec * kVec + tid; i < v; i += blockDim.x) f(float_to_key(Elem<T>::to_float(row[i])), i);
   } else {
-    for (int i = tid; i < v; i += kThreads) f(float_to_key(Elem<T>::to_float(row[i])), i);
+    for (int i = tid; i < v; i += blockDim.x) f(float_to_key(Elem<T>::to_float(row[i])), i);
   }
 }
 
@@ -81,7 +87,7 @@ __device__ __forceinline__ int block_sum_int(int v, int* s_warp) {
   __syncthreads();
   if (lane == 0) s_warp[warp] = v;
   __syncthreads();
-  int t = (lane < kWarps) ? s_warp[lane] : 0;
+  int t = (lane < static_cast<int>(blockDim.x >> 5)) ? s_warp[lane] : 0;
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
   return t;
@@ -100,7 +106,7 @@ __device__ __forceinline__ unsigned long long block_exscan_u64(unsigned long lon
   __syncthreads();
   if (lane == 31) s_warp[warp] = inc;
   __syncthreads();
-  unsigned long long w = (lane < kWarps) ? s_warp[lane] : 0ull;
+  unsigned long long w = (lane < static_cast<int>(blockDim.x >> 5)) ? s_warp[lane] : 0ull;
   unsigned long long winc = w;
 #pragma unroll
   for (int o = 1; o < 32; o <<= 1) {
@@ -123,72 +129,185 @@ struct TopkSmem {
   int count;
 };
 
-// Final step shared by both kernels' oracle definition: survivors sorted by (key desc, id asc)
-// with masses q[i]; apply top-p, draw, return the position picked.
-__device__ __forceinline__ int pick_sorted(const unsigned long long* q, int n, float top_p, uint32_t u24) {
-  unsigned long long z = 0;
-  for (int i = 0; i < n; ++i) z += q[i];
+// Final step of the top-k path, run by one warp: survivors sorted by (key desc, id asc) with
+// masses q[0..n); apply top-p, draw, return the position picked. All sums are integers, so
+// the warp-parallel prefix sums give exactly the result of a serial walk.
+__device__ __forceinline__ int pick_sorted_warp(const unsigned long long* q, int n, float top_p, uint32_t u24) {
+  const int lane = threadIdx.x & 31;
+  // lane owns the contiguous slice [lane * per, lane * per + per)
+  const int per = (n + 31) / 32;
+  const int lo = min(n, lane * per), hi = min(n, lo + per);
+  unsigned long long mine = 0;
+  for (int i = lo; i < hi; ++i) mine += q[i];
+  unsigned long long inc = mine;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const unsigned long long t = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += t;
+  }
+  const unsigned long long z = __shfl_sync(0xffffffffu, inc, 31);
+  const unsigned long long before = inc - mine;  // mass of the elements before this lane's slice
   int keep = n;
   unsigned long long zk = z;
   if (top_p < 1.0f) {
+    // keep = first i > 0 with (mass before i) > limit, else n
     const unsigned long long limit = mass_fraction(static_cast<double>(top_p), z);
-    unsigned long long cum = 0;
-    for (int i = 0; i < n; ++i) {
+    int first = n;
+    unsigned long long cum = before;
+    for (int i = lo; i < hi; ++i) {
       if (i > 0 && cum > limit) {
-        keep = i;
+        first = i;
         break;
       }
       cum += q[i];
     }
-    zk = 0;
-    for (int i = 0; i < keep; ++i) zk += q[i];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) first = min(first, __shfl_xor_sync(0xffffffffu, first, o));
+    keep = first;
+    // zk = mass of the first `keep` elements
+    unsigned long long part = 0;
+    for (int i = lo; i < min(hi, keep); ++i) part += q[i];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+    zk = part;
   }
   const unsigned long long target = mass_scale_u24(u24, zk);
-  unsigned long long acc = 0;
-  for (int i = 0; i < keep; ++i) {
-    acc += q[i];
-    if (acc > target) return i;
+  int pick = keep - 1;
+  {
+    int first = n;
+    unsigned long long acc = before;
+    for (int i = lo; i < min(hi, keep); ++i) {
+      acc += q[i];
+      if (acc > target) {
+        first = i;
+        break;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) first = min(first, __shfl_xor_sync(0xffffffffu, first, o));
+    if (first < keep) pick = first;
   }
-  return keep - 1;
+  return pick;
+}
+
+constexpr int kTopkThreads = 512;
+
+// Two 16-bit floats (bf16 or fp16 bit patterns) -> two order-preserving 16-bit keys; NaN -> 0.
+template <typename T>
+__device__ __forceinline__ uint32_t key16x2(uint32_t w) {
+  const uint32_t nan = __vcmpgtu2(w & 0x7FFF7FFFu, Elem<T>::kInf2);
+  const uint32_t sign = (w >> 15) & 0x00010001u;
+  const uint32_t k = w ^ (sign * 0xFFFFu | 0x80008000u);
+  return k & ~nan;
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kThreads, 1)
+__device__ __forceinline__ T from_bits16(uint32_t h) {
+  const unsigned short us = static_cast<unsigned short>(h);
+  return *reinterpret_cast<const T*>(&us);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kTopkThreads, 2)
 sample_topk_kernel(const T* __restrict__ logits, long long row_stride, int v, const long long* __restrict__ row_ids,
                    float inv_temp, int top_k, float top_p, unsigned long long seed, unsigned long long step,
                    int* __restrict__ out) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   TopkSmem& s = *reinterpret_cast<TopkSmem*>(smem_raw);
   const int tid = threadIdx.x;
+  const int nt = blockDim.x;
   const int row = blockIdx.x;
   const T* rp = logits + static_cast<long long>(row) * row_stride;
   const bool vec_ok = (reinterpret_cast<uintptr_t>(rp) & 15u) == 0;
   const int kk = min(min(top_k, kMaxTopK), v);
+  uint32_t lower = 0;  // 32-bit key: at least kk elements of the row are >= lower
 
-  // ---- pass 1 (HBM): per-thread maximum
-  uint32_t tmax = 0;
-  for_each_key<T>(rp, v, vec_ok, [&](uint32_t key, int) { tmax = max(tmax, key); });
-
-  // The kk-th largest of the 1024 thread maxima is a lower bound L for the kk-th largest
-  // element of the row: at least kk elements are >= L.
-  uint32_t lower = 0;
-  for (int bit = 31; bit >= Elem<T>::kLowBit; --bit) {
-    const uint32_t cand = lower | (1u << bit);
-    if (__syncthreads_count(tmax >= cand) >= kk) lower = cand;
-  }
-
-  // ---- pass 2 (L2): collect every element >= L
   if (tid == 0) s.count = 0;
-  __syncthreads();
-  for_each_key<T>(rp, v, vec_ok, [&](uint32_t key, int i) {
-    if (key >= lower) {
+  if constexpr (Elem<T>::kPacked) {
+    // ---- 16-bit inputs: keys stay packed two per register. Each thread keeps two running
+    // maxima (even / odd elements), 1024 in all; the kk-th largest of them bounds the kk-th
+    // largest element of the row from below.
+    uint32_t tm2 = 0;
+    const int nvec = vec_ok ? v / 8 : 0;
+    const uint4* vp = reinterpret_cast<const uint4*>(rp);
+    // eight independent 16-byte loads in flight per thread: the row is latency-, not
+    // bandwidth-bound when a single CTA pulls it
+    constexpr int kU = 8;
+    int i = tid;
+    for (; i + (kU - 1) * nt < nvec; i += kU * nt) {
+      uint4 raw[kU];
+#pragma unroll
+      for (int u = 0; u < kU; ++u) raw[u] = __ldg(vp + i + u * nt);
+#pragma unroll
+      for (int u = 0; u < kU; ++u)
+        tm2 = __vmaxu2(tm2, __vmaxu2(__vmaxu2(key16x2<T>(raw[u].x), key16x2<T>(raw[u].y)),
+                                     __vmaxu2(key16x2<T>(raw[u].z), key16x2<T>(raw[u].w))));
+    }
+    for (; i < nvec; i += nt) {
+      const uint4 raw = __ldg(vp + i);
+      tm2 = __vmaxu2(tm2, __vmaxu2(__vmaxu2(key16x2<T>(raw.x), key16x2<T>(raw.y)),
+                                   __vmaxu2(key16x2<T>(raw.z), key16x2<T>(raw.w))));
+    }
+    const unsigned short* hp = reinterpret_cast<const unsigned short*>(rp);
+    for (int t = nvec * 8 + tid; t < v; t += nt) tm2 = __vmaxu2(tm2, key16x2<T>(hp[t]) & 0xFFFFu);
+    const uint32_t m_lo = tm2 & 0xFFFFu, m_hi = tm2 >> 16;
+    uint32_t low16 = 0;
+    for (int bit = 15; bit >= 0; --bit) {
+      const uint32_t cand = low16 | (1u << bit);
+      const int cnt = __syncthreads_count(m_lo >= cand) + __syncthreads_count(m_hi >= cand);
+      if (cnt >= kk) low16 = cand;
+    }
+    // ---- pass 2 (L2): collect every element whose 16-bit key is >= the bound
+    const uint32_t low2 = low16 * 0x00010001u;
+    auto push = [&](uint32_t bits16, int idx) {
       const int slot = atomicAdd(&s.count, 1);
       if (slot < kCandCap) {
-        s.cand_key[slot] = key;
-        s.cand_idx[slot] = static_cast<uint32_t>(i);
+        s.cand_key[slot] = float_to_key(Elem<T>::to_float(from_bits16<T>(bits16)));
+        s.cand_idx[slot] = static_cast<uint32_t>(idx);
       }
+    };
+    auto scan_vec = [&](const uint4& raw, int vi) {
+      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+      const uint32_t h0 = __vcmpgeu2(key16x2<T>(w[0]), low2), h1 = __vcmpgeu2(key16x2<T>(w[1]), low2);
+      const uint32_t h2 = __vcmpgeu2(key16x2<T>(w[2]), low2), h3 = __vcmpgeu2(key16x2<T>(w[3]), low2);
+      if ((h0 | h1 | h2 | h3) == 0u) return;
+      const uint32_t hit[4] = {h0, h1, h2, h3};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (hit[j] & 0xFFFFu) push(w[j] & 0xFFFFu, vi * 8 + 2 * j);
+        if (hit[j] >> 16) push(w[j] >> 16, vi * 8 + 2 * j + 1);
+      }
+    };
+    i = tid;
+    for (; i + (kU - 1) * nt < nvec; i += kU * nt) {
+      uint4 raw[kU];
+#pragma unroll
+      for (int u = 0; u < kU; ++u) raw[u] = __ldg(vp + i + u * nt);
+#pragma unroll
+      for (int u = 0; u < kU; ++u) scan_vec(raw[u], i + u * nt);
     }
-  });
+    for (; i < nvec; i += nt) scan_vec(__ldg(vp + i), i);
+    for (int t = nvec * 8 + tid; t < v; t += nt)
+      if ((key16x2<T>(hp[t]) & 0xFFFFu) >= low16) push(hp[t], t);
+  } else {
+    // ---- 32-bit inputs
+    uint32_t tm[2] = {0, 0};
+    for_each_key<T>(rp, v, vec_ok, [&](uint32_t key, int i) { tm[i & 1] = max(tm[i & 1], key); });
+    for (int bit = 31; bit >= Elem<T>::kLowBit; --bit) {
+      const uint32_t cand = lower | (1u << bit);
+      const int cnt = __syncthreads_count(tm[0] >= cand) + __syncthreads_count(tm[1] >= cand);
+      if (cnt >= kk) lower = cand;
+    }
+    for_each_key<T>(rp, v, vec_ok, [&](uint32_t key, int i) {
+      if (key >= lower) {
+        const int slot = atomicAdd(&s.count, 1);
+        if (slot < kCandCap) {
+          s.cand_key[slot] = key;
+          s.cand_idx[slot] = static_cast<uint32_t>(i);
+        }
+      }
+    });
+  }
   __syncthreads();
   int n_cand = s.count;
   __syncthreads();
@@ -219,7 +338,7 @@ sample_topk_kernel(const T* __restrict__ logits, long long row_stride, int v, co
     __syncthreads();
     unsigned long long tie_base = 0;
     constexpr int kPer = 8;
-    for (int base = 0; base < v && tie_base < static_cast<unsigned long long>(quota); base += kThreads * kPer) {
+    for (int base = 0; base < v && tie_base < static_cast<unsigned long long>(quota); base += nt * kPer) {
       const int i0 = base + tid * kPer;
       int mine = 0;
       for (int j = 0; j < kPer; ++j) {
@@ -245,7 +364,7 @@ sample_topk_kernel(const T* __restrict__ logits, long long row_stride, int v, co
   }
 
   // ---- rank sort of the candidates by (key desc, id asc); the first kk are the survivors
-  for (int i = tid; i < n_cand; i += kThreads) {
+  for (int i = tid; i < n_cand; i += nt) {
     const uint32_t ki = s.cand_key[i], ii = s.cand_idx[i];
     int rank = 0;
     for (int j = 0; j < n_cand; ++j) {
@@ -261,16 +380,16 @@ sample_topk_kernel(const T* __restrict__ logits, long long row_stride, int v, co
 
   // ---- masses, top-p, draw
   const float y0 = mul_rn(key_to_float(s.sorted_key[0]), inv_temp);
-  if (tid < kk) {
-    const float y = mul_rn(key_to_float(s.sorted_key[tid]), inv_temp);
-    s.mass[tid] = mass_fixed(exp_det(sub_rn(y, y0)));
+  for (int i = tid; i < kk; i += nt) {
+    const float y = mul_rn(key_to_float(s.sorted_key[i]), inv_temp);
+    s.mass[i] = mass_fixed(exp_det(sub_rn(y, y0)));
   }
   __syncthreads();
-  if (tid == 0) {
+  if (tid < 32) {
     const unsigned long long rid = row_ids ? static_cast<unsigned long long>(row_ids[row])
                                            : static_cast<unsigned long long>(row);
-    const int pos = pick_sorted(s.mass, kk, top_p, uniform_u24(seed, rid, step));
-    out[row] = static_cast<int>(s.sorted_idx[pos]);
+    const int pos = pick_sorted_warp(s.mass, kk, top_p, uniform_u24(seed, rid, step));
+    if (tid == 0) out[row] = static_cast<int>(s.sorted_idx[pos]);
   }
 }
 
@@ -544,7 +663,7 @@ int launch_sampling(const void* logits, long long row_stride, int rows, int v, c
       if (e != cudaSuccess) return -10;
       configured = true;
     }
-    sample_topk_kernel<T><<<rows, kThreads, sizeof(TopkSmem), stream>>>(lp, row_stride, v, row_ids, inv_temp, top_k,
+    sample_topk_kernel<T><<<rows, kTopkThreads, sizeof(TopkSmem), stream>>>(lp, row_stride, v, row_ids, inv_temp, top_k,
                                                                          top_p, seed, step, out);
   } else {
     static bool configured = false;

@@ -108,10 +108,16 @@ rope_kernel(__nv_bfloat16* __restrict__ x, long long token_stride, const long lo
   }
 }
 
+__device__ __forceinline__ float tanh_approx(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __device__ __forceinline__ float silu_f(float g) {
-  // g * sigmoid(g) with exp through ex2
-  const float e = ex2_approx(__fmul_rn(-g, kLog2e));
-  return __fdiv_rn(g, __fadd_rn(1.f, e));
+  // g * sigmoid(g) = g * (0.5 + 0.5 * tanh(g / 2)): one special-function op per element
+  // (the result is rounded to bf16, tanh.approx is accurate to about 2^-11)
+  return __fmul_rn(g, __fmaf_rn(0.5f, tanh_approx(__fmul_rn(0.5f, g)), 0.5f));
 }
 
 // out[r, j] = silu(gate[r, j]) * up[r, j]; gate/up are column halves of one [rows, 2f] tensor

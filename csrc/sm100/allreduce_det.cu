@@ -32,7 +32,9 @@ struct ArParams {
   unsigned long long timeout_ns;
 };
 
-__device__ __forceinline__ float4 ld4(const float* p) { return ld_relaxed_sys_f4(reinterpret_cast<const float4*>(p)); }
+// Bulk data uses weak L2 loads / plain stores (they pipeline); ordering against the other ranks
+// comes from the acquire / release on the handshake flags.
+__device__ __forceinline__ float4 ld4(const float* p) { return __ldcg(reinterpret_cast<const float4*>(p)); }
 __device__ __forceinline__ float4 add4(float4 a, float4 b) {
   return make_float4(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y), __fadd_rn(a.z, b.z), __fadd_rn(a.w, b.w));
 }
@@ -73,7 +75,7 @@ allreduce_det_kernel(const __grid_constant__ ArParams p) {
       const float4 t = tree8(s, p.world);
 #pragma unroll
       for (int r = 0; r < 8; ++r)
-        if (r < p.world) st_relaxed_sys_f4(reinterpret_cast<float4*>(static_cast<float*>(p.buf[r]) + off), t);
+        if (r < p.world) *reinterpret_cast<float4*>(static_cast<float*>(p.buf[r]) + off) = t;
     }
   } else {
     const long long nvec = slice / 4;  // 4 bf16 = 8 bytes per step
@@ -83,7 +85,7 @@ allreduce_det_kernel(const __grid_constant__ ArParams p) {
 #pragma unroll
       for (int r = 0; r < 8; ++r)
         if (r < p.world) {
-          const uint2 raw = ld_relaxed_sys_u2(static_cast<const __nv_bfloat16*>(p.buf[r]) + off);
+          const uint2 raw = __ldcg(reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(p.buf[r]) + off));
           const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
           const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
           s[r] = make_float4(__bfloat162float(a.x), __bfloat162float(a.y), __bfloat162float(b.x), __bfloat162float(b.y));
@@ -95,7 +97,7 @@ allreduce_det_kernel(const __grid_constant__ ArParams p) {
       o.y = *reinterpret_cast<const uint32_t*>(&o1);
 #pragma unroll
       for (int r = 0; r < 8; ++r)
-        if (r < p.world) st_relaxed_sys_u2(static_cast<__nv_bfloat16*>(p.buf[r]) + off, o);
+        if (r < p.world) *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(p.buf[r]) + off) = o;
     }
   }
 

@@ -24,14 +24,18 @@ constexpr int kBM = 128;           // rows per CTA
 constexpr int kBN = 256;           // columns per tile
 constexpr int kBK = 64;            // K per stage
 constexpr int kUmmaK = 16;
-constexpr int kThreads = 192;      // warps 0-3 epilogue, 4 producer, 5 MMA
+constexpr int kEpiWarps = 8;        // two per TMEM lane quarter: columns [0,128) and [128,256)
+constexpr int kEpiThreads = kEpiWarps * 32;
+constexpr int kWarpTma = kEpiWarps, kWarpMma = kEpiWarps + 1, kWarpPub = kEpiWarps + 2;
+constexpr int kThreads = kEpiThreads + 96;  // epilogue warps, TMA producer, MMA issuer, flag publisher
 constexpr int kStages = 6;
 constexpr int kABytes = kBM * kBK * 2;            // 16 KiB
 constexpr int kBBytes = (kBN / kG) * kBK * 2;     // 16 KiB
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kTxBytes = kStageBytes * kG;
 constexpr int kTileBytes = kStages * kStageBytes;
-constexpr int kSmemBytes = kTileBytes + 1024 + 1024;
+constexpr int kEpiBufWords = 32 * 33;     // per epilogue warp: 32 rows x 32 words, padded
+constexpr int kSmemBytes = kTileBytes + 1024 + 512 + kEpiWarps * kEpiBufWords * 4;
 constexpr int kGroupM = 8;         // row tiles that share a column tile in the schedule
 
 struct Control {
@@ -39,6 +43,8 @@ struct Control {
   uint64_t empty[kStages];
   uint64_t tfull[2];
   uint64_t tempty[2];
+  uint64_t pub_full[2];   // a unit's partial tile has been stored by every epilogue warp
+  uint64_t pub_empty[2];  // the publisher has raised the flag of the unit that used this slot
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -75,7 +81,7 @@ __device__ __forceinline__ void decode_unit(const GemmParams& p, int tiles_m, in
   if (p.a_gather) out.m_blk = (out.m_blk + (p.rank * p.a_rows_per_rank) / (kBM * kG)) % tiles_m;
 }
 
-__device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory"); }
 
 __device__ __forceinline__ void tmem_ld_wait_dep(uint32_t (&v)[32]) {
   asm volatile(
@@ -100,14 +106,22 @@ struct RowCtx {
   long long tgt;   // target column inside this shard (or out of range)
 };
 
-// Store 32 consecutive accumulator columns of one row.
-__device__ __forceinline__ void store_group(const GemmParams& p, const uint32_t (&v)[32], long long row, int col,
-                                            int slice_global, const RowCtx& rc) {
-  if (col >= p.n) return;
-  const bool full = col + 32 <= p.n;
-  if (p.epilogue == kEpiLogitsGrad) {
+// Store 32 consecutive accumulator columns of the warp's 32 rows. Each lane holds one row
+// (that is how tcgen05.ld hands out TMEM lanes); the values are transposed through a padded
+// shared-memory tile so that the global stores are whole 64 / 128-byte row segments: eight
+// (fp32) or four (bf16) lanes cover one row segment contiguously. This matters most for the
+// partial tiles that go to another GPU, where every store instruction becomes NVLink packets.
+__device__ __forceinline__ void store_group_warp(const GemmParams& p, const uint32_t (&v)[32], uint32_t* wbuf,
+                                                 long long row_w0, int col, int slice_global, const RowCtx& rc,
+                                                 int lane) {
+  if (col >= p.n) return;  // uniform over the warp
+  const bool f32 = p.epilogue == kEpiStoreF32;
+  uint32_t* mine = wbuf + lane * 33;
+  if (f32) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) mine[j] = v[j];
+  } else if (p.epilogue == kEpiLogitsGrad) {
     const float s2 = p.scale * 1.4426950408889634f;
-    __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.c) + row * p.ldc + col;
     float d[32];
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
@@ -116,45 +130,50 @@ __device__ __forceinline__ void store_group(const GemmParams& p, const uint32_t 
       d[j] = __fmul_rn(rc.gs, __fsub_rn(one, pr));
     }
 #pragma unroll
-    for (int j = 0; j < 32; j += 8) {
-      if (full || col + j + 8 <= p.n) {
-        uint4 o;
-        o.x = pack_bf16(d[j], d[j + 1]);
-        o.y = pack_bf16(d[j + 2], d[j + 3]);
-        o.z = pack_bf16(d[j + 4], d[j + 5]);
-        o.w = pack_bf16(d[j + 6], d[j + 7]);
-        *reinterpret_cast<uint4*>(dst + j) = o;
-      }
-    }
-  } else if (p.epilogue == kEpiStoreBf16) {
-    __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.c) + row * p.ldc + col;
+    for (int j = 0; j < 16; ++j) mine[j] = pack_bf16(d[2 * j], d[2 * j + 1]);
+  } else {
 #pragma unroll
-    for (int j = 0; j < 32; j += 8) {
-      if (full || col + j + 8 <= p.n) {
-        uint4 o;
-        o.x = pack_bf16(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
-        o.y = pack_bf16(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
-        o.z = pack_bf16(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]));
-        o.w = pack_bf16(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
-        *reinterpret_cast<uint4*>(dst + j) = o;
+    for (int j = 0; j < 16; ++j) mine[j] = pack_bf16(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+  }
+  __syncwarp();
+  if (f32) {
+    float* base = static_cast<float*>(p.c) + row_w0 * p.ldc + col;
+    const long long ld = p.ldc;
+    const int c = lane & 7, r0 = lane >> 3;
+    const bool col_ok = col + c * 4 + 4 <= p.n;
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+      const int r = r0 + 4 * it;
+      if (col_ok && row_w0 + r < p.m) {
+        const uint32_t* src = wbuf + r * 33 + c * 4;
+        *reinterpret_cast<uint4*>(base + r * ld + c * 4) = make_uint4(src[0], src[1], src[2], src[3]);
       }
     }
   } else {
-    float* dst;
-    if (p.epilogue == kEpiStoreF32) {
-      dst = static_cast<float*>(p.c) + row * p.ldc + col;
+    __nv_bfloat16* base;
+    long long ld;
+    if (p.epilogue == kEpiPartialF32) {
+      const int owner = static_cast<int>(row_w0 / p.rows_per_rank);
+      const long long lr = row_w0 - static_cast<long long>(owner) * p.rows_per_rank;
+      base = static_cast<__nv_bfloat16*>(p.stage[owner]) +
+             (static_cast<long long>(slice_global) * p.rows_per_rank + lr) * p.n + col;
+      ld = p.n;
     } else {
-      const int owner = static_cast<int>(row / p.rows_per_rank);
-      const long long lr = row - static_cast<long long>(owner) * p.rows_per_rank;
-      dst = p.stage[owner] + (static_cast<long long>(slice_global) * p.rows_per_rank + lr) * p.n + col;
+      base = static_cast<__nv_bfloat16*>(p.c) + row_w0 * p.ldc + col;
+      ld = p.ldc;
     }
+    const int c = lane & 3, r0 = lane >> 2;
+    const bool col_ok = col + c * 8 + 8 <= p.n;
 #pragma unroll
-    for (int j = 0; j < 32; j += 4) {
-      if (full || col + j + 4 <= p.n) {
-        *reinterpret_cast<uint4*>(dst + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+    for (int it = 0; it < 4; ++it) {
+      const int r = r0 + 8 * it;
+      if (col_ok && row_w0 + r < p.m) {
+        const uint32_t* src = wbuf + r * 33 + c * 4;
+        *reinterpret_cast<uint4*>(base + r * ld + c * 8) = make_uint4(src[0], src[1], src[2], src[3]);
       }
     }
   }
+  __syncwarp();
 }
 
 __device__ __forceinline__ float4 ld_f4_sys(const float* p) {
@@ -172,6 +191,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   const uint32_t tiles_addr = (raw_addr + 1023u) & ~1023u;
   uint8_t* tiles = smem_raw + (tiles_addr - raw_addr);
   Control* ctl = reinterpret_cast<Control*>(tiles + kTileBytes);
+  uint32_t* epi_buf = reinterpret_cast<uint32_t*>(tiles + kTileBytes + 512);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -194,16 +214,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&ctl->tfull[b]), 1);
-      mbar_init(smem_u32(&ctl->tempty[b]), 4 * kG);
+      mbar_init(smem_u32(&ctl->tempty[b]), kEpiWarps * kG);
+      mbar_init(smem_u32(&ctl->pub_full[b]), kEpiWarps);
+      mbar_init(smem_u32(&ctl->pub_empty[b]), 1);
     }
     ctl->abort_flag = 0;
     fence_mbar_init_cluster();
   }
-  if (warp == 5) {
+  if (warp == kWarpMma) {
     tmem_alloc<kG>(smem_u32(&ctl->tmem_base), 512);
     tmem_relinquish<kG>();
   }
-  if (warp == 4 && lane == 0) {
+  if (warp == kWarpTma && lane == 0) {
     tma_prefetch_desc(&tm_a);
     tma_prefetch_desc(&tm_b);
   }
@@ -214,7 +236,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   tc_fence_after_sync();
   const uint32_t tmem_base = ctl->tmem_base;
 
-  if (warp == 4) {
+  if (warp == kWarpTma) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       int stage = 0;
@@ -264,7 +286,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == kWarpMma) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0 && leader) {
       const uint32_t idesc = umma_idesc_bf16_f32(kBM * kG, kBN) | (static_cast<uint32_t>(p.a_major) << 15) |
@@ -305,11 +327,40 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         if (abuf == 0) aphase ^= 1u;
       }
     }
+  } else if (warp == kWarpPub) {
+    // ------------------------------------------------------------------ flag publisher
+    // Partial tiles become visible to their owner through a system-scope fence and a flag
+    // store. The fence waits for this SM's outstanding (possibly NVLink) writes, which takes
+    // microseconds, so it runs in a warp of its own, off the epilogue's critical path.
+    if (lane == 0 && p.epilogue == kEpiPartialF32) {
+      int slot = 0;
+      uint32_t phase = 0;
+      const int rblks = p.rows_per_rank / kBM;
+      for (int u = pair_id; u < n_units; u += n_pairs) {
+        Unit un;
+        decode_unit(p, tiles_m, tiles_n, u, un);
+        if (!mbar_wait_bounded(smem_u32(&ctl->pub_full[slot]), phase, wctx, kWReduceFlag, slot)) break;
+        __threadfence_system();
+        const long long row0 = static_cast<long long>(un.m_blk) * (kBM * kG) + cta_rank * kBM;
+        if (row0 < p.m) {
+          const int owner = static_cast<int>(row0 / p.rows_per_rank);
+          const int rblk = static_cast<int>((row0 - static_cast<long long>(owner) * p.rows_per_rank) / kBM);
+          st_release_sys_u32(p.flags[owner] + (static_cast<size_t>(p.slice_base + un.slice) * rblks + rblk) * tiles_n +
+                                 un.n_blk,
+                             p.epoch);
+        }
+        mbar_arrive(smem_u32(&ctl->pub_empty[slot]));
+        slot ^= 1;
+        if (slot == 0) phase ^= 1u;
+      }
+    }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 0-3)
-    // Every named barrier below is reached by all 128 threads; leaving is decided from the
-    // shared abort flag right after a barrier.
+    // ------------------------------------------------------------------ epilogue (warps 0-7)
+    // Warp w reads TMEM lanes 32 * (w & 3) .. +31 (its rows) and columns 128 * (w >> 2) .. +127.
+    // The unit loop has no CTA-wide barrier: a warp whose wait runs out simply leaves it. The
+    // named barriers of the copy and reduce phases are reached by all 256 threads.
     const int tid = threadIdx.x;
+    const int wq = warp & 3, wh = warp >> 2;
     bool ok = true;
 
     if (p.a_gather) {
@@ -318,19 +369,33 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       const int blocks = p.a_rows_per_rank / kBM;
       const int vec_per_row = p.k / 8;  // 16-byte vectors
       const uint4* src = static_cast<const uint4*>(p.a_local);
-      for (int blk = blockIdx.x; blk < blocks; blk += gridDim.x) {
-        const long long v0 = static_cast<long long>(blk) * kBM * vec_per_row;
-        const long long nv = static_cast<long long>(kBM) * vec_per_row;
-        for (int d = 0; d < p.world; ++d) {
-          const int dst_rank = (p.rank + d) % p.world;  // start with the local copy
-          uint4* dst = static_cast<uint4*>(p.a_bufs[dst_rank]) +
-                       static_cast<long long>(p.rank) * p.a_rows_per_rank * vec_per_row + v0;
-          for (long long i = tid; i < nv; i += 128) dst[i] = src[v0 + i];
+      const long long nv = static_cast<long long>(kBM) * vec_per_row;
+      // work item = (destination, 128-row block), destination-major starting with this rank, so
+      // the local copy (which this rank's own GEMM needs first) leaves first
+      for (int it = blockIdx.x; it < blocks * p.world; it += gridDim.x) {
+        const int d = it / blocks, blk = it - d * blocks;
+        const int dst_rank = (p.rank + d) % p.world;
+        const long long v0 = static_cast<long long>(blk) * nv;
+        uint4* dst = static_cast<uint4*>(p.a_bufs[dst_rank]) +
+                     static_cast<long long>(p.rank) * p.a_rows_per_rank * vec_per_row + v0;
+        constexpr int kS = kEpiThreads;
+        for (long long i = tid; i < nv; i += 4 * kS) {
+          // four independent 16-byte copies in flight per thread
+          uint4 t0 = src[v0 + i], t1, t2, t3;
+          const bool b1 = i + kS < nv, b2 = i + 2 * kS < nv, b3 = i + 3 * kS < nv;
+          if (b1) t1 = src[v0 + i + kS];
+          if (b2) t2 = src[v0 + i + 2 * kS];
+          if (b3) t3 = src[v0 + i + 3 * kS];
+          dst[i] = t0;
+          if (b1) dst[i + kS] = t1;
+          if (b2) dst[i + 2 * kS] = t2;
+          if (b3) dst[i + 3 * kS] = t3;
         }
-        __threadfence_system();
         epi_bar();
-        if (tid < p.world)
-          st_release_sys_u32(p.a_flags[tid] + static_cast<size_t>(p.rank) * blocks + blk, p.epoch);
+        if (tid == 0) {
+          __threadfence_system();
+          st_release_sys_u32(p.a_flags[dst_rank] + static_cast<size_t>(p.rank) * blocks + blk, p.epoch);
+        }
       }
     }
 
@@ -340,64 +405,57 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     for (int u = pair_id; u < n_units; u += n_pairs) {
       Unit un;
       decode_unit(p, tiles_m, tiles_n, u, un);
-      const long long row = static_cast<long long>(un.m_blk) * (kBM * kG) + cta_rank * kBM + tid;
+      const long long row_w0 = static_cast<long long>(un.m_blk) * (kBM * kG) + cta_rank * kBM + wq * 32;
+      const long long row = row_w0 + lane;
       const bool mine = mbar_wait_bounded(smem_u32(&ctl->tfull[abuf]), aphase, wctx, kWEpi, abuf);
       ok = __all_sync(0xffffffffu, mine) != 0;
-      if (ok) {
-        tc_fence_after_sync();
-        const uint32_t trow = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + static_cast<uint32_t>(abuf * kBN);
-        const int slice_global = p.slice_base + un.slice;
-        RowCtx rc = {0.f, 0.f, -1};
-        if (p.epilogue == kEpiLogitsGrad && row < p.m) {
-          rc.neg_lse2 = __fmul_rn(-p.row_lse[row], 1.4426950408889634f);
-          rc.gs = __fmul_rn(p.row_g[row], p.scale);
-          rc.tgt = p.row_ids[row] - p.col_offset;
-        }
-        uint32_t va[32], vb[32];
-        tmem_ld_32x32(trow, va);
-        tmem_ld_wait_dep(va);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t trow = tmem_base + (static_cast<uint32_t>(wq * 32) << 16) +
+                            static_cast<uint32_t>(abuf * kBN + wh * (kBN / 2));
+      const int col0 = un.n_blk * kBN + wh * (kBN / 2);
+      const int slice_global = p.slice_base + un.slice;
+      RowCtx rc = {0.f, 0.f, -1};
+      if (p.epilogue == kEpiLogitsGrad && row < p.m) {
+        rc.neg_lse2 = __fmul_rn(-p.row_lse[row], 1.4426950408889634f);
+        rc.gs = __fmul_rn(p.row_g[row], p.scale);
+        rc.tgt = p.row_ids[row] - p.col_offset;
+      }
+      uint32_t* wbuf = epi_buf + warp * kEpiBufWords;
+      uint32_t va[32], vb[32];
+      tmem_ld_32x32(trow, va);
+      tmem_ld_wait_dep(va);
 #pragma unroll
-        for (int g = 0; g < kBN / 32; g += 2) {
-          __syncwarp();
-          tmem_ld_32x32(trow + (g + 1) * 32, vb);
-          if (row < p.m) store_group(p, va, row, un.n_blk * kBN + g * 32, slice_global, rc);
-          __syncwarp();
-          tmem_ld_wait_dep(vb);
-          if (g + 2 < kBN / 32) tmem_ld_32x32(trow + (g + 2) * 32, va);
-          if (row < p.m) store_group(p, vb, row, un.n_blk * kBN + (g + 1) * 32, slice_global, rc);
-          __syncwarp();
-          if (g + 2 < kBN / 32) tmem_ld_wait_dep(va);
-        }
-        tc_fence_before_sync();
+      for (int g = 0; g < kBN / 64; g += 2) {
         __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(tempty_leader + static_cast<uint32_t>(abuf) * 8u);
-        abuf ^= 1;
-        if (abuf == 0) aphase ^= 1u;
+        tmem_ld_32x32(trow + (g + 1) * 32, vb);
+        store_group_warp(p, va, wbuf, row_w0, col0 + g * 32, slice_global, rc, lane);
+        __syncwarp();
+        tmem_ld_wait_dep(vb);
+        if (g + 2 < kBN / 64) tmem_ld_32x32(trow + (g + 2) * 32, va);
+        store_group_warp(p, vb, wbuf, row_w0, col0 + (g + 1) * 32, slice_global, rc, lane);
+        __syncwarp();
+        if (g + 2 < kBN / 64) tmem_ld_wait_dep(va);
       }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(tempty_leader + static_cast<uint32_t>(abuf) * 8u);
       if (p.epilogue == kEpiPartialF32) {
-        // publish: this CTA's 128 rows x 256 columns of slice `slice_global` are in place
-        __threadfence_system();
-        epi_bar();
-        if (ctl->abort_flag) {
-          ok = false;
-          break;
-        }
-        if (tid == 0) {
-          const long long row0 = static_cast<long long>(un.m_blk) * (kBM * kG) + cta_rank * kBM;
-          if (row0 < p.m) {
-            const int owner = static_cast<int>(row0 / p.rows_per_rank);
-            const int rblk = static_cast<int>((row0 - static_cast<long long>(owner) * p.rows_per_rank) / kBM);
-            const int rblks = p.rows_per_rank / kBM;
-            st_release_sys_u32(p.flags[owner] + (static_cast<size_t>(p.slice_base + un.slice) * rblks + rblk) * tiles_n +
-                                   un.n_blk,
-                               p.epoch);
-          }
-        }
-      } else if (!ok) {
-        break;
+        // this warp's part of the partial tile has been stored: let the publisher count it, once
+        // the publisher is done with the unit that used this slot two units ago
+        const bool free_slot = mbar_wait_bounded(smem_u32(&ctl->pub_empty[abuf]), aphase ^ 1u, wctx, kWReduceFlag, 100 + abuf);
+        ok = __all_sync(0xffffffffu, free_slot) != 0;
+        if (!ok) break;
+        if (lane == 0) mbar_arrive(smem_u32(&ctl->pub_full[abuf]));
       }
+      abuf ^= 1;
+      if (abuf == 0) aphase ^= 1u;
     }
 
+    if (p.epilogue == kEpiPartialF32) {
+      epi_bar();  // every epilogue thread gets here, whether or not its loop ran to the end
+      if (ctl->abort_flag) ok = false;
+    }
     if (p.epilogue == kEpiPartialF32 && ok) {
       // ---- reduce-scatter tail: the rows this rank owns, slices combined by a balanced tree
       const int rblks = p.rows_per_rank / kBM;
@@ -412,37 +470,57 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         epi_bar();
         if (ctl->abort_flag) break;
         const int ncols = min(kBN, p.n - nb * kBN);
-        const int vec_per_row = ncols / 4;
+        const int vec_per_row = ncols / 8;  // 8 bf16 = 16 bytes
         const size_t slice_stride = static_cast<size_t>(p.rows_per_rank) * p.n;
-        for (int i = tid; i < kBM * vec_per_row; i += 128) {
-          const int r = i / vec_per_row, c4 = i - r * vec_per_row;
+#pragma unroll 2
+        for (int i = tid; i < kBM * vec_per_row; i += kEpiThreads) {
+          const int r = i / vec_per_row, c8 = i - r * vec_per_row;
           const int lr = rblk * kBM + r;
           if (lr >= rows_valid) continue;
-          const size_t off = static_cast<size_t>(lr) * p.n + nb * kBN + c4 * 4;
-          const float* base = p.stage[p.rank] + off;
-          float4 s[8];
+          const size_t off = static_cast<size_t>(lr) * p.n + nb * kBN + c8 * 8;
+          const __nv_bfloat16* base = static_cast<const __nv_bfloat16*>(p.stage[p.rank]) + off;
+          float4 lo[8], hi[8];
 #pragma unroll
-          for (int q = 0; q < 8; ++q)
-            s[q] = q < p.total_slices ? ld_f4_sys(base + q * slice_stride) : make_float4(0.f, 0.f, 0.f, 0.f);
-          const float4 t01 = add4(s[0], s[1]), t23 = add4(s[2], s[3]), t45 = add4(s[4], s[5]), t67 = add4(s[6], s[7]);
-          float4 acc = add4(add4(t01, t23), add4(t45, t67));
-          __nv_bfloat16* outp = static_cast<__nv_bfloat16*>(p.out) + off;
+          for (int q = 0; q < 8; ++q) {
+            if (q < p.total_slices) {
+              // weak L2 loads: the acquire on the flags (and the barrier) orders them after the peers'
+              // stores, and unlike system-scope strong loads they pipeline
+              const float4 raw = __ldcg(reinterpret_cast<const float4*>(base + q * slice_stride));
+              const uint32_t w0 = __float_as_uint(raw.x), w1 = __float_as_uint(raw.y), w2 = __float_as_uint(raw.z),
+                             w3 = __float_as_uint(raw.w);
+              lo[q] = make_float4(__uint_as_float(w0 << 16), __uint_as_float(w0 & 0xFFFF0000u),
+                                  __uint_as_float(w1 << 16), __uint_as_float(w1 & 0xFFFF0000u));
+              hi[q] = make_float4(__uint_as_float(w2 << 16), __uint_as_float(w2 & 0xFFFF0000u),
+                                  __uint_as_float(w3 << 16), __uint_as_float(w3 & 0xFFFF0000u));
+            } else {
+              lo[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+              hi[q] = lo[q];
+            }
+          }
+          float4 a0 = add4(add4(add4(lo[0], lo[1]), add4(lo[2], lo[3])), add4(add4(lo[4], lo[5]), add4(lo[6], lo[7])));
+          float4 a1 = add4(add4(add4(hi[0], hi[1]), add4(hi[2], hi[3])), add4(add4(hi[4], hi[5]), add4(hi[6], hi[7])));
           if (p.residual) {
             // residual add in bf16 arithmetic order: round the GEMM result first, as a separate
             // bf16 linear + add would
-            const __nv_bfloat16* rp = static_cast<const __nv_bfloat16*>(p.residual) + off;
-            const uint2 rr = *reinterpret_cast<const uint2*>(rp);
-            const __nv_bfloat162 r01 = *reinterpret_cast<const __nv_bfloat162*>(&rr.x);
-            const __nv_bfloat162 r23 = *reinterpret_cast<const __nv_bfloat162*>(&rr.y);
-            acc.x = __fadd_rn(__bfloat162float(__float2bfloat16_rn(acc.x)), __bfloat162float(r01.x));
-            acc.y = __fadd_rn(__bfloat162float(__float2bfloat16_rn(acc.y)), __bfloat162float(r01.y));
-            acc.z = __fadd_rn(__bfloat162float(__float2bfloat16_rn(acc.z)), __bfloat162float(r23.x));
-            acc.w = __fadd_rn(__bfloat162float(__float2bfloat16_rn(acc.w)), __bfloat162float(r23.y));
+            const uint4 rr = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.residual) + off);
+            auto addr = [](float g, uint32_t rbits) {
+              return __fadd_rn(__bfloat162float(__float2bfloat16_rn(g)), __uint_as_float(rbits));
+            };
+            a0.x = addr(a0.x, rr.x << 16);
+            a0.y = addr(a0.y, rr.x & 0xFFFF0000u);
+            a0.z = addr(a0.z, rr.y << 16);
+            a0.w = addr(a0.w, rr.y & 0xFFFF0000u);
+            a1.x = addr(a1.x, rr.z << 16);
+            a1.y = addr(a1.y, rr.z & 0xFFFF0000u);
+            a1.z = addr(a1.z, rr.w << 16);
+            a1.w = addr(a1.w, rr.w & 0xFFFF0000u);
           }
-          uint2 o;
-          o.x = pack_bf16(acc.x, acc.y);
-          o.y = pack_bf16(acc.z, acc.w);
-          *reinterpret_cast<uint2*>(outp) = o;
+          uint4 o;
+          o.x = pack_bf16(a0.x, a0.y);
+          o.y = pack_bf16(a0.z, a0.w);
+          o.z = pack_bf16(a1.x, a1.y);
+          o.w = pack_bf16(a1.z, a1.w);
+          *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + off) = o;
         }
       }
     }
@@ -457,7 +535,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   __syncthreads();
   cluster_arrive();
   cluster_wait();
-  if (warp == 5) {
+  if (warp == kWarpMma) {
     __syncwarp();
     tc_fence_after_sync();
     tmem_dealloc<kG>(tmem_base, 512);

@@ -10,7 +10,8 @@
 // Invariance: one CTA pair owns a 256 x 256 output tile and walks K in a fixed order that
 // does not depend on M, N or the grid; there is no split-K chosen from the problem size.
 // With k_slices > 1 the K range is cut into that many equal slices whose fp32 partial sums
-// are emitted separately (the tensor-parallel path combines them in a fixed tree order).
+// are emitted separately, each rounded to bf16 once (the tensor-parallel path adds them in fp32
+// in a fixed tree order and rounds the sum once more).
 #pragma once
 
 #include <cstddef>
@@ -22,7 +23,7 @@ namespace ka {
 enum GemmEpilogue : int {
   kEpiStoreBf16 = 0,    // C bf16 [M, N]
   kEpiStoreF32 = 1,     // C fp32 [M, N]
-  kEpiPartialF32 = 2,   // fp32 partial per K slice, pushed to the row owner's staging buffer
+  kEpiPartialF32 = 2,   // K-slice partial (fp32 accumulated, stored as bf16), pushed to the row owner's staging buffer
   kEpiLogitsGrad = 3    // C bf16 = g[row] * scale * (onehot(ids[row]) - exp(scale * acc - lse[row]))
 };
 
@@ -38,7 +39,7 @@ struct GemmParams {
   int total_slices;       // canonical slice count (8)
   int world, rank;
   int rows_per_rank;      // rows of the output each rank owns (multiple of 128)
-  float* stage[8];        // per owner rank: [total_slices][rows_per_rank][n] fp32
+  void* stage[8];         // per owner rank: [total_slices][rows_per_rank][n] bf16
   unsigned* flags[8];     // per owner rank: [total_slices][row blocks of 128][n tiles of 256]
   unsigned epoch;
   void* out;              // reduced bf16 [rows_per_rank, n] of this rank

@@ -2,9 +2,9 @@
 // (csrc/sm100/gemm.cu does the work; this file owns the entry points and buffer layouts).
 //
 //   ka_gemm_reduce_scatter   row-parallel linear (K sharded): every rank multiplies its K
-//       slices; the epilogue stores each fp32 slice partial straight into the staging buffer of
+//       slices; the epilogue stores each slice partial (rounded to bf16 once) into the staging buffer of
 //       the rank that owns those rows (peer stores over NVLink) and raises a per-tile flag; the
-//       same kernel then combines, for the rows it owns, the 8 canonical slices in the fixed
+//       same kernel then adds, in fp32, for the rows it owns, the 8 canonical slices in the fixed
 //       order ((0+1)+(2+3))+((4+5)+(6+7)), adds the residual and writes bf16. Because K is
 //       always cut into the same 8 slices, 1, 2, 4 and 8 ranks perform the same additions.
 //   ka_all_gather_gemm       column-parallel linear on row-sharded input: every rank copies
@@ -33,10 +33,10 @@ inline int rows_per_rank_of(int m, int world) {
 extern "C" {
 
 // Bytes of the symmetric buffer a rank maps for ka_gemm_reduce_scatter: two generations of
-// [8 slices][rows_per_rank][n] fp32 staging, then the flags of both generations.
+// [8 slices][rows_per_rank][n] bf16 staging, then the flags of both generations.
 size_t ka_gemm_rs_exchange_bytes(int m, int n, int world) {
   const size_t rpr = rows_per_rank_of(m, world);
-  const size_t stage = round256(static_cast<size_t>(kSlices) * rpr * n * sizeof(float));
+  const size_t stage = round256(static_cast<size_t>(kSlices) * rpr * n * sizeof(__nv_bfloat16));
   const size_t flags = round256(static_cast<size_t>(kSlices) * (rpr / kBlk) * ((n + kTileN - 1) / kTileN) * 4);
   return 2 * stage + 2 * flags;
 }
@@ -68,13 +68,13 @@ int ka_gemm_reduce_scatter(const void* a, long long lda, const void* b, long lon
   p.rank = rank;
   p.rows_per_rank = rows_per_rank_of(m, world);
   const size_t rpr = p.rows_per_rank;
-  const size_t stage = round256(static_cast<size_t>(kSlices) * rpr * n * sizeof(float));
+  const size_t stage = round256(static_cast<size_t>(kSlices) * rpr * n * sizeof(__nv_bfloat16));
   const size_t flags = round256(static_cast<size_t>(kSlices) * (rpr / kBlk) * ((n + kTileN - 1) / kTileN) * 4);
   const unsigned gen = epoch & 1u;
   for (int r = 0; r < world; ++r) {
     uint8_t* base = static_cast<uint8_t*>(exchange[r]);
     if (!base) return -52;
-    p.stage[r] = reinterpret_cast<float*>(base + gen * stage);
+    p.stage[r] = base + gen * stage;
     p.flags[r] = reinterpret_cast<unsigned*>(base + 2 * stage + gen * flags);
   }
   p.epoch = epoch;

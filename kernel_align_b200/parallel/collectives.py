@@ -121,8 +121,9 @@ class GradReducer:
     """Bucketed, overlapped, deterministic gradient all-reduce for data parallelism.
 
     Parameters are packed (in reverse registration order, the order backward produces them)
-    into buckets of about ``bucket_bytes``; each bucket is one :class:`SymmetricVector` and the
-    parameters' ``.grad`` tensors are views into it, so no copy is needed. A bucket is reduced
+    into buckets of about ``bucket_bytes`` (one dtype per bucket); each bucket is one
+    :class:`SymmetricVector` and the parameters' ``.grad`` tensors are views into it, so no copy
+    is needed. A bucket is reduced
     on ``self.stream`` as soon as all of its gradients have been accumulated. ``finish()`` makes
     the current stream wait for every bucket and divides by the world size if ``average``.
     """
@@ -137,8 +138,8 @@ class GradReducer:
         self.buckets: list[dict] = []
         cur, cur_bytes = [], 0
         for p in reversed(self.params):
-            nbytes = p.numel() * 4
-            if cur and cur_bytes + nbytes > bucket_bytes:
+            nbytes = p.numel() * p.element_size()
+            if cur and (cur_bytes + nbytes > bucket_bytes or p.dtype != cur[0].dtype):
                 self._make_bucket(cur)
                 cur, cur_bytes = [], 0
             cur.append(p)
@@ -149,7 +150,10 @@ class GradReducer:
 
     def _make_bucket(self, plist):
         total = sum(p.numel() for p in plist)
-        vec = SymmetricVector(total, torch.float32, self.group, plist[0].device)
+        # the bucket carries the parameters' dtype (what autograd produces); the all-reduce adds
+        # in fp32 and rounds once at the end
+        dtype = torch.bfloat16 if plist[0].dtype == torch.bfloat16 else torch.float32
+        vec = SymmetricVector(total, dtype, self.group, plist[0].device)
         vec.tensor.zero_()
         off = 0
         for p in plist:

@@ -20,8 +20,8 @@ def _run_worker(script, nproc, timeout=600, extra_env=None):
     proc = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
     lines = [l for l in proc.stdout.splitlines() if l.startswith("RESULT ")]
     if proc.returncode != 0 or not lines:
-        err = [l for l in proc.stderr.splitlines() if "Error" in l or "error" in l or "rejected" in l]
-        raise AssertionError("worker failed: " + " | ".join(err[-12:]) + "\n" + proc.stdout[-1500:])
+        i = proc.stdout.find("WORKER_ERROR")
+        raise AssertionError("worker failed: " + (proc.stdout[i:i + 2500] if i >= 0 else proc.stdout[-1500:]))
     return json.loads(lines[-1][len("RESULT "):])
 
 

@@ -68,4 +68,10 @@ def main():
 
 
 if __name__ == "__main__":
-    main()
+    try:
+        main()
+    except Exception:  # make the failure visible in the parent's captured stdout
+        import traceback
+
+        print("WORKER_ERROR rank", os.environ.get("RANK"), traceback.format_exc()[-1500:], flush=True)
+        raise

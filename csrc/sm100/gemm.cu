@@ -456,8 +456,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       epi_bar();  // every epilogue thread gets here, whether or not its loop ran to the end
       if (ctl->abort_flag) ok = false;
     }
-    if (p.epilogue == kEpiPartialF32 && ok) {
-      // ---- reduce-scatter tail: the rows this rank owns, slices combined by a balanced tree
+    if (p.epilogue == kEpiPartialF32 && ok && p.out != nullptr) {
+      // ---- reduce-scatter tail (skipped when the caller only wants the partials staged): the rows this rank owns, slices combined by a balanced tree
       const int rblks = p.rows_per_rank / kBM;
       const int items = rblks * tiles_n;
       const int rows_valid = min(p.rows_per_rank, p.m - p.rank * p.rows_per_rank);

@@ -76,3 +76,35 @@ def sample_cpu(logits, *, inv_temperature: float, top_k: int, top_p: float, seed
     if rc != 0:
         raise RuntimeError(f"ka_cpu_sample failed ({rc})")
     return out
+
+
+def gemm_cpu(a, b):
+    """``a @ b.T`` in fp32 with a fixed per-element accumulation order (CPU oracle)."""
+    lib = _native.cpu()
+    af, bf = _f32(a), _f32(b)
+    m, k = af.shape
+    n = bf.shape[0]
+    out = torch.empty(m, n, dtype=torch.float32)
+    fn = lib.ka_cpu_gemm
+    fn.restype = c_int
+    fn.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int]
+    if fn(af.data_ptr(), bf.data_ptr(), out.data_ptr(), m, n, k) != 0:
+        raise RuntimeError("ka_cpu_gemm failed")
+    return out
+
+
+def gemm_sliced_cpu(a, b, residual=None, world: int = 1):
+    """CPU emulation of the fused GEMM -> reduce-scatter arithmetic (8 canonical K slices, bf16
+    partials, fp32 tree). ``world`` only assigns slices to emulated ranks."""
+    lib = _native.cpu()
+    af, bf = _f32(a), _f32(b)
+    rf = _f32(residual) if residual is not None else None
+    m, k = af.shape
+    n = bf.shape[0]
+    out = torch.empty(m, n, dtype=torch.float32)
+    fn = lib.ka_cpu_gemm_sliced
+    fn.restype = c_int
+    fn.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int]
+    if fn(af.data_ptr(), bf.data_ptr(), rf.data_ptr() if rf is not None else None, out.data_ptr(), m, n, k, world) != 0:
+        raise RuntimeError("ka_cpu_gemm_sliced failed")
+    return out

@@ -134,3 +134,18 @@ def test_sampling_ties_prefer_low_ids():
     assert all(t in (0, 1, 2) for t in tok.tolist())
     tok = sample(logits, top_k=None, top_p=0.01, seed=1, step=0)  # 1% of 500 equal tokens: ids 0..5
     assert all(t <= 5 for t in tok.tolist())
+
+
+def test_cpu_gemm_and_rank_emulator():
+    g = torch.Generator().manual_seed(7)
+    a = torch.randn(37, 256, generator=g).bfloat16()
+    b = (torch.randn(50, 256, generator=g) * 0.1).bfloat16()
+    r = torch.randn(37, 50, generator=g).bfloat16()
+    ref = a.float() @ b.float().t()
+    assert (cpu_ops.gemm_cpu(a, b) - ref).abs().max().item() < 1e-4
+    assert torch.equal(cpu_ops.gemm_cpu(a[5:6], b), cpu_ops.gemm_cpu(a, b)[5:6])
+    outs = [cpu_ops.gemm_sliced_cpu(a, b, residual=r, world=w) for w in (1, 2, 4, 8)]
+    for o in outs[1:]:
+        assert torch.equal(o, outs[0])  # the emulated rank count never enters the arithmetic
+    want = (ref.bfloat16().float() + r.float()).bfloat16().float()
+    assert (outs[0] - want).abs().max().item() <= 0.05 * want.abs().max().item()

@@ -66,10 +66,44 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool
     return (out, lse) if return_lse else out
 
 
+def attention_backward(q, k, v, out, d_out, lse, *, causal: bool = True, scale: Optional[float] = None):
+    """``(dq, dk, dv)`` from the saved forward results. CUDA: the tcgen05 kernels of
+    ``csrc/sm100/attention_bwd.cu`` (a dQ kernel and a dK/dV kernel, no atomics, fixed
+    accumulation order); CPU: fp32 matmul math."""
+    b, l, hq, d = q.shape
+    hkv = k.shape[2]
+    sc = float(scale) if scale is not None else 1.0 / math.sqrt(d)
+    if q.device.type != "cuda" or d != 128 or q.dtype != torch.bfloat16:
+        return _attention_backward_math(q, k, v, out, d_out, lse, causal, sc)
+
+    def tok(t):
+        ok = t.stride(3) == 1 and t.stride(2) == d and t.stride(0) == l * t.stride(1) and t.stride(1) % 8 == 0 \
+            and t.data_ptr() % 16 == 0
+        return t if ok else t.contiguous()
+
+    q, k, v, out, d_out = tok(q), tok(k), tok(v), tok(out), tok(d_out)
+    dq = torch.empty(b, l, hq, d, dtype=torch.bfloat16, device=q.device)
+    dk = torch.empty(b, l, hkv, d, dtype=torch.bfloat16, device=q.device)
+    dv = torch.empty(b, l, hkv, d, dtype=torch.bfloat16, device=q.device)
+    delta = torch.empty(b, hq, l, dtype=torch.float32, device=q.device)
+    lse = lse.contiguous()
+    fn = _native.cuda().ka_attention_bwd
+    fn.restype = c_int
+    fn.argtypes = [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p,
+                   c_longlong, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong,
+                   c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_ulonglong, c_void_p]
+    rc = fn(q.data_ptr(), q.stride(1), k.data_ptr(), k.stride(1), v.data_ptr(), v.stride(1), out.data_ptr(),
+            out.stride(1), d_out.data_ptr(), d_out.stride(1), lse.data_ptr(), delta.data_ptr(), dq.data_ptr(),
+            dq.stride(1), dk.data_ptr(), dk.stride(1), dv.data_ptr(), dv.stride(1), b, l, hq, hkv, d, sc, int(causal),
+            status_buffer(q.device).data_ptr(), default_timeout_ns(), torch.cuda.current_stream(q.device).cuda_stream)
+    if rc != 0:
+        raise RuntimeError(f"ka_attention_bwd rejected its arguments (code {rc})")
+    return dq, dk, dv
+
+
 def _attention_backward_math(q, k, v, out, d_out, lse, causal, scale):
-    """Gradient of attention from saved (q, k, v, out, lse), one (batch, kv head) block at a time
-    in fp32. Deterministic (plain matmuls, fixed order); a fused tcgen05 backward kernel is
-    the planned replacement for this interim path."""
+    """fp32 matmul formulation of the attention gradient, one sequence at a time (CPU path and
+    test oracle). Deterministic: plain matmuls in a fixed order."""
     b, l, hq, d = q.shape
     hkv = k.shape[2]
     g = hq // hkv
@@ -111,12 +145,12 @@ class _AttentionFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, d_out):
         q, k, v, out, lse = ctx.saved_tensors
-        dq, dk, dv = _attention_backward_math(q, k, v, out, d_out, lse, ctx.causal, ctx.scale)
+        dq, dk, dv = attention_backward(q, k, v, out, d_out.contiguous(), lse, causal=ctx.causal, scale=ctx.scale)
         return dq, dk, dv, None, None
 
 
 def attention_fn(q, k, v, *, causal: bool = True, scale: Optional[float] = None):
-    """Differentiable attention: forward on the tcgen05 kernel."""
+    """Differentiable attention: forward and backward on the tcgen05 kernels."""
     sc = float(scale) if scale is not None else 1.0 / math.sqrt(q.shape[-1])
     if not torch.is_grad_enabled() or not (q.requires_grad or k.requires_grad or v.requires_grad):
         return attention(q, k, v, causal=causal, scale=sc)

@@ -69,6 +69,20 @@ def main():
         flops = 4.0 * b_ * 32 * l * l * 128 / 2
         rec(f"attention fwd B={b_} L={l}", t, tb, flops / t / 1e9 / tf_burst,
             f"{flops / t / 1e9:.0f} TFLOP/s (causal) vs torch SDPA {flops / tb / 1e9:.0f}")
+        # backward: time (delta + dQ + dK/dV) alone against SDPA's backward alone
+        from kernel_align_b200.ops.attention import attention_backward
+        o, lse = attention(q, k, v, return_lse=True)
+        d_o = torch.randn_like(o)
+        t = time_cuda(lambda: attention_backward(q, k, v, o, d_o, lse, causal=True), flush_l2=False)
+        qr, kr, vr = (x.detach().requires_grad_() for x in (qs, ks, vs))
+        with torch.nn.attention.sdpa_kernel(torch.nn.attention.SDPBackend.FLASH_ATTENTION):
+            orr = F.scaled_dot_product_attention(qr, kr, vr, is_causal=True, enable_gqa=True)
+        dor = d_o.permute(0, 2, 1, 3)
+        tb = time_cuda(lambda: torch.autograd.grad(orr, (qr, kr, vr), dor, retain_graph=True), flush_l2=False)
+        bfl = 2.5 * flops
+        rec(f"attention bwd B={b_} L={l}", t, tb, bfl / t / 1e9 / tf_burst,
+            f"{bfl / t / 1e9:.0f} TFLOP/s (causal, 5 GEMMs) vs torch SDPA backward {bfl / tb / 1e9:.0f}")
+        del o, lse, d_o, orr, qr, kr, vr
     # memory-bound ops
     x = torch.randn(32768, 4096, device=dev, generator=g).to(torch.bfloat16)
     w = torch.ones(4096, device=dev, dtype=torch.bfloat16)

@@ -1,15 +1,19 @@
 // Batch-invariant causal attention forward for sm_100a (GQA, head_dim 128).
 //
-// One CTA per (sequence, query head, 128-row query tile). Q, K and V tiles arrive by TMA;
-// S = Q K^T and O_j = P_j V_j are tcgen05.mma (M=128, N=128) with fp32 accumulators in TMEM
-// (two S buffers and one O accumulator); eight softmax warps give every query row two
-// threads (64 columns each, so each scheduler has two warps to interleave; four per row ran
-// slower, the registers no longer fit), pull their part of the S row into registers in one go, write P as bf16 into a swizzled shared-memory tile
-// that the second MMA consumes, and let the MMA accumulate O in TMEM. The running maximum is
-// only moved when it grows by more than 2^8 (then O is rescaled in TMEM), so the common tile
-// needs no correction pass.
-// KV tiles are visited in increasing order, always 128 wide, whatever the batch size or the
-// number of heads on this GPU, so a query row's output depends on that sequence only.
+// One CTA works on TWO 128-row query tiles that share a KV head: two query heads of one GQA
+// group at the same rows (even group size) or two consecutive row tiles of one head. K and V
+// tiles arrive by TMA into a five-slot ring and are used by both tiles. S_t = Q_t K^T and
+// O_t += P_t V are tcgen05.mma (M=128, N=128) with fp32 accumulators in TMEM: columns
+// [0,128) and [128,256) hold S_0 and S_1, [256,384) and [384,512) hold O_0 and O_1. Four
+// softmax warps per tile give every query row one thread: it pulls its S row (128 columns)
+// into registers, and writes P as packed bf16 back into the first 64 columns of the same S
+// region, from where the second MMA reads it as a TMEM A operand, so P never touches shared
+// memory. While the softmax warps of one tile work, the tensor core runs the other tile's
+// MMAs. The running maximum is only moved when it grows by more than 2^8 (then the O row is
+// rescaled in TMEM), so the common tile needs no correction pass.
+// KV tiles are visited in increasing order, always 128 wide, whatever the batch size, the
+// pairing or the number of heads on this GPU, so a query row's output depends on its own
+// sequence only.
 //
 // The reference only routes the name "attention" to a backend string
 // (rl_engine/kernels/registry.py:41-55); there is no attention kernel in it.
@@ -27,29 +31,25 @@ namespace ka {
 namespace {
 
 constexpr int kD = 128;         // head dim
-constexpr int kBQ = 128;        // query rows per CTA
+constexpr int kBQ = 128;        // query rows per tile
 constexpr int kBKV = 128;       // keys per tile
-constexpr int kSplit = 2;        // softmax threads per query row (64 columns each)
-constexpr int kSoftThreads = 128 * kSplit;
+constexpr int kTiles = 2;       // query tiles per CTA
+constexpr int kSoftThreads = 128 * kTiles;
 constexpr int kThreads = kSoftThreads + 64;  // softmax warps, then one TMA warp and one MMA warp
 constexpr int kTileBytes = 128 * 128 * 2;  // 32 KiB: two 64-column boxes of 128 rows
-constexpr int kKvStages = 2;
-constexpr int kSmemBytes = kTileBytes /*Q*/ + kKvStages * 2 * kTileBytes /*K,V*/ + kTileBytes /*P*/ + 1024 + 8192;
+constexpr int kSlots = 5;                  // ring of K / V tiles
+constexpr int kSmemBytes = kTiles * kTileBytes + kSlots * kTileBytes + 1024 + 512;
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct Control {
   uint64_t q_full;
-  uint64_t kv_full[kKvStages];
-  uint64_t kv_empty[kKvStages];
-  uint64_t s_full[2];
-  uint64_t s_empty[2];
-  uint64_t p_full;
-  uint64_t p_empty;
-  uint64_t o_full;
+  uint64_t ring_full[kSlots];
+  uint64_t ring_empty[kSlots];
+  uint64_t s_full[kTiles];    // S_t of the next KV tile is in TMEM
+  uint64_t p_full[kTiles];    // P_t written (and the S_t columns read)
+  uint64_t pv_done[kTiles];   // O_t includes every P V product issued so far
   uint32_t tmem_base;
   int abort_flag;
-  float half_max[2][kSplit][128];  // [tile parity][column part][row]
-  float half_sum[kSplit][128];
 };
 
 struct AttnParams {
@@ -57,11 +57,39 @@ struct AttnParams {
   float* lse;             // [B, Hq, L] or null (natural-log log-sum-exp of the scaled scores)
   long long out_stride;   // elements between tokens in out
   int batch, seq_len, hq, hkv;
+  int pair_heads;         // 1: the two tiles are heads h, h+1 at the same rows; 0: row tiles 2i, 2i+1
   float scale;            // softmax scale (1/sqrt(D))
   int causal;
   int* status;
   unsigned long long timeout_ns;
 };
+
+struct TileCoord {
+  int h;        // query head
+  int row0;     // first query row inside the sequence
+  int n_kv;     // KV tiles this query tile visits (0: the tile does not exist)
+};
+
+__device__ __forceinline__ TileCoord tile_coord(const AttnParams& p, int unit, int head_unit, int t) {
+  const int n_qt = (p.seq_len + kBQ - 1) / kBQ;
+  TileCoord c;
+  int qt;
+  if (p.pair_heads) {
+    c.h = head_unit * 2 + t;
+    qt = unit;
+  } else {
+    c.h = head_unit;
+    qt = unit * 2 + t;
+  }
+  c.row0 = qt * kBQ;
+  if (qt >= n_qt) {
+    c.n_kv = 0;
+  } else {
+    const int kv_end = p.causal ? min(p.seq_len, c.row0 + kBQ) : p.seq_len;
+    c.n_kv = (kv_end + kBKV - 1) / kBKV;
+  }
+  return c;
+}
 
 __global__ void __launch_bounds__(kThreads, 1)
 attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -70,40 +98,38 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (base - raw_addr);
-  const uint32_t q_tile = base;
-  const uint32_t kv_tiles = base + kTileBytes;                       // stage s: K at +s*64K, V at +s*64K+32K
-  const uint32_t p_tile = kv_tiles + kKvStages * 2 * kTileBytes;
-  uint8_t* p_ptr = smem + kTileBytes + kKvStages * 2 * kTileBytes;
-  Control* ctl = reinterpret_cast<Control*>(p_ptr + kTileBytes);
+  const uint32_t q_tiles = base;                               // tile t at + t * 32 KiB
+  const uint32_t ring = base + kTiles * kTileBytes;            // slot s at + s * 32 KiB
+  Control* ctl = reinterpret_cast<Control*>(smem + (kTiles + kSlots) * kTileBytes);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // work decomposition: x = row unit (heavy, late rows first), then head unit, then sequence
   const int n_qt = (p.seq_len + kBQ - 1) / kBQ;
-  // heavy (late) query tiles first
-  const int qt = n_qt - 1 - static_cast<int>(blockIdx.x % n_qt);
-  const int bh = blockIdx.x / n_qt;
-  const int h = bh % p.hq;
-  const int b = bh / p.hq;
-  const int hk = h / (p.hq / p.hkv);
-  const int q_row0 = qt * kBQ;                       // inside the sequence
+  const int n_units = p.pair_heads ? n_qt : (n_qt + 1) / 2;
+  const int n_head_units = p.pair_heads ? p.hq / 2 : p.hq;
+  const int unit = n_units - 1 - static_cast<int>(blockIdx.x % n_units);
+  const int bh = blockIdx.x / n_units;
+  const int head_unit = bh % n_head_units;
+  const int b = bh / n_head_units;
+  const TileCoord tc0 = tile_coord(p, unit, head_unit, 0);
+  const TileCoord tc1 = tile_coord(p, unit, head_unit, 1);
+  const int hk = tc0.h / (p.hq / p.hkv);
   const int tok0 = b * p.seq_len;                    // first token of the sequence
-  const int kv_end = p.causal ? min(p.seq_len, q_row0 + kBQ) : p.seq_len;
-  const int n_kv = (kv_end + kBKV - 1) / kBKV;
+  const int n_max = max(tc0.n_kv, tc1.n_kv);
 
   WaitCtx wctx{&ctl->abort_flag, p.status, p.timeout_ns};
 
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(&ctl->q_full), 1);
-    for (int s = 0; s < kKvStages; ++s) {
-      mbar_init(smem_u32(&ctl->kv_full[s]), 1);
-      mbar_init(smem_u32(&ctl->kv_empty[s]), 1);
+    for (int s = 0; s < kSlots; ++s) {
+      mbar_init(smem_u32(&ctl->ring_full[s]), 1);
+      mbar_init(smem_u32(&ctl->ring_empty[s]), 1);
     }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(smem_u32(&ctl->s_full[i]), 1);
-      mbar_init(smem_u32(&ctl->s_empty[i]), 4 * kSplit);
+    for (int t = 0; t < kTiles; ++t) {
+      mbar_init(smem_u32(&ctl->s_full[t]), 1);
+      mbar_init(smem_u32(&ctl->p_full[t]), 4);
+      mbar_init(smem_u32(&ctl->pv_done[t]), 1);
     }
-    mbar_init(smem_u32(&ctl->o_full), 1);
-    mbar_init(smem_u32(&ctl->p_full), 4 * kSplit);
-    mbar_init(smem_u32(&ctl->p_empty), 1);
     ctl->abort_flag = 0;
     fence_mbar_init_cluster();
   }
@@ -115,126 +141,152 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = ctl->tmem_base;
-  const uint32_t tmem_s = tmem_base;          // S buffers: columns [0,128) and [128,256)
-  const uint32_t tmem_o = tmem_base + 256;    // O accumulator: columns [256,384)
 
   if (warp == kSoftThreads / 32) {
     // ------------------------------------------------------------------ TMA producer
+    // Ring order: K(0), then for every KV tile j: K(j+1) (if any), V(j). The MMA warp consumes
+    // and releases the slots in this same order.
     if (lane == 0) {
       const uint32_t qf = smem_u32(&ctl->q_full);
-      mbar_arrive_expect_tx(qf, kTileBytes);
-      tma_load_2d(q_tile, &tm_q, h * kD, tok0 + q_row0, qf);
-      tma_load_2d(q_tile + 16384, &tm_q, h * kD + 64, tok0 + q_row0, qf);
-      for (int j = 0; j < n_kv; ++j) {
-        const int s = j % kKvStages;
-        const uint32_t ph = (j / kKvStages) & 1;
-        if (!mbar_wait_bounded(smem_u32(&ctl->kv_empty[s]), ph ^ 1u, wctx, 31, s)) break;
-        const uint32_t full = smem_u32(&ctl->kv_full[s]);
-        const uint32_t kt = kv_tiles + s * 2 * kTileBytes, vt = kt + kTileBytes;
-        mbar_arrive_expect_tx(full, 2 * kTileBytes);
-        const int row = tok0 + j * kBKV;
-        tma_load_2d(kt, &tm_k, hk * kD, row, full);
-        tma_load_2d(kt + 16384, &tm_k, hk * kD + 64, row, full);
-        tma_load_2d(vt, &tm_v, hk * kD, row, full);
-        tma_load_2d(vt + 16384, &tm_v, hk * kD + 64, row, full);
+      mbar_arrive_expect_tx(qf, (tc1.n_kv > 0 ? 2 : 1) * kTileBytes);
+      tma_load_2d(q_tiles, &tm_q, tc0.h * kD, tok0 + tc0.row0, qf);
+      tma_load_2d(q_tiles + 16384, &tm_q, tc0.h * kD + 64, tok0 + tc0.row0, qf);
+      if (tc1.n_kv > 0) {
+        tma_load_2d(q_tiles + kTileBytes, &tm_q, tc1.h * kD, tok0 + tc1.row0, qf);
+        tma_load_2d(q_tiles + kTileBytes + 16384, &tm_q, tc1.h * kD + 64, tok0 + tc1.row0, qf);
+      }
+      int it = 0;
+      bool ok = true;
+      auto load = [&](const CUtensorMap* tm, int j) {
+        const int s = it % kSlots;
+        if (!mbar_wait_bounded(smem_u32(&ctl->ring_empty[s]), ((it / kSlots) & 1) ^ 1u, wctx, 31, s)) {
+          ok = false;
+          return;
+        }
+        const uint32_t full = smem_u32(&ctl->ring_full[s]);
+        const uint32_t dst = ring + s * kTileBytes;
+        mbar_arrive_expect_tx(full, kTileBytes);
+        tma_load_2d(dst, tm, hk * kD, tok0 + j * kBKV, full);
+        tma_load_2d(dst + 16384, tm, hk * kD + 64, tok0 + j * kBKV, full);
+        ++it;
+      };
+      if (n_max > 0) load(&tm_k, 0);
+      for (int j = 0; j < n_max && ok; ++j) {
+        if (j + 1 < n_max) load(&tm_k, j + 1);
+        if (ok) load(&tm_v, j);
       }
     }
   } else if (warp == kSoftThreads / 32 + 1) {
     // ------------------------------------------------------------------ MMA issuer
+    // Per KV tile j and query tile t: O_t += P_t(j) V(j), then S_t(j+1) = Q_t K(j+1). The P V
+    // product is issued first because P_t(j) lives in the S_t columns that the next Q K product
+    // overwrites; the tensor core executes the two in issue order.
     if (lane == 0) {
       const uint32_t idesc_s = umma_idesc_bf16_f32(kBQ, kBKV);
       const uint32_t idesc_o = umma_idesc_bf16_f32(kBQ, kD) | (1u << 16);  // B (V) is MN-major
       bool ok = mbar_wait_bounded(smem_u32(&ctl->q_full), 0, wctx, 32, 0);
-      auto issue_s = [&](int j) -> bool {
-        const int s = j % kKvStages, sb = j & 1;
-        if (!mbar_wait_bounded(smem_u32(&ctl->kv_full[s]), (j / kKvStages) & 1, wctx, 33, s)) return false;
-        if (!mbar_wait_bounded(smem_u32(&ctl->s_empty[sb]), ((j >> 1) & 1) ^ 1u, wctx, 34, sb)) return false;
-        tc_fence_after_sync();
-        const uint32_t kt = kv_tiles + s * 2 * kTileBytes;
+      int it = 0;
+      auto take = [&](uint32_t& tile_addr, int& slot) {
+        slot = it % kSlots;
+        if (!mbar_wait_bounded(smem_u32(&ctl->ring_full[slot]), (it / kSlots) & 1, wctx, 33, slot)) ok = false;
+        tile_addr = ring + slot * kTileBytes;
+        ++it;
+      };
+      auto issue_s = [&](int t, uint32_t kt) {
 #pragma unroll
         for (int kk = 0; kk < kD / 16; ++kk)
-          umma_bf16<1>(tmem_s + sb * 128, desc_kmajor(q_tile, kk), desc_kmajor(kt, kk), idesc_s, kk > 0 ? 1u : 0u);
-        umma_commit<1>(smem_u32(&ctl->s_full[sb]));
-        return true;
+          umma_bf16<1>(tmem_base + t * 128, desc_kmajor(q_tiles + t * kTileBytes, kk), desc_kmajor(kt, kk), idesc_s,
+                       kk > 0 ? 1u : 0u);
+        umma_commit<1>(smem_u32(&ctl->s_full[t]));
       };
-      if (ok && n_kv > 0) ok = issue_s(0);
-      for (int j = 0; j < n_kv && ok; ++j) {
-        if (j + 1 < n_kv) ok = issue_s(j + 1);
+      uint32_t kt = 0, vt = 0;
+      int kslot = 0, vslot = 0;
+      if (ok && n_max > 0) {
+        take(kt, kslot);
+        if (ok) {
+          tc_fence_after_sync();
+          for (int t = 0; t < kTiles; ++t)
+            if ((t == 0 ? tc0.n_kv : tc1.n_kv) > 0) issue_s(t, kt);
+          umma_commit<1>(smem_u32(&ctl->ring_empty[kslot]));
+        }
+      }
+      for (int j = 0; j < n_max && ok; ++j) {
+        const bool has_next = j + 1 < n_max;
+        if (has_next) take(kt, kslot);
+        if (ok) take(vt, vslot);
         if (!ok) break;
-        const int s = j % kKvStages;
-        ok = mbar_wait_bounded(smem_u32(&ctl->p_full), j & 1, wctx, 35, j);
-        if (!ok) break;
-        tc_fence_after_sync();
-        const uint32_t vt = kv_tiles + s * 2 * kTileBytes + kTileBytes;
+        for (int t = 0; t < kTiles && ok; ++t) {
+          const int n_t = t == 0 ? tc0.n_kv : tc1.n_kv;
+          if (j >= n_t) continue;
+          ok = mbar_wait_bounded(smem_u32(&ctl->p_full[t]), j & 1, wctx, 35, t);
+          if (!ok) break;
+          tc_fence_after_sync();
 #pragma unroll
-        for (int kk = 0; kk < kBKV / 16; ++kk)
-          umma_bf16<1>(tmem_o, desc_kmajor(p_tile, kk), desc_mnmajor(vt, kk), idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
-        umma_commit<1>(smem_u32(&ctl->p_empty));      // P tile reusable, O up to date
-        umma_commit<1>(smem_u32(&ctl->kv_empty[s]));
-        if (j + 1 == n_kv) umma_commit<1>(smem_u32(&ctl->o_full));
+          for (int kk = 0; kk < kBKV / 16; ++kk)
+            umma_bf16_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + kk * 8, desc_mnmajor(vt, kk), idesc_o,
+                         (j > 0 || kk > 0) ? 1u : 0u);
+          umma_commit<1>(smem_u32(&ctl->pv_done[t]));
+          if (j + 1 < n_t) issue_s(t, kt);
+        }
+        if (!ok) break;
+        if (has_next) umma_commit<1>(smem_u32(&ctl->ring_empty[kslot]));
+        umma_commit<1>(smem_u32(&ctl->ring_empty[vslot]));
       }
     }
   } else {
     // ------------------------------------------------------------------ softmax + output
-    // Thread (row, part) owns 32 columns of query row `row`: four threads per row, so every
-    // scheduler interleaves four warps. Every iteration executes exactly one named barrier
-    // whatever happened before it, and the decision to stop is taken from the shared abort
-    // flag after that barrier, so no thread is left behind.
-    constexpr int kCols = kBKV / kSplit;    // columns per thread
-    constexpr int kLd = kCols / 32;         // tcgen05.ld groups per thread
-    const int tid = threadIdx.x;
-    const int row = tid & 127;              // query row inside the tile == TMEM lane
-    const int part = tid >> 7;              // which kCols columns
-    const int q_pos = q_row0 + row;
+    // Warps 0-3 own query tile 0, warps 4-7 tile 1; thread `row` owns one query row == one TMEM
+    // lane. No thread waits for another softmax thread, so a warp that gives up just stops.
+    const int t = warp >> 2;
+    const TileCoord tc = t == 0 ? tc0 : tc1;
+    const int row = threadIdx.x & 127;
+    const int q_pos = tc.row0 + row;
     const float c = p.scale * kLog2e;
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t tmem_s = tmem_base + lane_base + t * 128;          // S_t, and P_t in its first 64 columns
+    const uint32_t tmem_o = tmem_base + lane_base + 256 + t * 128;
     float m = -CUDART_INF_F;                // reference maximum of the row (may lag the true one by < 2^8)
-    float l = 0.f;                          // this thread's part of the row sum
+    float l = 0.f;
     bool ok = true;
 
-    for (int j = 0; j < n_kv; ++j) {
-      const int sb = j & 1;
-      uint32_t sv[kLd][32];
-      float mx = -CUDART_INF_F;
-      const int kv0 = j * kBKV + part * kCols;
+    for (int j = 0; j < tc.n_kv && ok; ++j) {
+      uint32_t sv[4][32];
+      const int kv0 = j * kBKV;
       const int limit = (p.causal ? min(q_pos, p.seq_len - 1) : p.seq_len - 1) - kv0;  // last allowed column
-      const bool full_tile = limit >= kCols - 1;
-      if (ok) {
-        const bool mine = mbar_wait_bounded(smem_u32(&ctl->s_full[sb]), (j >> 1) & 1, wctx, 38, sb);
+      const bool full_tile = limit >= kBKV - 1;
+      {
+        const bool mine = mbar_wait_bounded(smem_u32(&ctl->s_full[t]), j & 1, wctx, 38, t);
         ok = __all_sync(0xffffffffu, mine) != 0;
+        if (!ok) break;
       }
-      if (ok) {
-        tc_fence_after_sync();
+      tc_fence_after_sync();
 #pragma unroll
-        for (int g = 0; g < kLd; ++g) tmem_ld_32x32(tmem_s + lane_base + sb * 128 + part * kCols + g * 32, sv[g]);
+      for (int g = 0; g < 4; ++g) tmem_ld_32x32(tmem_s + g * 32, sv[g]);
 #pragma unroll
-        for (int g = 0; g < kLd; ++g) tmem_ld_wait_dep(sv[g]);
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&ctl->s_empty[sb]));  // S buffer free for tile j + 2
-        float a0 = -CUDART_INF_F, a1 = -CUDART_INF_F;
+      for (int g = 0; g < 4; ++g) tmem_ld_wait_dep(sv[g]);
+      float a0 = -CUDART_INF_F, a1 = -CUDART_INF_F, a2 = -CUDART_INF_F, a3 = -CUDART_INF_F;
+      if (full_tile) {
 #pragma unroll
-        for (int g = 0; g < kLd; ++g) {
-          if (full_tile) {
+        for (int g = 0; g < 4; ++g) {
 #pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-              a0 = fmaxf(a0, __uint_as_float(sv[g][i]));
-              a1 = fmaxf(a1, __uint_as_float(sv[g][i + 1]));
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              a0 = fmaxf(a0, (g * 32 + i <= limit) ? __uint_as_float(sv[g][i]) : -CUDART_INF_F);
+          for (int i = 0; i < 32; i += 4) {
+            a0 = fmaxf(a0, __uint_as_float(sv[g][i]));
+            a1 = fmaxf(a1, __uint_as_float(sv[g][i + 1]));
+            a2 = fmaxf(a2, __uint_as_float(sv[g][i + 2]));
+            a3 = fmaxf(a3, __uint_as_float(sv[g][i + 3]));
           }
         }
-        mx = fmaxf(a0, a1);
-      }
-      ctl->half_max[sb][part][row] = mx;
-      asm volatile("bar.sync 1, %0;" ::"n"(kSoftThreads) : "memory");
-      if (ctl->abort_flag) ok = false;
-      if (!ok) continue;
+      } else {
 #pragma unroll
-      for (int q = 0; q < kSplit; ++q) mx = fmaxf(mx, ctl->half_max[sb][q][row]);
+        for (int g = 0; g < 4; ++g) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            if (g * 32 + i > limit) sv[g][i] = __float_as_uint(-CUDART_INF_F);
+            a0 = fmaxf(a0, __uint_as_float(sv[g][i]));
+          }
+        }
+      }
+      const float mx = fmaxf(fmaxf(a0, a1), fmaxf(a2, a3));
       // move the reference maximum only on the first tile or when it would grow by more than
       // 2^8 in the exponent; otherwise probabilities are taken relative to the old reference
       float alpha = 1.f;
@@ -251,87 +303,68 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       const float m_ref = (m == -CUDART_INF_F) ? 0.f : m;
       const float neg = __fmul_rn(-m_ref, c);
 
-      // the P tile (and O) are ours once the previous P V product has completed
-      {
-        const bool mine2 = mbar_wait_bounded(smem_u32(&ctl->p_empty), (j & 1) ^ 1u, wctx, 39, j);
-        ok = __all_sync(0xffffffffu, mine2) != 0;
-        if (!ok) continue;
-      }
       if (__any_sync(0xffffffffu, rescale)) {
-        // rare: bring this thread's columns of O in TMEM to the new reference
+        // rare: bring this row of O in TMEM to the new reference, once the P V product of the
+        // previous KV tile has landed
+        const bool mine = mbar_wait_bounded(smem_u32(&ctl->pv_done[t]), (j - 1) & 1, wctx, 39, t);
+        ok = __all_sync(0xffffffffu, mine) != 0;
+        if (!ok) break;
         tc_fence_after_sync();
         uint32_t v[32];
 #pragma unroll
-        for (int g = 0; g < kLd; ++g) {
+        for (int g = 0; g < 4; ++g) {
           __syncwarp();
-          tmem_ld_32x32(tmem_o + lane_base + part * kCols + g * 32, v);
+          tmem_ld_32x32(tmem_o + g * 32, v);
           tmem_ld_wait_dep(v);
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__fmul_rn(__uint_as_float(v[i]), alpha));
-          tmem_st_32x32(tmem_o + lane_base + part * kCols + g * 32, v);
+          tmem_st_32x32(tmem_o + g * 32, v);
         }
-        tmem_st_wait();
       }
       float ls0 = 0.f, ls1 = 0.f, ls2 = 0.f, ls3 = 0.f;
 #pragma unroll
-      for (int g = 0; g < kLd; ++g) {
-        float e[32];
-        if (full_tile) {
+      for (int hblk = 0; hblk < 2; ++hblk) {
+        uint32_t w[32];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) e[i] = ex2_approx(__fmaf_rn(__uint_as_float(sv[g][i]), c, neg));
-        } else {
+        for (int g2 = 0; g2 < 2; ++g2) {
+          const int g = hblk * 2 + g2;
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            e[i] = (g * 32 + i <= limit) ? ex2_approx(__fmaf_rn(__uint_as_float(sv[g][i]), c, neg)) : 0.f;
+          for (int i = 0; i < 32; i += 4) {
+            // masked columns hold -inf: ex2(-inf) = 0
+            const float e0 = ex2_approx(__fmaf_rn(__uint_as_float(sv[g][i]), c, neg));
+            const float e1 = ex2_approx(__fmaf_rn(__uint_as_float(sv[g][i + 1]), c, neg));
+            const float e2 = ex2_approx(__fmaf_rn(__uint_as_float(sv[g][i + 2]), c, neg));
+            const float e3 = ex2_approx(__fmaf_rn(__uint_as_float(sv[g][i + 3]), c, neg));
+            ls0 = __fadd_rn(ls0, e0);
+            ls1 = __fadd_rn(ls1, e1);
+            ls2 = __fadd_rn(ls2, e2);
+            ls3 = __fadd_rn(ls3, e3);
+            w[g2 * 16 + (i >> 1)] = pack_bf16(e0, e1);
+            w[g2 * 16 + (i >> 1) + 1] = pack_bf16(e2, e3);
+          }
         }
-#pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-          ls0 = __fadd_rn(ls0, e[i]);
-          ls1 = __fadd_rn(ls1, e[i + 1]);
-          ls2 = __fadd_rn(ls2, e[i + 2]);
-          ls3 = __fadd_rn(ls3, e[i + 3]);
-        }
-        // columns col .. col+31 of the row: box (col >> 6), 16-byte chunks ((col >> 5) & 1) * 4 + 0..3
-        const int col = part * kCols + g * 32;
-        uint8_t* rowp = p_ptr + (col >> 6) * 16384 + row * 128;
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          const int phys = (((col >> 5) & 1) * 4 + ch) ^ (row & 7);
-          uint4 w;
-          w.x = pack_bf16(e[ch * 8 + 0], e[ch * 8 + 1]);
-          w.y = pack_bf16(e[ch * 8 + 2], e[ch * 8 + 3]);
-          w.z = pack_bf16(e[ch * 8 + 4], e[ch * 8 + 5]);
-          w.w = pack_bf16(e[ch * 8 + 6], e[ch * 8 + 7]);
-          *reinterpret_cast<uint4*>(rowp + phys * 16) = w;
-        }
+        tmem_st_32x32(tmem_s + hblk * 32, w);   // P columns [64 hblk, 64 hblk + 64) as 32 packed words
       }
       l = __fmaf_rn(l, alpha, __fadd_rn(__fadd_rn(ls0, ls1), __fadd_rn(ls2, ls3)));
+      tmem_st_wait();
       tc_fence_before_sync();
-      fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&ctl->p_full));
+      if (lane == 0) mbar_arrive(smem_u32(&ctl->p_full[t]));
     }
 
-    // combine the parts of the row sum (fixed order)
-    ctl->half_sum[part][row] = l;
-    asm volatile("bar.sync 1, %0;" ::"n"(kSoftThreads) : "memory");
-    if (ctl->abort_flag) ok = false;
-    float l_total = ctl->half_sum[0][row];
-#pragma unroll
-    for (int q = 1; q < kSplit; ++q) l_total = __fadd_rn(l_total, ctl->half_sum[q][row]);
-    if (ok && n_kv > 0) {
-      const bool mine = mbar_wait_bounded(smem_u32(&ctl->o_full), 0, wctx, 37, 0);
+    if (ok && tc.n_kv > 0) {
+      const bool mine = mbar_wait_bounded(smem_u32(&ctl->pv_done[t]), (tc.n_kv - 1) & 1, wctx, 37, t);
       ok = __all_sync(0xffffffffu, mine) != 0;
     }
-    if (ok) {
+    if (ok && tc.n_kv > 0) {
       tc_fence_after_sync();
-      const float inv = l_total > 0.f ? __fdiv_rn(1.f, l_total) : 0.f;
-      __nv_bfloat16* dst = p.out + static_cast<long long>(tok0 + q_pos) * p.out_stride + h * kD + part * kCols;
+      const float inv = l > 0.f ? __fdiv_rn(1.f, l) : 0.f;
+      __nv_bfloat16* dst = p.out + static_cast<long long>(tok0 + q_pos) * p.out_stride + tc.h * kD;
       uint32_t v[32];
 #pragma unroll
-      for (int g = 0; g < kLd; ++g) {
+      for (int g = 0; g < 4; ++g) {
         __syncwarp();
-        tmem_ld_32x32(tmem_o + lane_base + part * kCols + g * 32, v);
+        tmem_ld_32x32(tmem_o + g * 32, v);
         tmem_ld_wait_dep(v);
         if (q_pos < p.seq_len) {
 #pragma unroll
@@ -345,9 +378,9 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           }
         }
       }
-      if (p.lse && part == 0 && q_pos < p.seq_len)
-        p.lse[(static_cast<long long>(b) * p.hq + h) * p.seq_len + q_pos] =
-            __fmaf_rn(lg2_approx(l_total), 0.6931471805599453f, __fmul_rn(m, p.scale));
+      if (p.lse && q_pos < p.seq_len)
+        p.lse[(static_cast<long long>(b) * p.hq + tc.h) * p.seq_len + q_pos] =
+            __fmaf_rn(lg2_approx(l), 0.6931471805599453f, __fmul_rn(m, p.scale));
     }
   }
 
@@ -404,7 +437,9 @@ extern "C" int ka_attention_fwd(const void* q, long long q_stride, const void* k
   p.status = status;
   p.timeout_ns = timeout_ns;
   const int n_qt = (seq_len + kBQ - 1) / kBQ;
-  const unsigned grid = static_cast<unsigned>(batch) * hq * n_qt;
+  p.pair_heads = ((hq / hkv) % 2 == 0) ? 1 : 0;
+  const unsigned grid = p.pair_heads ? static_cast<unsigned>(batch) * (hq / 2) * n_qt
+                                     : static_cast<unsigned>(batch) * hq * ((n_qt + 1) / 2);
   attention_fwd_kernel<<<grid, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(tq, tk, tv, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }

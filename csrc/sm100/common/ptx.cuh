@@ -211,6 +211,20 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint
   }
 }
 
+// A operand in TMEM (128 lanes x K/2 columns, two bf16 per 32-bit column), B through a shared
+// memory descriptor: the form the second GEMM of attention uses for P V.
+__device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+      "}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // Make `bar` (in this CTA for G == 1; at the same offset in both CTAs of the pair for
 // G == 2) receive one arrival once every MMA issued so far by this thread has completed.
 template <int G>

@@ -43,6 +43,7 @@ constexpr float kLog2e = 1.4426950408889634f;
 
 struct Control {
   uint64_t q_full;
+  uint64_t q_empty;   // every S product of the current item has completed: the Q tiles may be replaced
   uint64_t ring_full[kSlots];
   uint64_t ring_empty[kSlots];
   uint64_t s_full[kTiles];    // S_t of the next KV tile is in TMEM
@@ -63,6 +64,15 @@ struct AttnParams {
   int* status;
   unsigned long long timeout_ns;
 };
+
+#ifdef KA_ATTN_TIMING
+__device__ unsigned long long ka_attn_dbg[16];
+#define KA_T(var) const long long var = clock64()
+#define KA_ACC(slot, val) do { if ((threadIdx.x & 127) == 0) atomicAdd(&ka_attn_dbg[slot], static_cast<unsigned long long>(val)); } while (0)
+#else
+#define KA_T(var)
+#define KA_ACC(slot, val)
+#endif
 
 struct TileCoord {
   int h;        // query head
@@ -91,6 +101,26 @@ __device__ __forceinline__ TileCoord tile_coord(const AttnParams& p, int unit, i
   return c;
 }
 
+struct Item {
+  TileCoord tc[kTiles];
+  int b, hk, tok0, n_max;
+};
+
+__device__ __forceinline__ Item decode_item(const AttnParams& p, int item, int n_units, int n_head_units, int per_unit,
+                                            int group) {
+  Item w;
+  const int unit = n_units - 1 - item / per_unit;     // heavy (late) rows first
+  const int bh = item % per_unit;
+  const int head_unit = bh % n_head_units;
+  w.b = bh / n_head_units;
+  w.tc[0] = tile_coord(p, unit, head_unit, 0);
+  w.tc[1] = tile_coord(p, unit, head_unit, 1);
+  w.hk = w.tc[0].h / group;
+  w.tok0 = w.b * p.seq_len;
+  w.n_max = max(w.tc[0].n_kv, w.tc[1].n_kv);
+  return w;
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
 attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ AttnParams p) {
@@ -103,24 +133,22 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   Control* ctl = reinterpret_cast<Control*>(smem + (kTiles + kSlots) * kTileBytes);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // work decomposition: x = row unit (heavy, late rows first), then head unit, then sequence
+  // Work items: (row unit, head unit, sequence). Items are numbered heaviest row unit first
+  // and dealt round-robin to the resident CTAs, which walk their items in a loop; all
+  // pipeline counters run on across items, so the loads and the first S products of the next
+  // item overlap the last softmax tiles and the output pass of the current one.
   const int n_qt = (p.seq_len + kBQ - 1) / kBQ;
   const int n_units = p.pair_heads ? n_qt : (n_qt + 1) / 2;
   const int n_head_units = p.pair_heads ? p.hq / 2 : p.hq;
-  const int unit = n_units - 1 - static_cast<int>(blockIdx.x % n_units);
-  const int bh = blockIdx.x / n_units;
-  const int head_unit = bh % n_head_units;
-  const int b = bh / n_head_units;
-  const TileCoord tc0 = tile_coord(p, unit, head_unit, 0);
-  const TileCoord tc1 = tile_coord(p, unit, head_unit, 1);
-  const int hk = tc0.h / (p.hq / p.hkv);
-  const int tok0 = b * p.seq_len;                    // first token of the sequence
-  const int n_max = max(tc0.n_kv, tc1.n_kv);
+  const int per_unit = n_head_units * p.batch;
+  const int n_items = n_units * per_unit;
+  const int group = p.hq / p.hkv;
 
   WaitCtx wctx{&ctl->abort_flag, p.status, p.timeout_ns};
 
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(&ctl->q_full), 1);
+    mbar_init(smem_u32(&ctl->q_empty), 1);
     for (int s = 0; s < kSlots; ++s) {
       mbar_init(smem_u32(&ctl->ring_full[s]), 1);
       mbar_init(smem_u32(&ctl->ring_empty[s]), 1);
@@ -148,32 +176,36 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     // and releases the slots in this same order.
     if (lane == 0) {
       const uint32_t qf = smem_u32(&ctl->q_full);
-      mbar_arrive_expect_tx(qf, (tc1.n_kv > 0 ? 2 : 1) * kTileBytes);
-      tma_load_2d(q_tiles, &tm_q, tc0.h * kD, tok0 + tc0.row0, qf);
-      tma_load_2d(q_tiles + 16384, &tm_q, tc0.h * kD + 64, tok0 + tc0.row0, qf);
-      if (tc1.n_kv > 0) {
-        tma_load_2d(q_tiles + kTileBytes, &tm_q, tc1.h * kD, tok0 + tc1.row0, qf);
-        tma_load_2d(q_tiles + kTileBytes + 16384, &tm_q, tc1.h * kD + 64, tok0 + tc1.row0, qf);
-      }
-      int it = 0;
+      int it = 0, qi = 0;
       bool ok = true;
-      auto load = [&](const CUtensorMap* tm, int j) {
-        const int s = it % kSlots;
-        if (!mbar_wait_bounded(smem_u32(&ctl->ring_empty[s]), ((it / kSlots) & 1) ^ 1u, wctx, 31, s)) {
-          ok = false;
-          return;
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++qi) {
+        const Item w = decode_item(p, item, n_units, n_head_units, per_unit, group);
+        if (!mbar_wait_bounded(smem_u32(&ctl->q_empty), (qi & 1) ^ 1u, wctx, 30, item)) break;
+        mbar_arrive_expect_tx(qf, (w.tc[1].n_kv > 0 ? 2 : 1) * kTileBytes);
+        tma_load_2d(q_tiles, &tm_q, w.tc[0].h * kD, w.tok0 + w.tc[0].row0, qf);
+        tma_load_2d(q_tiles + 16384, &tm_q, w.tc[0].h * kD + 64, w.tok0 + w.tc[0].row0, qf);
+        if (w.tc[1].n_kv > 0) {
+          tma_load_2d(q_tiles + kTileBytes, &tm_q, w.tc[1].h * kD, w.tok0 + w.tc[1].row0, qf);
+          tma_load_2d(q_tiles + kTileBytes + 16384, &tm_q, w.tc[1].h * kD + 64, w.tok0 + w.tc[1].row0, qf);
         }
-        const uint32_t full = smem_u32(&ctl->ring_full[s]);
-        const uint32_t dst = ring + s * kTileBytes;
-        mbar_arrive_expect_tx(full, kTileBytes);
-        tma_load_2d(dst, tm, hk * kD, tok0 + j * kBKV, full);
-        tma_load_2d(dst + 16384, tm, hk * kD + 64, tok0 + j * kBKV, full);
-        ++it;
-      };
-      if (n_max > 0) load(&tm_k, 0);
-      for (int j = 0; j < n_max && ok; ++j) {
-        if (j + 1 < n_max) load(&tm_k, j + 1);
-        if (ok) load(&tm_v, j);
+        auto load = [&](const CUtensorMap* tm, int j) {
+          const int s = it % kSlots;
+          if (!mbar_wait_bounded(smem_u32(&ctl->ring_empty[s]), ((it / kSlots) & 1) ^ 1u, wctx, 31, s)) {
+            ok = false;
+            return;
+          }
+          const uint32_t full = smem_u32(&ctl->ring_full[s]);
+          const uint32_t dst = ring + s * kTileBytes;
+          mbar_arrive_expect_tx(full, kTileBytes);
+          tma_load_2d(dst, tm, w.hk * kD, w.tok0 + j * kBKV, full);
+          tma_load_2d(dst + 16384, tm, w.hk * kD + 64, w.tok0 + j * kBKV, full);
+          ++it;
+        };
+        load(&tm_k, 0);
+        for (int j = 0; j < w.n_max && ok; ++j) {
+          if (j + 1 < w.n_max) load(&tm_k, j + 1);
+          if (ok) load(&tm_v, j);
+        }
       }
     }
   } else if (warp == kSoftThreads / 32 + 1) {
@@ -184,8 +216,9 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     if (lane == 0) {
       const uint32_t idesc_s = umma_idesc_bf16_f32(kBQ, kBKV);
       const uint32_t idesc_o = umma_idesc_bf16_f32(kBQ, kD) | (1u << 16);  // B (V) is MN-major
-      bool ok = mbar_wait_bounded(smem_u32(&ctl->q_full), 0, wctx, 32, 0);
-      int it = 0;
+      int it = 0, qi = 0;
+      int cnt[kTiles] = {0, 0};     // tile-iterations so far: the phase of p_full / s_full / pv_done
+      bool ok = true;
       auto take = [&](uint32_t& tile_addr, int& slot) {
         slot = it % kSlots;
         if (!mbar_wait_bounded(smem_u32(&ctl->ring_full[slot]), (it / kSlots) & 1, wctx, 33, slot)) ok = false;
@@ -199,38 +232,44 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                        kk > 0 ? 1u : 0u);
         umma_commit<1>(smem_u32(&ctl->s_full[t]));
       };
-      uint32_t kt = 0, vt = 0;
-      int kslot = 0, vslot = 0;
-      if (ok && n_max > 0) {
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++qi) {
+        const Item w = decode_item(p, item, n_units, n_head_units, per_unit, group);
+        ok = mbar_wait_bounded(smem_u32(&ctl->q_full), qi & 1, wctx, 32, item);
+        if (!ok) break;
+        uint32_t kt = 0, vt = 0;
+        int kslot = 0, vslot = 0;
         take(kt, kslot);
-        if (ok) {
-          tc_fence_after_sync();
-          for (int t = 0; t < kTiles; ++t)
-            if ((t == 0 ? tc0.n_kv : tc1.n_kv) > 0) issue_s(t, kt);
-          umma_commit<1>(smem_u32(&ctl->ring_empty[kslot]));
-        }
-      }
-      for (int j = 0; j < n_max && ok; ++j) {
-        const bool has_next = j + 1 < n_max;
-        if (has_next) take(kt, kslot);
-        if (ok) take(vt, vslot);
         if (!ok) break;
-        for (int t = 0; t < kTiles && ok; ++t) {
-          const int n_t = t == 0 ? tc0.n_kv : tc1.n_kv;
-          if (j >= n_t) continue;
-          ok = mbar_wait_bounded(smem_u32(&ctl->p_full[t]), j & 1, wctx, 35, t);
-          if (!ok) break;
-          tc_fence_after_sync();
+        tc_fence_after_sync();
 #pragma unroll
-          for (int kk = 0; kk < kBKV / 16; ++kk)
-            umma_bf16_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + kk * 8, desc_mnmajor(vt, kk), idesc_o,
-                         (j > 0 || kk > 0) ? 1u : 0u);
-          umma_commit<1>(smem_u32(&ctl->pv_done[t]));
-          if (j + 1 < n_t) issue_s(t, kt);
+        for (int t = 0; t < kTiles; ++t)
+          if (w.tc[t].n_kv > 0) issue_s(t, kt);
+        umma_commit<1>(smem_u32(&ctl->ring_empty[kslot]));
+        if (w.n_max == 1) umma_commit<1>(smem_u32(&ctl->q_empty));
+        for (int j = 0; j < w.n_max && ok; ++j) {
+          const bool has_next = j + 1 < w.n_max;
+          if (has_next) take(kt, kslot);
+          if (ok) take(vt, vslot);
+          if (!ok) break;
+#pragma unroll
+          for (int t = 0; t < kTiles; ++t) {
+            if (!ok || j >= w.tc[t].n_kv) continue;
+            ok = mbar_wait_bounded(smem_u32(&ctl->p_full[t]), cnt[t] & 1, wctx, 35, t);
+            if (!ok) continue;
+            ++cnt[t];
+            tc_fence_after_sync();
+#pragma unroll
+            for (int kk = 0; kk < kBKV / 16; ++kk)
+              umma_bf16_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + kk * 8, desc_mnmajor(vt, kk), idesc_o,
+                           (j > 0 || kk > 0) ? 1u : 0u);
+            umma_commit<1>(smem_u32(&ctl->pv_done[t]));
+            if (j + 1 < w.tc[t].n_kv) issue_s(t, kt);
+          }
+          if (!ok) break;
+          if (has_next) umma_commit<1>(smem_u32(&ctl->ring_empty[kslot]));
+          umma_commit<1>(smem_u32(&ctl->ring_empty[vslot]));
+          if (j + 2 == w.n_max) umma_commit<1>(smem_u32(&ctl->q_empty));   // the last S products are issued
         }
-        if (!ok) break;
-        if (has_next) umma_commit<1>(smem_u32(&ctl->ring_empty[kslot]));
-        umma_commit<1>(smem_u32(&ctl->ring_empty[vslot]));
       }
     }
   } else {
@@ -238,54 +277,71 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     // Warps 0-3 own query tile 0, warps 4-7 tile 1; thread `row` owns one query row == one TMEM
     // lane. No thread waits for another softmax thread, so a warp that gives up just stops.
     const int t = warp >> 2;
-    const TileCoord tc = t == 0 ? tc0 : tc1;
     const int row = threadIdx.x & 127;
-    const int q_pos = tc.row0 + row;
     const float c = p.scale * kLog2e;
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tmem_s = tmem_base + lane_base + t * 128;          // S_t, and P_t in its first 64 columns
     const uint32_t tmem_o = tmem_base + lane_base + 256 + t * 128;
-    float m = -CUDART_INF_F;                // reference maximum of the row (may lag the true one by < 2^8)
-    float l = 0.f;
+    int cnt = 0;                            // tile-iterations of this tile so far (barrier phases)
     bool ok = true;
 
-    for (int j = 0; j < tc.n_kv && ok; ++j) {
-      uint32_t sv[4][32];
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+    const Item wi = decode_item(p, item, n_units, n_head_units, per_unit, group);
+    const TileCoord tc = wi.tc[t];
+    const int b = wi.b, tok0 = wi.tok0;
+    const int q_pos = tc.row0 + row;
+    float m = -CUDART_INF_F;                // reference maximum of the row (may lag the true one by < 2^8)
+    float l = 0.f;
+
+    for (int j = 0; j < tc.n_kv && ok; ++j, ++cnt) {
+      uint32_t va[32], vb[32];     // two 32-column chunks of the S row in flight
       const int kv0 = j * kBKV;
       const int limit = (p.causal ? min(q_pos, p.seq_len - 1) : p.seq_len - 1) - kv0;  // last allowed column
       const bool full_tile = limit >= kBKV - 1;
+      KA_T(t_a);
       {
-        const bool mine = mbar_wait_bounded(smem_u32(&ctl->s_full[t]), j & 1, wctx, 38, t);
+        const bool mine = mbar_wait_bounded(smem_u32(&ctl->s_full[t]), cnt & 1, wctx, 38, t);
         ok = __all_sync(0xffffffffu, mine) != 0;
         if (!ok) break;
       }
+      KA_T(t_b);
       tc_fence_after_sync();
+      // Pass 1: the row maximum. Chunks 2 and 3 first, then 0 and 1, which stay in registers
+      // for the start of pass 2 (the S row is read from TMEM one and a half times, never
+      // held whole: 128 live values would not fit the register budget of this kernel).
+      auto mask_chunk = [&](uint32_t (&v)[32], int g) {
+        if (!full_tile) {
 #pragma unroll
-      for (int g = 0; g < 4; ++g) tmem_ld_32x32(tmem_s + g * 32, sv[g]);
-#pragma unroll
-      for (int g = 0; g < 4; ++g) tmem_ld_wait_dep(sv[g]);
+          for (int i = 0; i < 32; ++i)
+            if (g * 32 + i > limit) v[i] = __float_as_uint(-CUDART_INF_F);
+        }
+      };
       float a0 = -CUDART_INF_F, a1 = -CUDART_INF_F, a2 = -CUDART_INF_F, a3 = -CUDART_INF_F;
-      if (full_tile) {
+      auto max_chunk = [&](const uint32_t (&v)[32]) {
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-#pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            a0 = fmaxf(a0, __uint_as_float(sv[g][i]));
-            a1 = fmaxf(a1, __uint_as_float(sv[g][i + 1]));
-            a2 = fmaxf(a2, __uint_as_float(sv[g][i + 2]));
-            a3 = fmaxf(a3, __uint_as_float(sv[g][i + 3]));
-          }
+        for (int i = 0; i < 32; i += 4) {
+          a0 = fmaxf(a0, __uint_as_float(v[i]));
+          a1 = fmaxf(a1, __uint_as_float(v[i + 1]));
+          a2 = fmaxf(a2, __uint_as_float(v[i + 2]));
+          a3 = fmaxf(a3, __uint_as_float(v[i + 3]));
         }
-      } else {
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            if (g * 32 + i > limit) sv[g][i] = __float_as_uint(-CUDART_INF_F);
-            a0 = fmaxf(a0, __uint_as_float(sv[g][i]));
-          }
-        }
-      }
+      };
+      tmem_ld_32x32(tmem_s + 64, va);
+      tmem_ld_32x32(tmem_s + 96, vb);
+      tmem_ld_wait_dep(va);
+      tmem_ld_wait_dep(vb);
+      mask_chunk(va, 2);
+      mask_chunk(vb, 3);
+      max_chunk(va);
+      max_chunk(vb);
+      tmem_ld_32x32(tmem_s, va);
+      tmem_ld_32x32(tmem_s + 32, vb);
+      tmem_ld_wait_dep(va);
+      tmem_ld_wait_dep(vb);
+      mask_chunk(va, 0);
+      mask_chunk(vb, 1);
+      max_chunk(va);
+      max_chunk(vb);
       const float mx = fmaxf(fmaxf(a0, a1), fmaxf(a2, a3));
       // move the reference maximum only on the first tile or when it would grow by more than
       // 2^8 in the exponent; otherwise probabilities are taken relative to the old reference
@@ -306,7 +362,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       if (__any_sync(0xffffffffu, rescale)) {
         // rare: bring this row of O in TMEM to the new reference, once the P V product of the
         // previous KV tile has landed
-        const bool mine = mbar_wait_bounded(smem_u32(&ctl->pv_done[t]), (j - 1) & 1, wctx, 39, t);
+        const bool mine = mbar_wait_bounded(smem_u32(&ctl->pv_done[t]), (cnt - 1) & 1, wctx, 39, t);
         ok = __all_sync(0xffffffffu, mine) != 0;
         if (!ok) break;
         tc_fence_after_sync();
@@ -321,39 +377,53 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           tmem_st_32x32(tmem_o + g * 32, v);
         }
       }
+      KA_T(t_c);
+      // Pass 2: probabilities, 32 columns at a time; masked columns hold -inf and give 0.
       float ls0 = 0.f, ls1 = 0.f, ls2 = 0.f, ls3 = 0.f;
+      uint32_t w[32];
+      auto exp_chunk = [&](const uint32_t (&v)[32], int half) {
 #pragma unroll
-      for (int hblk = 0; hblk < 2; ++hblk) {
-        uint32_t w[32];
-#pragma unroll
-        for (int g2 = 0; g2 < 2; ++g2) {
-          const int g = hblk * 2 + g2;
-#pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            // masked columns hold -inf: ex2(-inf) = 0
-            const float e0 = ex2_approx(__fmaf_rn(__uint_as_float(sv[g][i]), c, neg));
-            const float e1 = ex2_approx(__fmaf_rn(__uint_as_float(sv[g][i + 1]), c, neg));
-            const float e2 = ex2_approx(__fmaf_rn(__uint_as_float(sv[g][i + 2]), c, neg));
-            const float e3 = ex2_approx(__fmaf_rn(__uint_as_float(sv[g][i + 3]), c, neg));
-            ls0 = __fadd_rn(ls0, e0);
-            ls1 = __fadd_rn(ls1, e1);
-            ls2 = __fadd_rn(ls2, e2);
-            ls3 = __fadd_rn(ls3, e3);
-            w[g2 * 16 + (i >> 1)] = pack_bf16(e0, e1);
-            w[g2 * 16 + (i >> 1) + 1] = pack_bf16(e2, e3);
-          }
+        for (int i = 0; i < 32; i += 4) {
+          const float e0 = ex2_approx(__fmaf_rn(__uint_as_float(v[i]), c, neg));
+          const float e1 = ex2_approx(__fmaf_rn(__uint_as_float(v[i + 1]), c, neg));
+          const float e2 = ex2_approx(__fmaf_rn(__uint_as_float(v[i + 2]), c, neg));
+          const float e3 = ex2_approx(__fmaf_rn(__uint_as_float(v[i + 3]), c, neg));
+          ls0 = __fadd_rn(ls0, e0);
+          ls1 = __fadd_rn(ls1, e1);
+          ls2 = __fadd_rn(ls2, e2);
+          ls3 = __fadd_rn(ls3, e3);
+          w[half * 16 + (i >> 1)] = pack_bf16(e0, e1);
+          w[half * 16 + (i >> 1) + 1] = pack_bf16(e2, e3);
         }
-        tmem_st_32x32(tmem_s + hblk * 32, w);   // P columns [64 hblk, 64 hblk + 64) as 32 packed words
-      }
+      };
+      exp_chunk(va, 0);
+      tmem_ld_32x32(tmem_s + 64, va);        // chunk 2 on its way while chunk 1 is processed
+      exp_chunk(vb, 1);
+      tmem_st_32x32(tmem_s, w);              // P columns [0,64) as 32 packed words over S columns [0,32)
+      tmem_ld_wait_dep(va);
+      tmem_ld_32x32(tmem_s + 96, vb);
+      mask_chunk(va, 2);
+      exp_chunk(va, 0);
+      tmem_ld_wait_dep(vb);
+      mask_chunk(vb, 3);
+      exp_chunk(vb, 1);
+      tmem_st_32x32(tmem_s + 32, w);         // P columns [64,128) over S columns [32,64)
       l = __fmaf_rn(l, alpha, __fadd_rn(__fadd_rn(ls0, ls1), __fadd_rn(ls2, ls3)));
+      KA_T(t_d);
       tmem_st_wait();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&ctl->p_full[t]));
+      KA_T(t_e);
+      KA_ACC(0, t_b - t_a);
+      KA_ACC(1, t_c - t_b);
+      KA_ACC(2, t_d - t_c);
+      KA_ACC(3, t_e - t_d);
+      KA_ACC(4, 1);
     }
 
     if (ok && tc.n_kv > 0) {
-      const bool mine = mbar_wait_bounded(smem_u32(&ctl->pv_done[t]), (tc.n_kv - 1) & 1, wctx, 37, t);
+      const bool mine = mbar_wait_bounded(smem_u32(&ctl->pv_done[t]), (cnt - 1) & 1, wctx, 37, t);
       ok = __all_sync(0xffffffffu, mine) != 0;
     }
     if (ok && tc.n_kv > 0) {
@@ -381,7 +451,11 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       if (p.lse && q_pos < p.seq_len)
         p.lse[(static_cast<long long>(b) * p.hq + tc.h) * p.seq_len + q_pos] =
             __fmaf_rn(lg2_approx(l), 0.6931471805599453f, __fmul_rn(m, p.scale));
+      // the O columns are read: order those reads before this warp's next arrival on p_full,
+      // after which the MMA warp overwrites O
+      tc_fence_before_sync();
     }
+    }  // items
   }
 
   if (ctl->abort_flag) drain_in_flight();
@@ -400,6 +474,18 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 // q: [B*L, Hq*128] view with `q_stride` elements between tokens; k, v: [B*L, Hkv*128] views
 // (strides k_stride, v_stride); out: [B*L, Hq*128] with out_stride; lse: [B, Hq, L] fp32 or
 // null. All bf16, 16-byte aligned, strides multiples of 8.
+#ifdef KA_ATTN_TIMING
+extern "C" int ka_attention_dbg_read(unsigned long long* host_out, int reset) {
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(host_out, ka::ka_attn_dbg, sizeof(unsigned long long) * 16);
+  if (reset) {
+    unsigned long long z[16] = {};
+    cudaMemcpyToSymbol(ka::ka_attn_dbg, z, sizeof(z));
+  }
+  return 0;
+}
+#endif
+
 extern "C" int ka_attention_fwd(const void* q, long long q_stride, const void* k, long long k_stride, const void* v,
                                 long long v_stride, void* out, long long out_stride, float* lse, int batch,
                                 int seq_len, int hq, int hkv, int head_dim, float scale, int causal, int* status,
@@ -438,8 +524,12 @@ extern "C" int ka_attention_fwd(const void* q, long long q_stride, const void* k
   p.timeout_ns = timeout_ns;
   const int n_qt = (seq_len + kBQ - 1) / kBQ;
   p.pair_heads = ((hq / hkv) % 2 == 0) ? 1 : 0;
-  const unsigned grid = p.pair_heads ? static_cast<unsigned>(batch) * (hq / 2) * n_qt
-                                     : static_cast<unsigned>(batch) * hq * ((n_qt + 1) / 2);
+  const unsigned n_items = p.pair_heads ? static_cast<unsigned>(batch) * (hq / 2) * n_qt
+                                        : static_cast<unsigned>(batch) * hq * ((n_qt + 1) / 2);
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const unsigned grid = n_items < static_cast<unsigned>(sms) ? n_items : static_cast<unsigned>(sms);
   attention_fwd_kernel<<<grid, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(tq, tk, tv, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }

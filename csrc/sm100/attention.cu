@@ -2,7 +2,7 @@
 //
 // One CTA works on TWO 128-row query tiles that share a KV head: two query heads of one GQA
 // group at the same rows (even group size) or two consecutive row tiles of one head. K and V
-// tiles arrive by TMA into a five-slot ring and are used by both tiles. S_t = Q_t K^T and
+// tiles arrive by TMA into a four-slot ring and are used by both tiles. S_t = Q_t K^T and
 // O_t += P_t V are tcgen05.mma (M=128, N=128) with fp32 accumulators in TMEM: columns
 // [0,128) and [128,256) hold S_0 and S_1, [256,384) and [384,512) hold O_0 and O_1. Four
 // softmax warps per tile give every query row one thread: it pulls its S row (128 columns)
@@ -37,8 +37,11 @@ constexpr int kTiles = 2;       // query tiles per CTA
 constexpr int kSoftThreads = 128 * kTiles;
 constexpr int kThreads = kSoftThreads + 64;  // softmax warps, then one TMA warp and one MMA warp
 constexpr int kTileBytes = 128 * 128 * 2;  // 32 KiB: two 64-column boxes of 128 rows
-constexpr int kSlots = 5;                  // ring of K / V tiles
-constexpr int kSmemBytes = kTiles * kTileBytes + kSlots * kTileBytes + 1024 + 512;
+constexpr int kSlots = 4;                  // ring of K / V tiles
+constexpr int kStagePitch = 80;            // bytes between rows of an output staging tile (64 B + pad)
+constexpr int kStageWarpBytes = 32 * kStagePitch;
+constexpr int kStageBytes = (kSoftThreads / 32) * kStageWarpBytes;
+constexpr int kSmemBytes = kTiles * kTileBytes + kSlots * kTileBytes + kStageBytes + 1024 + 512;
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct Control {
@@ -47,7 +50,7 @@ struct Control {
   uint64_t ring_full[kSlots];
   uint64_t ring_empty[kSlots];
   uint64_t s_full[kTiles];    // S_t of the next KV tile is in TMEM
-  uint64_t p_full[kTiles];    // P_t written (and the S_t columns read)
+  uint64_t p_full[kTiles][2]; // P_t for keys [64 h, 64 h + 64) written (h = 1: the whole S_t row has been read)
   uint64_t pv_done[kTiles];   // O_t includes every P V product issued so far
   uint32_t tmem_base;
   int abort_flag;
@@ -121,6 +124,18 @@ __device__ __forceinline__ Item decode_item(const AttnParams& p, int item, int n
   return w;
 }
 
+// Items are dealt to the resident CTAs in rounds, left to right in even rounds and right to
+// left in odd ones: with items sorted heaviest first this keeps the CTAs' totals within about
+// one item of each other without a shared counter. Each pair of CTAs walks its rounds starting
+// at a different one, so the CTAs do not all reach their output pass (a burst of stores) at
+// the same moment. Returns -1 for a slot of the last, partial round that holds no item.
+__device__ __forceinline__ int item_of_step(int step, int n_rounds, int n_items) {
+  const int g = static_cast<int>(gridDim.x), c = static_cast<int>(blockIdx.x);
+  const int round = (step + (c >> 1)) % n_rounds;
+  const int item = round * g + ((round & 1) ? g - 1 - c : c);
+  return item < n_items ? item : -1;
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
 attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ AttnParams p) {
@@ -130,11 +145,12 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   uint8_t* smem = smem_raw + (base - raw_addr);
   const uint32_t q_tiles = base;                               // tile t at + t * 32 KiB
   const uint32_t ring = base + kTiles * kTileBytes;            // slot s at + s * 32 KiB
-  Control* ctl = reinterpret_cast<Control*>(smem + (kTiles + kSlots) * kTileBytes);
+  uint8_t* stage_base = smem + (kTiles + kSlots) * kTileBytes;
+  Control* ctl = reinterpret_cast<Control*>(stage_base + kStageBytes);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // Work items: (row unit, head unit, sequence). Items are numbered heaviest row unit first
-  // and dealt round-robin to the resident CTAs, which walk their items in a loop; all
+  // and dealt in rounds to the resident CTAs, which walk their items in a loop; all
   // pipeline counters run on across items, so the loads and the first S products of the next
   // item overlap the last softmax tiles and the output pass of the current one.
   const int n_qt = (p.seq_len + kBQ - 1) / kBQ;
@@ -143,8 +159,10 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   const int per_unit = n_head_units * p.batch;
   const int n_items = n_units * per_unit;
   const int group = p.hq / p.hkv;
+  const int n_rounds = (n_items + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
 
   WaitCtx wctx{&ctl->abort_flag, p.status, p.timeout_ns};
+  KA_T(t_k0);
 
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(&ctl->q_full), 1);
@@ -155,7 +173,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     }
     for (int t = 0; t < kTiles; ++t) {
       mbar_init(smem_u32(&ctl->s_full[t]), 1);
-      mbar_init(smem_u32(&ctl->p_full[t]), 4);
+      mbar_init(smem_u32(&ctl->p_full[t][0]), 4);
+      mbar_init(smem_u32(&ctl->p_full[t][1]), 4);
       mbar_init(smem_u32(&ctl->pv_done[t]), 1);
     }
     ctl->abort_flag = 0;
@@ -178,7 +197,9 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       const uint32_t qf = smem_u32(&ctl->q_full);
       int it = 0, qi = 0;
       bool ok = true;
-      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++qi) {
+      for (int step = 0; step < n_rounds && ok; ++step) {
+        const int item = item_of_step(step, n_rounds, n_items);
+        if (item < 0) continue;
         const Item w = decode_item(p, item, n_units, n_head_units, per_unit, group);
         if (!mbar_wait_bounded(smem_u32(&ctl->q_empty), (qi & 1) ^ 1u, wctx, 30, item)) break;
         mbar_arrive_expect_tx(qf, (w.tc[1].n_kv > 0 ? 2 : 1) * kTileBytes);
@@ -206,6 +227,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           if (j + 1 < w.n_max) load(&tm_k, j + 1);
           if (ok) load(&tm_v, j);
         }
+        ++qi;
       }
     }
   } else if (warp == kSoftThreads / 32 + 1) {
@@ -232,7 +254,9 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                        kk > 0 ? 1u : 0u);
         umma_commit<1>(smem_u32(&ctl->s_full[t]));
       };
-      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++qi) {
+      for (int step = 0; step < n_rounds && ok; ++step) {
+        const int item = item_of_step(step, n_rounds, n_items);
+        if (item < 0) continue;
         const Item w = decode_item(p, item, n_units, n_head_units, per_unit, group);
         ok = mbar_wait_bounded(smem_u32(&ctl->q_full), qi & 1, wctx, 32, item);
         if (!ok) break;
@@ -254,14 +278,23 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 #pragma unroll
           for (int t = 0; t < kTiles; ++t) {
             if (!ok || j >= w.tc[t].n_kv) continue;
-            ok = mbar_wait_bounded(smem_u32(&ctl->p_full[t]), cnt[t] & 1, wctx, 35, t);
+            // the first half of P is signalled as soon as it is written, so its part of the
+            // product runs while the softmax warps are still on the second half
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {
+              if (!ok) continue;
+              ok = mbar_wait_bounded(smem_u32(&ctl->p_full[t][hf]), cnt[t] & 1, wctx, 35, t);
+              if (!ok) continue;
+              tc_fence_after_sync();
+#pragma unroll
+              for (int k4 = 0; k4 < 4; ++k4) {
+                const int kk = hf * 4 + k4;
+                umma_bf16_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + kk * 8, desc_mnmajor(vt, kk), idesc_o,
+                             (j > 0 || kk > 0) ? 1u : 0u);
+              }
+            }
             if (!ok) continue;
             ++cnt[t];
-            tc_fence_after_sync();
-#pragma unroll
-            for (int kk = 0; kk < kBKV / 16; ++kk)
-              umma_bf16_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + kk * 8, desc_mnmajor(vt, kk), idesc_o,
-                           (j > 0 || kk > 0) ? 1u : 0u);
             umma_commit<1>(smem_u32(&ctl->pv_done[t]));
             if (j + 1 < w.tc[t].n_kv) issue_s(t, kt);
           }
@@ -270,6 +303,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           umma_commit<1>(smem_u32(&ctl->ring_empty[vslot]));
           if (j + 2 == w.n_max) umma_commit<1>(smem_u32(&ctl->q_empty));   // the last S products are issued
         }
+        ++qi;
       }
     }
   } else {
@@ -285,7 +319,10 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     int cnt = 0;                            // tile-iterations of this tile so far (barrier phases)
     bool ok = true;
 
-    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+    for (int step = 0; step < n_rounds && ok; ++step) {
+    const int item = item_of_step(step, n_rounds, n_items);
+    if (item < 0) continue;
+    KA_T(t_i0);
     const Item wi = decode_item(p, item, n_units, n_head_units, per_unit, group);
     const TileCoord tc = wi.tc[t];
     const int b = wi.b, tok0 = wi.tok0;
@@ -297,7 +334,12 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       uint32_t va[32], vb[32];     // two 32-column chunks of the S row in flight
       const int kv0 = j * kBKV;
       const int limit = (p.causal ? min(q_pos, p.seq_len - 1) : p.seq_len - 1) - kv0;  // last allowed column
-      const bool full_tile = limit >= kBKV - 1;
+      // Rows grow with the lane, so lane 0 has the smallest limit of the warp and lane 31 the
+      // largest: the tile is unmasked for the whole warp, or only its first n_act 32-column
+      // chunks hold any allowed column (the diagonal tile of a causal row block, a ragged end).
+      const int lim_lo = __shfl_sync(0xffffffffu, limit, 0), lim_hi = __shfl_sync(0xffffffffu, limit, 31);
+      const bool warp_full = lim_lo >= kBKV - 1;
+      const int n_act = lim_hi < 0 ? 0 : min(4, lim_hi / 32 + 1);
       KA_T(t_a);
       {
         const bool mine = mbar_wait_bounded(smem_u32(&ctl->s_full[t]), cnt & 1, wctx, 38, t);
@@ -306,11 +348,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       }
       KA_T(t_b);
       tc_fence_after_sync();
-      // Pass 1: the row maximum. Chunks 2 and 3 first, then 0 and 1, which stay in registers
-      // for the start of pass 2 (the S row is read from TMEM one and a half times, never
-      // held whole: 128 live values would not fit the register budget of this kernel).
       auto mask_chunk = [&](uint32_t (&v)[32], int g) {
-        if (!full_tile) {
+        if (g * 32 + 31 > lim_lo) {
 #pragma unroll
           for (int i = 0; i < 32; ++i)
             if (g * 32 + i > limit) v[i] = __float_as_uint(-CUDART_INF_F);
@@ -319,29 +358,37 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       float a0 = -CUDART_INF_F, a1 = -CUDART_INF_F, a2 = -CUDART_INF_F, a3 = -CUDART_INF_F;
       auto max_chunk = [&](const uint32_t (&v)[32]) {
 #pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-          a0 = fmaxf(a0, __uint_as_float(v[i]));
-          a1 = fmaxf(a1, __uint_as_float(v[i + 1]));
-          a2 = fmaxf(a2, __uint_as_float(v[i + 2]));
-          a3 = fmaxf(a3, __uint_as_float(v[i + 3]));
+        for (int i = 0; i < 32; i += 8) {
+          a0 = max3(a0, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+          a1 = max3(a1, __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+          a2 = max3(a2, __uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
+          a3 = max3(a3, __uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
         }
       };
-      tmem_ld_32x32(tmem_s + 64, va);
-      tmem_ld_32x32(tmem_s + 96, vb);
-      tmem_ld_wait_dep(va);
-      tmem_ld_wait_dep(vb);
-      mask_chunk(va, 2);
-      mask_chunk(vb, 3);
-      max_chunk(va);
-      max_chunk(vb);
-      tmem_ld_32x32(tmem_s, va);
-      tmem_ld_32x32(tmem_s + 32, vb);
-      tmem_ld_wait_dep(va);
-      tmem_ld_wait_dep(vb);
-      mask_chunk(va, 0);
-      mask_chunk(vb, 1);
-      max_chunk(va);
-      max_chunk(vb);
+      // Pass 1: the row maximum. Unmasked tile: chunks 2 and 3 first, then 0 and 1, which stay
+      // in registers for the start of pass 2 (the S row is read from TMEM one and a half
+      // times, never held whole: 128 live values would not fit the register budget).
+      if (warp_full) {
+        tmem_ld_32x32(tmem_s + 64, va);
+        tmem_ld_32x32(tmem_s + 96, vb);
+        tmem_ld_wait_dep(va);
+        tmem_ld_wait_dep(vb);
+        max_chunk(va);
+        max_chunk(vb);
+        tmem_ld_32x32(tmem_s, va);
+        tmem_ld_32x32(tmem_s + 32, vb);
+        tmem_ld_wait_dep(va);
+        tmem_ld_wait_dep(vb);
+        max_chunk(va);
+        max_chunk(vb);
+      } else {
+        for (int g = 0; g < n_act; ++g) {
+          tmem_ld_32x32(tmem_s + g * 32, va);
+          tmem_ld_wait_dep(va);
+          mask_chunk(va, g);
+          max_chunk(va);
+        }
+      }
       const float mx = fmaxf(fmaxf(a0, a1), fmaxf(a2, a3));
       // move the reference maximum only on the first tile or when it would grow by more than
       // 2^8 in the exponent; otherwise probabilities are taken relative to the old reference
@@ -384,36 +431,64 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       auto exp_chunk = [&](const uint32_t (&v)[32], int half) {
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {
-          const float e0 = ex2_approx(__fmaf_rn(__uint_as_float(v[i]), c, neg));
-          const float e1 = ex2_approx(__fmaf_rn(__uint_as_float(v[i + 1]), c, neg));
-          const float e2 = ex2_approx(__fmaf_rn(__uint_as_float(v[i + 2]), c, neg));
-          const float e3 = ex2_approx(__fmaf_rn(__uint_as_float(v[i + 3]), c, neg));
-          ls0 = __fadd_rn(ls0, e0);
-          ls1 = __fadd_rn(ls1, e1);
-          ls2 = __fadd_rn(ls2, e2);
-          ls3 = __fadd_rn(ls3, e3);
+          float x0, x1, x2, x3;
+          fma2(x0, x1, __uint_as_float(v[i]), __uint_as_float(v[i + 1]), c, c, neg, neg);
+          fma2(x2, x3, __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]), c, c, neg, neg);
+          const float e0 = ex2_approx(x0), e1 = ex2_approx(x1), e2 = ex2_approx(x2), e3 = ex2_approx(x3);
+          add2(ls0, ls1, ls0, ls1, e0, e1);
+          add2(ls2, ls3, ls2, ls3, e2, e3);
           w[half * 16 + (i >> 1)] = pack_bf16(e0, e1);
           w[half * 16 + (i >> 1) + 1] = pack_bf16(e2, e3);
         }
       };
-      exp_chunk(va, 0);
-      tmem_ld_32x32(tmem_s + 64, va);        // chunk 2 on its way while chunk 1 is processed
-      exp_chunk(vb, 1);
-      tmem_st_32x32(tmem_s, w);              // P columns [0,64) as 32 packed words over S columns [0,32)
-      tmem_ld_wait_dep(va);
-      tmem_ld_32x32(tmem_s + 96, vb);
-      mask_chunk(va, 2);
-      exp_chunk(va, 0);
-      tmem_ld_wait_dep(vb);
-      mask_chunk(vb, 3);
-      exp_chunk(vb, 1);
-      tmem_st_32x32(tmem_s + 32, w);         // P columns [64,128) over S columns [32,64)
+      if (warp_full) {
+        exp_chunk(va, 0);
+        tmem_ld_32x32(tmem_s + 64, va);        // chunk 2 on its way while chunk 1 is processed
+        exp_chunk(vb, 1);
+        tmem_st_32x32(tmem_s, w);              // P columns [0,64) as 32 packed words over S columns [0,32)
+        tmem_ld_wait_dep(va);
+        tmem_ld_32x32(tmem_s + 96, vb);
+        exp_chunk(va, 0);
+        tmem_st_wait();                        // first half of P is in TMEM: let its P V product start
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&ctl->p_full[t][0]));
+        tmem_ld_wait_dep(vb);
+        exp_chunk(vb, 1);
+        tmem_st_32x32(tmem_s + 32, w);         // P columns [64,128) over S columns [32,64)
+      } else {
+        // chunks past n_act are masked for every row of the warp: their P is zero, no exp
+#pragma unroll
+        for (int hblk = 0; hblk < 2; ++hblk) {
+#pragma unroll
+          for (int g2 = 0; g2 < 2; ++g2) {
+            const int g = hblk * 2 + g2;
+            if (g < n_act) {
+              tmem_ld_32x32(tmem_s + g * 32, va);
+              tmem_ld_wait_dep(va);
+              mask_chunk(va, g);
+              exp_chunk(va, g2);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) w[g2 * 16 + i] = 0u;
+            }
+          }
+          // P of this half overwrites S columns [32 hblk, 32 hblk + 32): chunk hblk, already read
+          tmem_st_32x32(tmem_s + hblk * 32, w);
+          if (hblk == 0) {
+            tmem_st_wait();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&ctl->p_full[t][0]));
+          }
+        }
+      }
       l = __fmaf_rn(l, alpha, __fadd_rn(__fadd_rn(ls0, ls1), __fadd_rn(ls2, ls3)));
       KA_T(t_d);
       tmem_st_wait();
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&ctl->p_full[t]));
+      if (lane == 0) mbar_arrive(smem_u32(&ctl->p_full[t][1]));
       KA_T(t_e);
       KA_ACC(0, t_b - t_a);
       KA_ACC(1, t_c - t_b);
@@ -422,30 +497,42 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       KA_ACC(4, 1);
     }
 
+    KA_T(t_p0);
     if (ok && tc.n_kv > 0) {
       const bool mine = mbar_wait_bounded(smem_u32(&ctl->pv_done[t]), (cnt - 1) & 1, wctx, 37, t);
       ok = __all_sync(0xffffffffu, mine) != 0;
     }
+    KA_T(t_p1);
     if (ok && tc.n_kv > 0) {
       tc_fence_after_sync();
       const float inv = l > 0.f ? __fdiv_rn(1.f, l) : 0.f;
-      __nv_bfloat16* dst = p.out + static_cast<long long>(tok0 + q_pos) * p.out_stride + tc.h * kD;
+      // Rows go out through a per-warp staging tile (32 rows x 64 B, 80 B pitch) so that a
+      // store instruction writes eight 64-byte row pieces instead of 32 scattered 16-byte ones.
+      uint8_t* stage = stage_base + warp * kStageWarpBytes;
+      const int warp_row0 = tc.row0 + (warp & 3) * 32;
+      __nv_bfloat16* dst0 = p.out + static_cast<long long>(tok0 + warp_row0) * p.out_stride + tc.h * kD;
       uint32_t v[32];
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
         __syncwarp();
         tmem_ld_32x32(tmem_o + g * 32, v);
         tmem_ld_wait_dep(v);
-        if (q_pos < p.seq_len) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint4 w;
-            w.x = pack_bf16(__fmul_rn(__uint_as_float(v[i]), inv), __fmul_rn(__uint_as_float(v[i + 1]), inv));
-            w.y = pack_bf16(__fmul_rn(__uint_as_float(v[i + 2]), inv), __fmul_rn(__uint_as_float(v[i + 3]), inv));
-            w.z = pack_bf16(__fmul_rn(__uint_as_float(v[i + 4]), inv), __fmul_rn(__uint_as_float(v[i + 5]), inv));
-            w.w = pack_bf16(__fmul_rn(__uint_as_float(v[i + 6]), inv), __fmul_rn(__uint_as_float(v[i + 7]), inv));
-            *reinterpret_cast<uint4*>(dst + g * 32 + i) = w;
-          }
+        for (int i = 0; i < 32; i += 8) {
+          uint4 w;
+          w.x = pack_bf16(__fmul_rn(__uint_as_float(v[i]), inv), __fmul_rn(__uint_as_float(v[i + 1]), inv));
+          w.y = pack_bf16(__fmul_rn(__uint_as_float(v[i + 2]), inv), __fmul_rn(__uint_as_float(v[i + 3]), inv));
+          w.z = pack_bf16(__fmul_rn(__uint_as_float(v[i + 4]), inv), __fmul_rn(__uint_as_float(v[i + 5]), inv));
+          w.w = pack_bf16(__fmul_rn(__uint_as_float(v[i + 6]), inv), __fmul_rn(__uint_as_float(v[i + 7]), inv));
+          *reinterpret_cast<uint4*>(stage + lane * kStagePitch + (i >> 3) * 16) = w;
+        }
+        __syncwarp();
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int idx = k * 32 + lane, r = idx >> 2, u = idx & 3;
+          const uint4 w = *reinterpret_cast<const uint4*>(stage + r * kStagePitch + u * 16);
+          if (warp_row0 + r < p.seq_len)
+            *reinterpret_cast<uint4*>(dst0 + static_cast<long long>(r) * p.out_stride + g * 32 + u * 8) = w;
         }
       }
       if (p.lse && q_pos < p.seq_len)
@@ -455,6 +542,12 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       // after which the MMA warp overwrites O
       tc_fence_before_sync();
     }
+    KA_T(t_p2);
+    KA_ACC(5, t_p1 - t_p0);
+    KA_ACC(6, t_p2 - t_p1);
+    KA_ACC(7, 1);
+    KA_ACC(14, t_p2 - t_i0);
+    KA_ACC(15, t_p0 - t_i0);
     }  // items
   }
 
@@ -466,6 +559,13 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     tc_fence_after_sync();
     tmem_dealloc<1>(tmem_base, 512);
   }
+#ifdef KA_ATTN_TIMING
+  if (threadIdx.x == 0) {
+    atomicAdd(&ka_attn_dbg[11], static_cast<unsigned long long>(clock64() - t_k0));
+    atomicAdd(&ka_attn_dbg[12], 1ull);
+    atomicMax(&ka_attn_dbg[13], static_cast<unsigned long long>(clock64() - t_k0));
+  }
+#endif
 }
 
 }  // namespace

@@ -2,15 +2,19 @@
 //
 // One CTA works on TWO 128-row query tiles that share a KV head: two query heads of one GQA
 // group at the same rows (even group size) or two consecutive row tiles of one head. K and V
-// tiles arrive by TMA into a four-slot ring and are used by both tiles. S_t = Q_t K^T and
+// tiles arrive by TMA into a five-slot ring and are used by both tiles. S_t = Q_t K^T and
 // O_t += P_t V are tcgen05.mma (M=128, N=128) with fp32 accumulators in TMEM: columns
 // [0,128) and [128,256) hold S_0 and S_1, [256,384) and [384,512) hold O_0 and O_1. Four
-// softmax warps per tile give every query row one thread: it pulls its S row (128 columns)
-// into registers, and writes P as packed bf16 back into the first 64 columns of the same S
-// region, from where the second MMA reads it as a TMEM A operand, so P never touches shared
-// memory. While the softmax warps of one tile work, the tensor core runs the other tile's
-// MMAs. The running maximum is only moved when it grows by more than 2^8 (then the O row is
-// rescaled in TMEM), so the common tile needs no correction pass.
+// softmax warps per tile give every query row one thread: it reads its S row from TMEM in
+// 32-column chunks (a maximum pass, then an exponential pass with packed two-lane fp32
+// arithmetic) and writes P as packed bf16 back into the first 64 columns of the same S region,
+// from where the second MMA reads it as a TMEM A operand, so P never touches shared memory
+// (whose bandwidth the Q K^T products need). The first half of P is signalled early, so half
+// of the P V product overlaps the rest of the softmax; while the softmax warps of one tile
+// work, the tensor core runs the other tile's MMAs. The running maximum is only moved when it
+// grows by more than 2^8 (then the O row is rescaled in TMEM), so the common tile needs no
+// correction pass. The kernel is persistent: one CTA per SM walks a list of work items dealt
+// heaviest first, and the loads and first products of the next item overlap the output pass.
 // KV tiles are visited in increasing order, always 128 wide, whatever the batch size, the
 // pairing or the number of heads on this GPU, so a query row's output depends on its own
 // sequence only.
@@ -37,11 +41,8 @@ constexpr int kTiles = 2;       // query tiles per CTA
 constexpr int kSoftThreads = 128 * kTiles;
 constexpr int kThreads = kSoftThreads + 64;  // softmax warps, then one TMA warp and one MMA warp
 constexpr int kTileBytes = 128 * 128 * 2;  // 32 KiB: two 64-column boxes of 128 rows
-constexpr int kSlots = 4;                  // ring of K / V tiles
-constexpr int kStagePitch = 80;            // bytes between rows of an output staging tile (64 B + pad)
-constexpr int kStageWarpBytes = 32 * kStagePitch;
-constexpr int kStageBytes = (kSoftThreads / 32) * kStageWarpBytes;
-constexpr int kSmemBytes = kTiles * kTileBytes + kSlots * kTileBytes + kStageBytes + 1024 + 512;
+constexpr int kSlots = 5;                  // ring of K / V tiles
+constexpr int kSmemBytes = kTiles * kTileBytes + kSlots * kTileBytes + 1024 + 512;
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct Control {
@@ -67,15 +68,6 @@ struct AttnParams {
   int* status;
   unsigned long long timeout_ns;
 };
-
-#ifdef KA_ATTN_TIMING
-__device__ unsigned long long ka_attn_dbg[16];
-#define KA_T(var) const long long var = clock64()
-#define KA_ACC(slot, val) do { if ((threadIdx.x & 127) == 0) atomicAdd(&ka_attn_dbg[slot], static_cast<unsigned long long>(val)); } while (0)
-#else
-#define KA_T(var)
-#define KA_ACC(slot, val)
-#endif
 
 struct TileCoord {
   int h;        // query head
@@ -145,8 +137,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   uint8_t* smem = smem_raw + (base - raw_addr);
   const uint32_t q_tiles = base;                               // tile t at + t * 32 KiB
   const uint32_t ring = base + kTiles * kTileBytes;            // slot s at + s * 32 KiB
-  uint8_t* stage_base = smem + (kTiles + kSlots) * kTileBytes;
-  Control* ctl = reinterpret_cast<Control*>(stage_base + kStageBytes);
+  Control* ctl = reinterpret_cast<Control*>(smem + (kTiles + kSlots) * kTileBytes);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // Work items: (row unit, head unit, sequence). Items are numbered heaviest row unit first
@@ -162,7 +153,6 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   const int n_rounds = (n_items + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
 
   WaitCtx wctx{&ctl->abort_flag, p.status, p.timeout_ns};
-  KA_T(t_k0);
 
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(&ctl->q_full), 1);
@@ -247,11 +237,18 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         tile_addr = ring + slot * kTileBytes;
         ++it;
       };
+      // Operand descriptors are a base (tile 0 of Q, slot 0 of the ring) plus small constants in
+      // the 16-byte address field: the whole buffer lies below 256 KiB, so the sums never carry
+      // out of that field, and issuing an MMA costs an add instead of rebuilding the descriptor.
+      const uint64_t dq0 = desc_kmajor(q_tiles, 0), dk0 = desc_kmajor(ring, 0), dv0 = desc_mnmajor(ring, 0);
       auto issue_s = [&](int t, uint32_t kt) {
+        const uint64_t dq = dq0 + static_cast<uint64_t>((t * kTileBytes) >> 4);
+        const uint64_t dk = dk0 + static_cast<uint64_t>((kt - ring) >> 4);
 #pragma unroll
-        for (int kk = 0; kk < kD / 16; ++kk)
-          umma_bf16<1>(tmem_base + t * 128, desc_kmajor(q_tiles + t * kTileBytes, kk), desc_kmajor(kt, kk), idesc_s,
-                       kk > 0 ? 1u : 0u);
+        for (int kk = 0; kk < kD / 16; ++kk) {
+          const uint64_t koff = static_cast<uint64_t>(((kk >> 2) * 16384 + (kk & 3) * 32) >> 4);
+          umma_bf16<1>(tmem_base + t * 128, dq + koff, dk + koff, idesc_s, kk > 0 ? 1u : 0u);
+        }
         umma_commit<1>(smem_u32(&ctl->s_full[t]));
       };
       for (int step = 0; step < n_rounds && ok; ++step) {
@@ -289,7 +286,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 #pragma unroll
               for (int k4 = 0; k4 < 4; ++k4) {
                 const int kk = hf * 4 + k4;
-                umma_bf16_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + kk * 8, desc_mnmajor(vt, kk), idesc_o,
+                const uint64_t dv = dv0 + static_cast<uint64_t>((vt - ring + kk * 2048) >> 4);
+                umma_bf16_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + kk * 8, dv, idesc_o,
                              (j > 0 || kk > 0) ? 1u : 0u);
               }
             }
@@ -322,7 +320,6 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     for (int step = 0; step < n_rounds && ok; ++step) {
     const int item = item_of_step(step, n_rounds, n_items);
     if (item < 0) continue;
-    KA_T(t_i0);
     const Item wi = decode_item(p, item, n_units, n_head_units, per_unit, group);
     const TileCoord tc = wi.tc[t];
     const int b = wi.b, tok0 = wi.tok0;
@@ -340,13 +337,11 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       const int lim_lo = __shfl_sync(0xffffffffu, limit, 0), lim_hi = __shfl_sync(0xffffffffu, limit, 31);
       const bool warp_full = lim_lo >= kBKV - 1;
       const int n_act = lim_hi < 0 ? 0 : min(4, lim_hi / 32 + 1);
-      KA_T(t_a);
       {
         const bool mine = mbar_wait_bounded(smem_u32(&ctl->s_full[t]), cnt & 1, wctx, 38, t);
         ok = __all_sync(0xffffffffu, mine) != 0;
         if (!ok) break;
       }
-      KA_T(t_b);
       tc_fence_after_sync();
       auto mask_chunk = [&](uint32_t (&v)[32], int g) {
         if (g * 32 + 31 > lim_lo) {
@@ -424,7 +419,6 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           tmem_st_32x32(tmem_o + g * 32, v);
         }
       }
-      KA_T(t_c);
       // Pass 2: probabilities, 32 columns at a time; masked columns hold -inf and give 0.
       float ls0 = 0.f, ls1 = 0.f, ls2 = 0.f, ls3 = 0.f;
       uint32_t w[32];
@@ -484,57 +478,48 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         }
       }
       l = __fmaf_rn(l, alpha, __fadd_rn(__fadd_rn(ls0, ls1), __fadd_rn(ls2, ls3)));
-      KA_T(t_d);
       tmem_st_wait();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&ctl->p_full[t][1]));
-      KA_T(t_e);
-      KA_ACC(0, t_b - t_a);
-      KA_ACC(1, t_c - t_b);
-      KA_ACC(2, t_d - t_c);
-      KA_ACC(3, t_e - t_d);
-      KA_ACC(4, 1);
     }
 
-    KA_T(t_p0);
     if (ok && tc.n_kv > 0) {
       const bool mine = mbar_wait_bounded(smem_u32(&ctl->pv_done[t]), (cnt - 1) & 1, wctx, 37, t);
       ok = __all_sync(0xffffffffu, mine) != 0;
     }
-    KA_T(t_p1);
     if (ok && tc.n_kv > 0) {
       tc_fence_after_sync();
       const float inv = l > 0.f ? __fdiv_rn(1.f, l) : 0.f;
-      // Rows go out through a per-warp staging tile (32 rows x 64 B, 80 B pitch) so that a
-      // store instruction writes eight 64-byte row pieces instead of 32 scattered 16-byte ones.
-      uint8_t* stage = stage_base + warp * kStageWarpBytes;
-      const int warp_row0 = tc.row0 + (warp & 3) * 32;
-      __nv_bfloat16* dst0 = p.out + static_cast<long long>(tok0 + warp_row0) * p.out_stride + tc.h * kD;
-      uint32_t v[32];
+      // The row goes out 32 columns at a time straight from registers (shared memory bandwidth
+      // belongs to the MMAs), with the next TMEM load in flight while a chunk is stored.
+      uint4* dst = reinterpret_cast<uint4*>(p.out + static_cast<long long>(tok0 + q_pos) * p.out_stride + tc.h * kD);
+      uint32_t va[32], vb[32];
+      auto emit = [&](const uint32_t (&v)[32], int g) {
+        if (q_pos < p.seq_len) {
 #pragma unroll
-      for (int g = 0; g < 4; ++g) {
-        __syncwarp();
-        tmem_ld_32x32(tmem_o + g * 32, v);
-        tmem_ld_wait_dep(v);
-#pragma unroll
-        for (int i = 0; i < 32; i += 8) {
-          uint4 w;
-          w.x = pack_bf16(__fmul_rn(__uint_as_float(v[i]), inv), __fmul_rn(__uint_as_float(v[i + 1]), inv));
-          w.y = pack_bf16(__fmul_rn(__uint_as_float(v[i + 2]), inv), __fmul_rn(__uint_as_float(v[i + 3]), inv));
-          w.z = pack_bf16(__fmul_rn(__uint_as_float(v[i + 4]), inv), __fmul_rn(__uint_as_float(v[i + 5]), inv));
-          w.w = pack_bf16(__fmul_rn(__uint_as_float(v[i + 6]), inv), __fmul_rn(__uint_as_float(v[i + 7]), inv));
-          *reinterpret_cast<uint4*>(stage + lane * kStagePitch + (i >> 3) * 16) = w;
+          for (int i = 0; i < 32; i += 8) {
+            uint4 w4;
+            w4.x = pack_bf16(__fmul_rn(__uint_as_float(v[i]), inv), __fmul_rn(__uint_as_float(v[i + 1]), inv));
+            w4.y = pack_bf16(__fmul_rn(__uint_as_float(v[i + 2]), inv), __fmul_rn(__uint_as_float(v[i + 3]), inv));
+            w4.z = pack_bf16(__fmul_rn(__uint_as_float(v[i + 4]), inv), __fmul_rn(__uint_as_float(v[i + 5]), inv));
+            w4.w = pack_bf16(__fmul_rn(__uint_as_float(v[i + 6]), inv), __fmul_rn(__uint_as_float(v[i + 7]), inv));
+            dst[g * 4 + (i >> 3)] = w4;
+          }
         }
-        __syncwarp();
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const int idx = k * 32 + lane, r = idx >> 2, u = idx & 3;
-          const uint4 w = *reinterpret_cast<const uint4*>(stage + r * kStagePitch + u * 16);
-          if (warp_row0 + r < p.seq_len)
-            *reinterpret_cast<uint4*>(dst0 + static_cast<long long>(r) * p.out_stride + g * 32 + u * 8) = w;
-        }
-      }
+      };
+      tmem_ld_32x32(tmem_o, va);
+      tmem_ld_32x32(tmem_o + 32, vb);
+      tmem_ld_wait_dep(va);
+      tmem_ld_wait_dep(vb);
+      emit(va, 0);
+      tmem_ld_32x32(tmem_o + 64, va);
+      emit(vb, 1);
+      tmem_ld_32x32(tmem_o + 96, vb);
+      tmem_ld_wait_dep(va);
+      tmem_ld_wait_dep(vb);
+      emit(va, 2);
+      emit(vb, 3);
       if (p.lse && q_pos < p.seq_len)
         p.lse[(static_cast<long long>(b) * p.hq + tc.h) * p.seq_len + q_pos] =
             __fmaf_rn(lg2_approx(l), 0.6931471805599453f, __fmul_rn(m, p.scale));
@@ -542,12 +527,6 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       // after which the MMA warp overwrites O
       tc_fence_before_sync();
     }
-    KA_T(t_p2);
-    KA_ACC(5, t_p1 - t_p0);
-    KA_ACC(6, t_p2 - t_p1);
-    KA_ACC(7, 1);
-    KA_ACC(14, t_p2 - t_i0);
-    KA_ACC(15, t_p0 - t_i0);
     }  // items
   }
 
@@ -559,13 +538,6 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     tc_fence_after_sync();
     tmem_dealloc<1>(tmem_base, 512);
   }
-#ifdef KA_ATTN_TIMING
-  if (threadIdx.x == 0) {
-    atomicAdd(&ka_attn_dbg[11], static_cast<unsigned long long>(clock64() - t_k0));
-    atomicAdd(&ka_attn_dbg[12], 1ull);
-    atomicMax(&ka_attn_dbg[13], static_cast<unsigned long long>(clock64() - t_k0));
-  }
-#endif
 }
 
 }  // namespace
@@ -574,18 +546,6 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 // q: [B*L, Hq*128] view with `q_stride` elements between tokens; k, v: [B*L, Hkv*128] views
 // (strides k_stride, v_stride); out: [B*L, Hq*128] with out_stride; lse: [B, Hq, L] fp32 or
 // null. All bf16, 16-byte aligned, strides multiples of 8.
-#ifdef KA_ATTN_TIMING
-extern "C" int ka_attention_dbg_read(unsigned long long* host_out, int reset) {
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(host_out, ka::ka_attn_dbg, sizeof(unsigned long long) * 16);
-  if (reset) {
-    unsigned long long z[16] = {};
-    cudaMemcpyToSymbol(ka::ka_attn_dbg, z, sizeof(z));
-  }
-  return 0;
-}
-#endif
-
 extern "C" int ka_attention_fwd(const void* q, long long q_stride, const void* k, long long k_stride, const void* v,
                                 long long v_stride, void* out, long long out_stride, float* lse, int batch,
                                 int seq_len, int hq, int hkv, int head_dim, float scale, int causal, int* status,

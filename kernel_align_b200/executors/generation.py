@@ -4,6 +4,12 @@ every token with the fused sampler and recording its log-probability.
 Runs per data-parallel rank (``tp.world == 1``): each rank generates for its own prompts. All
 heavy steps are the native kernels: GEMMs (``gemm_bi``), prefill attention, decode attention,
 RMSNorm, RoPE, SwiGLU, the sampler and the logits log-prob kernel.
+
+On CUDA the decode step (embedding -> every layer -> final norm -> LM-head logits: a few
+hundred small launches) is captured once in a CUDA graph and replayed per token; position,
+cache length and cache slot live in device tensors that the graph itself advances, so a
+replay needs no host input but the token buffer. Sampling and the log-prob pick stay outside
+the graph (their random stream is keyed by a host-side step counter).
 """
 from __future__ import annotations
 
@@ -48,9 +54,77 @@ def _layer_step(layer, x, batch, seq_len, positions, cos, sin, cache_k, cache_v,
 
 
 @torch.no_grad()
+def _layer_decode(layer, x, batch, pos_t, cos, sin, cache_k, cache_v, lens_t, slot_t):
+    """One decoder layer on one new token per sequence, with every step-dependent quantity in
+    a device tensor (``pos_t [B]`` int64 position, ``lens_t [B]`` int32 keys to attend to,
+    ``slot_t [1]`` int64 cache slot), so the same launches can be replayed from a graph."""
+    cfg = layer.cfg
+    hd, hq, hkv = cfg.head_dim, layer.hq, layer.hkv
+    h = rmsnorm(x, layer.norm1, cfg.rms_eps)
+    qkv = gemm_bi(h, layer.wqkv)
+    q = qkv[:, : hq * hd].reshape(batch, hq, hd).contiguous()
+    k = qkv[:, hq * hd:(hq + hkv) * hd].reshape(batch, hkv, hd).contiguous()
+    v = qkv[:, (hq + hkv) * hd:].reshape(batch, 1, hkv, hd)
+    rope_(q, pos_t, cos, sin)
+    rope_(k, pos_t, cos, sin)
+    cache_k.index_copy_(1, slot_t, k.view(batch, 1, hkv, hd))
+    cache_v.index_copy_(1, slot_t, v)
+    a = attention_decode(q, cache_k, cache_v, lens_t).reshape(batch, hq * hd)
+    x = x + gemm_bi(a, layer.wo)
+    h = rmsnorm(x, layer.norm2, cfg.rms_eps)
+    return x + gemm_bi(swiglu(gemm_bi(h, layer.wgu)), layer.wdown)
+
+
+class _DecodeGraph:
+    """The captured decode step. ``step(tok)`` consumes the tokens sampled at the previous
+    position and returns the logits of the next one (a static buffer, overwritten per call)."""
+
+    def __init__(self, model, caches, batch: int, first_pos: int):
+        dev = model.embed.device
+        self.model, self.caches, self.batch = model, caches, batch
+        self.tok = torch.zeros(batch, dtype=torch.int64, device=dev)
+        self.pos = torch.full((batch,), first_pos, dtype=torch.int64, device=dev)
+        self.lens = torch.full((batch,), first_pos + 1, dtype=torch.int32, device=dev)
+        self.slot = torch.full((1,), first_pos, dtype=torch.int64, device=dev)
+        self.graph = None
+        self.logits = None
+
+    def _body(self):
+        m = self.model
+        x = torch.nn.functional.embedding(self.tok, m.embed)
+        for layer, (ck, cv) in zip(m.layers, self.caches):
+            x = _layer_decode(layer, x, self.batch, self.pos, m.rope_cos, m.rope_sin, ck, cv, self.lens, self.slot)
+        logits = gemm_bi(rmsnorm(x, m.norm, m.cfg.rms_eps), m.lm_head)
+        self.pos += 1
+        self.lens += 1
+        self.slot += 1
+        return logits
+
+    def step(self, tok: torch.Tensor, capture: bool) -> torch.Tensor:
+        self.tok.copy_(tok)
+        if self.graph is not None:
+            self.graph.replay()
+            return self.logits
+        if not capture:
+            return self._body()          # eager: also the warm-up that precedes a capture
+        g = torch.cuda.CUDAGraph()
+        try:
+            with torch.cuda.graph(g):
+                self.logits = self._body()
+        except RuntimeError:
+            # something on this path cannot be captured: stay eager (state tensors untouched,
+            # a capture records launches without running them)
+            self.graph = None
+            return self._body()
+        self.graph = g
+        g.replay()
+        return self.logits
+
+
+@torch.no_grad()
 def generate(model, prompts: torch.Tensor, sampler: Optional[SamplerBackend] = None, max_new_tokens: int = 16,
              temperature: float = 1.0, top_k: Optional[int] = None, top_p: Optional[float] = None,
-             group_size: int = 1, row_id_offset: int = 0) -> dict:
+             group_size: int = 1, row_id_offset: int = 0, cuda_graph: bool = True) -> dict:
     """``prompts [P, Lp]`` -> ``group_size`` completions each.
 
     Returns ``sequences [P * G, Lp + T]`` (int64), ``logp [P * G, T]`` (log-probability of each
@@ -77,17 +151,22 @@ def generate(model, prompts: torch.Tensor, sampler: Optional[SamplerBackend] = N
     for layer, (ck, cv) in zip(model.layers, caches):
         x = _layer_step(layer, x, batch, lp, pos, model.rope_cos, model.rope_sin, ck, cv, 0)
     last = x.view(batch, lp, -1)[:, -1].contiguous()
+    logits = gemm_bi(rmsnorm(last, model.norm, cfg.rms_eps), model.lm_head)       # [batch, vocab] bf16
+    use_graph = cuda_graph and dev.type == "cuda" and max_new_tokens > 3
+    dec = _DecodeGraph(model, caches, batch, lp) if dev.type == "cuda" else None
     for t in range(max_new_tokens):
-        h = rmsnorm(last, model.norm, cfg.rms_eps)
-        logits = gemm_bi(h, model.lm_head)                                  # [batch, vocab] bf16
         tok = sampler.sample(logits, top_k=top_k, top_p=top_p, temperature=temperature, row_ids=row_ids).long()
         out_tokens[:, t] = tok
         out_logp[:, t] = logits_logp(logits, tok, scale=1.0 / temperature if temperature > 0 else 1.0)
         if t + 1 == max_new_tokens:
             break
+        if dec is not None:
+            # first decode step eager (loads every kernel at this shape), second one captured
+            logits = dec.step(tok, capture=use_graph and t >= 1)
+            continue
         x = torch.nn.functional.embedding(tok, model.embed)
         pos = torch.full((batch,), lp + t, dtype=torch.int64, device=dev)
         for layer, (ck, cv) in zip(model.layers, caches):
             x = _layer_step(layer, x, batch, 1, pos, model.rope_cos, model.rope_sin, ck, cv, lp + t)
-        last = x
+        logits = gemm_bi(rmsnorm(x, model.norm, cfg.rms_eps), model.lm_head)
     return {"sequences": torch.cat([seqs, out_tokens], 1), "new_tokens": out_tokens, "logp": out_logp}

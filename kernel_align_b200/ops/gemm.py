@@ -10,9 +10,14 @@ backward GEMMs need no transpose pass:
 
 A row of the result depends only on that row of ``a`` (fixed tiles, fixed K order, no split-K),
 so the output is bitwise identical for any batch size. ``Linear`` is the autograd wrapper.
+
+Decode-sized products (``M <= 64``, plain layouts, bf16 output) go to the weight-streaming
+kernel of ``csrc/sm100/gemm_skinny.cu`` (operands swapped, one accumulation chain over K in the
+same order), which gives the same bits; ``KA_GEMM_SKINNY=0`` keeps everything on the tiled kernel.
 """
 from __future__ import annotations
 
+import os
 from ctypes import c_int, c_longlong, c_ulonglong, c_void_p
 
 import torch
@@ -47,6 +52,34 @@ def _fn():
     return fn
 
 
+SKINNY_MAX_ROWS = 64
+
+
+def _skinny_fn():
+    fn = _native.cuda().ka_gemm_skinny_bf16
+    fn.restype = c_int
+    fn.argtypes = [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p,
+                   c_ulonglong, c_void_p]
+    return fn
+
+
+def gemm_skinny(a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``a [M <= 64, K] @ w[N, K].T`` on the weight-streaming kernel (bf16 in, bf16 out)."""
+    m, k = a.shape
+    n = w.shape[0]
+    if m > SKINNY_MAX_ROWS or w.shape[1] != k:
+        raise ValueError("gemm_skinny takes at most 64 rows and matching inner dimensions")
+    a = a if a.stride(-1) == 1 else a.contiguous()
+    w = w if w.stride(-1) == 1 else w.contiguous()
+    out = torch.empty(m, n, dtype=torch.bfloat16, device=a.device)
+    rc = _skinny_fn()(a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), m, n, k,
+                      status_buffer(a.device).data_ptr(), default_timeout_ns(),
+                      torch.cuda.current_stream(a.device).cuda_stream)
+    if rc != 0:
+        raise RuntimeError(f"ka_gemm_skinny_bf16 rejected its arguments (code {rc})")
+    return out
+
+
 def gemm_bi(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bool = False,
             out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
     """``op(a) @ op(b).T`` with ``op(a) = a.T if trans_a`` (a stored ``[K, M]``) and
@@ -63,6 +96,9 @@ def gemm_bi(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b:
     kb, n = (b.shape[0], b.shape[1]) if trans_b else (b.shape[1], b.shape[0])
     if k != kb:
         raise ValueError(f"inner dimensions differ: {k} vs {kb}")
+    if (0 < m <= SKINNY_MAX_ROWS and not trans_a and not trans_b and out_dtype == torch.bfloat16
+            and os.environ.get("KA_GEMM_SKINNY", "1") != "0"):
+        return gemm_skinny(a, b)
     out = torch.empty(m, n, dtype=out_dtype, device=a.device)
     props = torch.cuda.get_device_properties(a.device)
     rc = _fn()(a.data_ptr(), a.stride(0), int(trans_a), b.data_ptr(), b.stride(0), int(trans_b), out.data_ptr(),

@@ -54,3 +54,23 @@ def test_linear_autograd(cuda_device):
     (xr @ wr.t()).backward(dy.float())
     assert (x.grad.float() - xr.grad).abs().max().item() <= 0.02 * xr.grad.abs().max().item()
     assert (w.grad.float() - wr.grad).abs().max().item() <= 0.02 * wr.grad.abs().max().item()
+
+
+@pytest.mark.parametrize("m", [1, 8, 16, 17, 33, 64])
+@pytest.mark.parametrize("n,k", [(4096, 4096), (1000, 520), (28672, 4096), (4096, 14336)])
+def test_skinny_gemm_equals_tiled_kernel_bitwise(cuda_device, m, n, k, monkeypatch):
+    """The weight-streaming kernel for decode-sized batches must give the bits of the tiled
+    kernel: otherwise a row's result would depend on the batch size it is computed in."""
+    g = torch.Generator(device=cuda_device).manual_seed(m * 7 + n)
+    a = torch.randn(80, k, device=cuda_device, generator=g).to(torch.bfloat16)
+    w = (torch.randn(n, k, device=cuda_device, generator=g) * 0.05).to(torch.bfloat16)
+    tiled = gemm.gemm_bi(a, w)                      # 80 rows: the tiled kernel
+    skinny = gemm.gemm_skinny(a[:m], w)
+    gemm.check_status(cuda_device)
+    assert torch.equal(skinny, tiled[:m])
+    ref = a[:m].float() @ w.float().t()
+    assert (skinny.float() - ref).abs().max().item() <= 0.02 * ref.abs().max().item() + 1e-3
+    # and gemm_bi routes small batches to it
+    assert torch.equal(gemm.gemm_bi(a[:m], w), tiled[:m])
+    monkeypatch.setenv("KA_GEMM_SKINNY", "0")
+    assert torch.equal(gemm.gemm_bi(a[:m], w), tiled[:m])

@@ -43,6 +43,10 @@ def test_generation_is_seeded_batch_invariant_and_consistent_with_prefill(cuda_d
     other = generate(model, prompts, sampler=SamplerBackend(seed=6), max_new_tokens=8, temperature=0.8, top_k=50,
                      top_p=0.95, group_size=2)
     assert not torch.equal(out["sequences"], other["sequences"])
+    # the captured decode graph replays exactly the launches of the eager loop
+    eager = generate(model, prompts, sampler=SamplerBackend(seed=5), max_new_tokens=8, temperature=0.8, top_k=50,
+                     top_p=0.95, group_size=2, cuda_graph=False)
+    assert torch.equal(out["sequences"], eager["sequences"]) and torch.equal(out["logp"], eager["logp"])
     # the log-prob recorded during decoding agrees with a fresh full forward over the sequence
     from kernel_align_b200.ops.fused_logp import lmhead_logp
 

@@ -58,6 +58,17 @@ def main():
         tfl = 2.0 * m * n * k / t / 1e9
         rec(name, t, tb, tfl / tf_burst, f"{tfl:.0f} TFLOP/s vs cuBLAS {2.0 * m * n * k / tb / 1e9:.0f}")
         del a, b
+    # decode-sized GEMMs (8 rows): the weight-streaming kernel against cuBLAS, in bytes of weights per second
+    from _common import time_cuda_graph
+    for name, (n, k) in {"gemm decode wqkv 8x6144x4096": (6144, 4096), "gemm decode gate_up 8x28672x4096": (28672, 4096),
+                         "gemm decode lm_head 8x128256x4096": (128256, 4096)}.items():
+        a = torch.randn(8, k, device=dev, generator=g).to(torch.bfloat16)
+        b = (torch.randn(n, k, device=dev, generator=g) * 0.02).to(torch.bfloat16)
+        t = time_cuda_graph(lambda: gemm.gemm_bi(a, b))
+        tb = time_cuda_graph(lambda: a @ b.t())
+        by = n * k * 2
+        rec(name, t, tb, by / t / 1e6 / hbm, f"{by / t / 1e6:.0f} GB/s of weights vs cuBLAS {by / tb / 1e6:.0f}")
+        del a, b
     # attention, B=16 L=512 and B=4 L=4096, 32q/8kv heads
     for b_, l in ((16, 512), (4, 4096)):
         q = torch.randn(b_, l, 32, 128, device=dev, generator=g).to(torch.bfloat16)

@@ -20,7 +20,7 @@ from _common import ROOT  # noqa: F401  (puts the repository root on sys.path)
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--op", required=True,
-                    choices=["fused_logp", "logits_logp", "sampling", "rmsnorm", "swiglu", "gemm", "attention",
+                    choices=["fused_logp", "logits_logp", "sampling", "rmsnorm", "swiglu", "gemm", "attention", "attention_bwd",
                              "grpo_loss"])
     ap.add_argument("--rows", type=int, default=4736)
     ap.add_argument("--vocab", type=int, default=128256)
@@ -69,6 +69,16 @@ def main():
         k = torch.randn(b_, l, 8, 128, device=dev, generator=g).to(torch.bfloat16)
         v = torch.randn(b_, l, 8, 128, device=dev, generator=g).to(torch.bfloat16)
         fn = lambda: attention(q, k, v)  # noqa: E731
+    elif args.op == "attention_bwd":
+        from kernel_align_b200.ops.attention import attention, attention_backward
+
+        b_, l = 2, args.rows if args.rows <= 8192 else 4096
+        q = torch.randn(b_, l, 32, 128, device=dev, generator=g).to(torch.bfloat16)
+        k = torch.randn(b_, l, 8, 128, device=dev, generator=g).to(torch.bfloat16)
+        v = torch.randn(b_, l, 8, 128, device=dev, generator=g).to(torch.bfloat16)
+        o, lse = attention(q, k, v, return_lse=True)
+        d_o = torch.randn_like(o)
+        fn = lambda: attention_backward(q, k, v, o, d_o, lse, causal=True)  # noqa: E731
     elif args.op == "gemm":
         from kernel_align_b200.ops.gemm import gemm_bi
 

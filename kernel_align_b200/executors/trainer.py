@@ -40,7 +40,8 @@ class GRPOTrainer:
         self.dp = data_parallel and dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1
         self.dp_rank = dist.get_rank() if self.dp else 0
         self.reducer = None
-        if self.dp:
+        self.on_cuda = next(model.parameters()).device.type == "cuda"
+        if self.dp and self.on_cuda:
             from ..parallel.collectives import GradReducer
 
             self.reducer = GradReducer(model.parameters(), bucket_bytes=bucket_bytes, average=True)
@@ -80,6 +81,15 @@ class GRPOTrainer:
         loss.backward()
         if self.reducer is not None:
             self.reducer.finish()
+        elif self.dp:
+            # CPU ranks (gloo): the same fixed-order sum, one tensor at a time, no overlap
+            from ..parallel.collectives import all_reduce_det
+
+            world = dist.get_world_size()
+            for p in self.model.parameters():
+                if p.grad is not None:
+                    all_reduce_det(p.grad)
+                    p.grad.div_(world)
         self.optimizer.step()
         self.step_index += 1
         tokens = roll["new_tokens"].numel()

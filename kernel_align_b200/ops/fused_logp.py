@@ -219,8 +219,6 @@ class _LmheadLogpFn(torch.autograd.Function):
         from . import gemm as _gemm
 
         hidden, weight, ids, lse = ctx.saved_tensors
-        if hidden.device.type != "cuda":
-            raise RuntimeError("backward of the fused log-prob runs on CUDA only; use PyTorch ops on CPU")
         k = hidden.shape[-1]
         h2 = hidden.reshape(-1, k).contiguous()
         m = h2.shape[0]
@@ -234,6 +232,22 @@ class _LmheadLogpFn(torch.autograd.Function):
         g32 = (g.reshape(-1).float() * valid).contiguous()
         lse32 = lse.reshape(-1).float().contiguous()
         w = weight.contiguous()
+        if hidden.device.type != "cuda":
+            # the same formula in PyTorch (d_logits rounded to bf16 like the kernel's output)
+            logits = float(ctx.scale) * (h2.float() @ w.float().t())
+            d_logits = -(g32 * float(ctx.scale))[:, None] * torch.exp(logits - lse32[:, None])
+            mine = valid & (ids64 >= lo) & (ids64 < hi)
+            rows = torch.nonzero(mine).flatten()
+            d_logits[rows, ids64[rows] - lo] += g32[rows] * float(ctx.scale)
+            d_logits = d_logits.to(torch.bfloat16).float()
+            d_hidden = (d_logits @ w.float()).to(hidden.dtype) if ctx.needs_input_grad[0] else None
+            d_weight = (d_logits.t() @ h2.float()).to(weight.dtype) if ctx.needs_input_grad[1] else None
+            if d_hidden is not None and world > 1:
+                from ..parallel.collectives import all_reduce_det
+
+                all_reduce_det(d_hidden, getattr(ctx.group, "process_group", None))
+            return (d_hidden.reshape(hidden.shape) if d_hidden is not None else None), d_weight, None, None, None, None, \
+                None, None
         lib = _native.cuda()
         fn = lib.ka_lmhead_logits_grad
         fn.restype = ctypes.c_int
@@ -281,10 +295,10 @@ def lmhead_logp(hidden: torch.Tensor, weight: torch.Tensor, ids: torch.Tensor, *
     hidden: ``[..., K]`` bf16; weight: ``[V_local, K]`` bf16 (this rank's vocabulary shard,
     whole canonical slices, see :func:`vocab_shard_range`); ids: ``[...]`` integer, global
     ids. Ids outside ``[0, vocab)`` give 0. Returns fp32 ``[...]`` (and the log-sum-exp if
-    ``return_lse``). Differentiable with respect to ``hidden`` and ``weight`` on CUDA.
+    ``return_lse``). Differentiable with respect to ``hidden`` and ``weight``.
     """
     needs_grad = torch.is_grad_enabled() and (hidden.requires_grad or weight.requires_grad)
-    if needs_grad and hidden.device.type == "cuda" and not return_lse and out is None:
+    if needs_grad and not return_lse and out is None:
         return _LmheadLogpFn.apply(hidden, weight, ids, float(scale), vocab, group, panel_rows, cta_group)
     return _lmhead_logp_forward(hidden, weight, ids, scale=scale, vocab=vocab, group=group, return_lse=return_lse,
                                 panel_rows=panel_rows, cta_group=cta_group, out=out, check=check)

@@ -133,7 +133,8 @@ def swiglu(gate_up: torch.Tensor, up: Optional[torch.Tensor] = None) -> torch.Te
 
 
 # --------------------------------------------------------------------------------------------
-# Differentiable wrappers (CUDA): forward and backward both run the hand-written kernels.
+# Differentiable wrappers: on CUDA forward and backward both run the hand-written kernels; on
+# CPU the forward is the C++ library and the backward the same formulas in PyTorch fp32.
 # --------------------------------------------------------------------------------------------
 class _RMSNormFn(torch.autograd.Function):
     @staticmethod
@@ -149,6 +150,13 @@ class _RMSNormFn(torch.autograd.Function):
         x2 = x.reshape(-1, d).contiguous()
         dy2 = dy.reshape(-1, d).contiguous()
         rows = x2.shape[0]
+        if x.device.type != "cuda":
+            xf, gf, wf = x2.float(), dy2.float(), weight.float()
+            r = torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + ctx.eps)
+            gw = gf * wf
+            dx = r * gw - xf * (r.pow(3) * (gw * xf).mean(-1, keepdim=True))
+            dw = (gf * xf * r).sum(0)
+            return dx.to(x.dtype).reshape(x.shape), dw.to(weight.dtype), None
         dx = torch.empty_like(x2)
         dw = torch.empty_like(weight)
         part = torch.empty((rows + 127) // 128, d, dtype=torch.float32, device=x.device)
@@ -162,7 +170,7 @@ class _RMSNormFn(torch.autograd.Function):
 
 def rmsnorm_fn(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
     """Differentiable RMSNorm (no fused residual; add the residual with ``+`` before it)."""
-    if x.device.type != "cuda" or not (x.requires_grad or weight.requires_grad) or not torch.is_grad_enabled():
+    if not (x.requires_grad or weight.requires_grad) or not torch.is_grad_enabled():
         return rmsnorm(x, weight, eps)
     return _RMSNormFn.apply(x, weight, eps)
 
@@ -199,6 +207,11 @@ class _SwigluFn(torch.autograd.Function):
         gu = gate_up.reshape(-1, 2 * f)
         d2 = d_out.reshape(-1, f).contiguous()
         rows = gu.shape[0]
+        if gate_up.device.type != "cuda":
+            g, u, d = gu[:, :f].float(), gu[:, f:].float(), d2.float()
+            sg = torch.sigmoid(g)
+            grad = torch.cat([d * u * sg * (1 + g * (1 - sg)), d * g * sg], 1)
+            return grad.to(gate_up.dtype).reshape(gate_up.shape)
         grad = torch.empty_like(gu)
         fn = _native.cuda().ka_swiglu_bwd
         fn.restype = c_int
@@ -211,6 +224,6 @@ class _SwigluFn(torch.autograd.Function):
 
 def swiglu_fn(gate_up: torch.Tensor) -> torch.Tensor:
     """Differentiable SwiGLU on a contiguous ``[..., 2F]`` tensor holding ``[gate | up]``."""
-    if gate_up.device.type != "cuda" or not gate_up.requires_grad or not torch.is_grad_enabled():
+    if not gate_up.requires_grad or not torch.is_grad_enabled():
         return swiglu(gate_up)
     return _SwigluFn.apply(gate_up.contiguous())

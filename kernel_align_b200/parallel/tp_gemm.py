@@ -8,6 +8,11 @@
 Kernels: ``csrc/sm100/tp_gemm.cu`` / ``gemm.cu``; peer buffers: :class:`PeerArena`. With
 ``world == 1`` the same kernels run on local buffers, which is what makes TP=1 and TP=8 agree
 bit for bit: K is always reduced as 8 canonical slices in one fixed tree order.
+
+CPU tensors take a PyTorch path with the same arithmetic contract (8 canonical K slices, each
+partial rounded to bf16, the fixed tree, residual added after rounding), exchanging over the
+process group's CPU backend (gloo): it is what the multi-process CPU tests run, and it is
+invariant in the number of ranks for the same reason the kernels are.
 """
 from __future__ import annotations
 
@@ -43,7 +48,12 @@ class TPContext:
             self.world = dist.get_world_size(self.group)
         else:
             self.group, self.rank, self.world = None, 0, 1
-        self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        if device is not None:
+            self.device = torch.device(device)
+        elif torch.cuda.is_available():
+            self.device = torch.device("cuda", torch.cuda.current_device())
+        else:
+            self.device = torch.device("cpu")
         self._arenas: dict = {}
 
     def arena(self, key, nbytes: int):
@@ -79,6 +89,39 @@ def _lib():
     return lib
 
 
+def _tree8(p: torch.Tensor) -> torch.Tensor:
+    """``p [8, ...]`` fp32 -> ((0+1)+(2+3))+((4+5)+(6+7))."""
+    return ((p[0] + p[1]) + (p[2] + p[3])) + ((p[4] + p[5]) + (p[6] + p[7]))
+
+
+def _gemm_reduce_scatter_cpu(x, w_shard, ctx, residual, trans_b, keep_padding):
+    m, k_local = x.shape
+    wf = w_shard.float().t() if trans_b else w_shard.float()          # [N, K_local]
+    n = wf.shape[0]
+    s_local = 8 // ctx.world
+    ks = k_local // s_local
+    xf = x.float()
+    parts = torch.stack([(xf[:, i * ks:(i + 1) * ks] @ wf[:, i * ks:(i + 1) * ks].t()).to(torch.bfloat16).float()
+                         for i in range(s_local)])                       # this rank's slices, rounded
+    if ctx.world > 1:
+        gathered = [torch.empty_like(parts) for _ in range(ctx.world)]
+        dist.all_gather(gathered, parts.contiguous(), group=ctx.group)
+        parts = torch.cat(gathered)
+    v = _tree8(parts)
+    rpr = rows_per_rank(m, ctx.world)
+    lo = ctx.rank * rpr
+    rows_valid = max(0, min(rpr, m - lo))
+    out = torch.zeros(rpr, n, dtype=torch.float32)
+    out[:rows_valid] = v[lo:lo + rows_valid]
+    if residual is not None:
+        res = residual.float()
+        if res.shape[0] < rpr:
+            res = torch.cat([res, res.new_zeros(rpr - res.shape[0], n)])
+        out = out.to(torch.bfloat16).float() + res[:rpr]
+    out = out.to(torch.bfloat16)
+    return out if keep_padding else out[:rows_valid]
+
+
 def gemm_reduce_scatter(x: torch.Tensor, w_shard: torch.Tensor, ctx: TPContext,
                         residual: Optional[torch.Tensor] = None, trans_b: bool = False,
                         keep_padding: bool = False) -> torch.Tensor:
@@ -86,14 +129,16 @@ def gemm_reduce_scatter(x: torch.Tensor, w_shard: torch.Tensor, ctx: TPContext,
 
     ``w_shard`` is ``[N, K_local]``, or ``[K_local, N]`` with ``trans_b``. ``keep_padding`` returns
     all ``rows_per_rank`` rows (a multiple of 128) instead of cutting at the end of the matrix."""
-    lib = _lib()
     m, k_local = x.shape
     n = w_shard.shape[1] if trans_b else w_shard.shape[0]
     if k_local % (8 // ctx.world * 64) != 0:
         raise ValueError("the K shard must split into whole 64-wide blocks per canonical slice")
+    if x.device.type != "cuda":
+        return _gemm_reduce_scatter_cpu(x, w_shard, ctx, residual, trans_b, keep_padding)
+    lib = _lib()
     x = x.contiguous()
     w = w_shard.contiguous()
-    rpr = lib.ka_gemm_rs_rows_per_rank(m, ctx.world)
+    rpr = rows_per_rank(m, ctx.world)
     nbytes = lib.ka_gemm_rs_exchange_bytes(m, n, ctx.world)
     arena, epoch = ctx.arena(("rs", m, n), nbytes)
     rows_valid = max(0, min(rpr, m - ctx.rank * rpr))
@@ -116,8 +161,10 @@ def gemm_reduce_scatter(x: torch.Tensor, w_shard: torch.Tensor, ctx: TPContext,
 
 
 def rows_per_rank(m: int, world: int) -> int:
-    """Rows of a reduce-scattered ``[m, n]`` result that each rank owns (multiple of 128)."""
-    return int(_lib().ka_gemm_rs_rows_per_rank(m, world))
+    """Rows of a reduce-scattered ``[m, n]`` result that each rank owns (multiple of 128; the
+    same rule as ``ka_gemm_rs_rows_per_rank``)."""
+    per = (m + world - 1) // world
+    return (per + 127) // 128 * 128
 
 
 def all_gather_gemm(x_local: torch.Tensor, w_shard: torch.Tensor, ctx: TPContext, trans_b: bool = False,
@@ -126,11 +173,22 @@ def all_gather_gemm(x_local: torch.Tensor, w_shard: torch.Tensor, ctx: TPContext
 
     ``w_shard`` is ``[N_local, K]``, or ``[K, N_local]`` with ``trans_b``. With ``return_gathered``
     also returns a copy of the gathered activations ``[world * rows, K]``."""
-    lib = _lib()
     rows, k = x_local.shape
     n_local = w_shard.shape[1] if trans_b else w_shard.shape[0]
     if rows % 128 != 0:
         raise ValueError("rows per rank must be a multiple of 128")
+    if x_local.device.type != "cuda":
+        from ..ops.gemm import gemm_bi
+
+        if ctx.world > 1:
+            pieces = [torch.empty_like(x_local) for _ in range(ctx.world)]
+            dist.all_gather(pieces, x_local.contiguous(), group=ctx.group)
+            x_full = torch.cat(pieces)
+        else:
+            x_full = x_local
+        out = gemm_bi(x_full, w_shard, trans_b=trans_b)
+        return (out, x_full.clone()) if return_gathered else out
+    lib = _lib()
     x = x_local.contiguous()
     w = w_shard.contiguous()
     nbytes = lib.ka_ag_gemm_exchange_bytes(rows, k, ctx.world)

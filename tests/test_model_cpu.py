@@ -1,0 +1,203 @@
+"""CPU tier for the model stack: the tiny Llama, its tensor-parallel layers over gloo, and a
+whole GRPO step, all on the CPU paths (C++ library forward, PyTorch-formula backward)."""
+import math
+import os
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+import torch.nn.functional as F
+
+from kernel_align_b200.executors.trainer import GRPOTrainer
+from kernel_align_b200.models.llama import LlamaConfig, LlamaModel
+from kernel_align_b200.ops.fused_logp import lmhead_logp
+from kernel_align_b200.parallel.tp_gemm import TPContext, all_gather_gemm, gemm_reduce_scatter, rows_per_rank
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+CPU = torch.device("cpu")
+
+
+def _cfg(layers=1):
+    return LlamaConfig(vocab_size=512, hidden=256, n_layers=layers, n_heads=4, n_kv_heads=2, head_dim=128, ffn=512,
+                       max_pos=256)
+
+
+def _ref_hidden(model, ids):
+    """Plain PyTorch fp32 forward of the same weights."""
+    cfg = model.cfg
+    hd = cfg.head_dim
+    b, l = ids.shape
+    x = model.embed.float()[ids.reshape(-1)]
+    cos, sin = model.rope_cos.float(), model.rope_sin.float()
+    pos = torch.arange(l).repeat(b)
+
+    def rms(v, w):
+        return v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + cfg.rms_eps) * w.float()
+
+    def rope(t):
+        h = hd // 2
+        c, s = cos[pos][:, None, :], sin[pos][:, None, :]
+        return torch.cat([t[..., :h] * c - t[..., h:] * s, t[..., h:] * c + t[..., :h] * s], -1)
+
+    for layer in model.layers:
+        hq, hkv = layer.hq, layer.hkv
+        qkv = rms(x, layer.norm1) @ layer.wqkv.float().t()
+        q = rope(qkv[:, : hq * hd].view(-1, hq, hd)).view(b, l, hq, hd).permute(0, 2, 1, 3)
+        k = rope(qkv[:, hq * hd:(hq + hkv) * hd].view(-1, hkv, hd)).view(b, l, hkv, hd).permute(0, 2, 1, 3)
+        v = qkv[:, (hq + hkv) * hd:].view(b, l, hkv, hd).permute(0, 2, 1, 3)
+        g = hq // hkv
+        a = F.scaled_dot_product_attention(q, k.repeat_interleave(g, 1), v.repeat_interleave(g, 1), is_causal=True)
+        x = x + a.permute(0, 2, 1, 3).reshape(-1, hq * hd) @ layer.wo.float().t()
+        gu = rms(x, layer.norm2) @ layer.wgu.float().t()
+        f = gu.shape[1] // 2
+        x = x + (F.silu(gu[:, :f]) * gu[:, f:]) @ layer.wdown.float().t()
+    return rms(x, model.norm)
+
+
+def test_cpu_model_matches_fp32_reference_and_has_repeatable_grads():
+    cfg = _cfg(layers=2)
+    model = LlamaModel(cfg, seed=1, device=CPU)
+    ids = torch.randint(0, cfg.vocab_size, (2, 48), generator=torch.Generator().manual_seed(2))
+    h = model.hidden_states(ids)[: ids.numel()]
+    ref = _ref_hidden(model, ids)
+    assert (h.float() - ref).abs().max().item() < 0.06 * ref.abs().max().item()
+    # a sequence's rows do not depend on the batch it is computed in
+    one = model.hidden_states(ids[1:2])[:48]
+    assert torch.equal(one, h[48:96])
+
+    def run():
+        model.zero_grad(set_to_none=True)
+        hh = model.hidden_states(ids)
+        loss = -lmhead_logp(hh[: ids.numel()], model.lm_head, ids.reshape(-1)).mean()
+        loss.backward()
+        return loss.detach().clone(), [p.grad.clone() for p in model.parameters()]
+
+    l1, g1 = run()
+    l2, g2 = run()
+    assert torch.isfinite(l1) and abs(l1.item() - math.log(cfg.vocab_size)) < 1.0
+    assert l1.item() == l2.item() and all(torch.equal(a, b) for a, b in zip(g1, g2))
+    assert len(g1) == len(list(model.parameters())) and all(torch.isfinite(t.float()).all() for t in g1)
+    # the gradient of the loss with respect to the LM head agrees with autograd of plain PyTorch
+    hf = model.hidden_states(ids)[: ids.numel()].detach().float()
+    wf = model.lm_head.detach().float().requires_grad_()
+    (-torch.log_softmax(hf @ wf.t(), -1).gather(1, ids.reshape(-1, 1)).mean()).backward()
+    assert (model.lm_head.grad.float() - wf.grad).abs().max().item() < 0.02 * wf.grad.abs().max().item() + 1e-4
+
+
+def test_cpu_grpo_step_is_repeatable():
+    cfg = _cfg()
+
+    def reward(prompts, new_tokens):
+        return (new_tokens % 7 == 0).float().mean(1) + 0.1 * (new_tokens[:, 0] % 3).float()
+
+    prompts = torch.randint(0, cfg.vocab_size, (2, 8), generator=torch.Generator().manual_seed(9))
+
+    def fresh():
+        return GRPOTrainer(LlamaModel(cfg, seed=2, device=CPU), reward, group_size=2, max_new_tokens=4,
+                           temperature=1.0, top_k=50, lr=1e-3, seed=3)
+
+    a, b = fresh(), fresh()
+    la = [a.train_step(prompts)["loss"].item() for _ in range(2)]
+    lb = [b.train_step(prompts)["loss"].item() for _ in range(2)]
+    assert all(math.isfinite(v) for v in la) and la == lb
+
+
+def _tp_worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.set_num_threads(2)
+    tp = TPContext(device=CPU)
+    g = torch.Generator().manual_seed(5)
+    m, k, n = 200, 1024, 96
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(n, k, generator=g) * 0.05).to(torch.bfloat16)
+    res = torch.randn(rows_per_rank(m, world) * world, n, generator=g).to(torch.bfloat16)
+    kl = k // world
+    rpr = rows_per_rank(m, world)
+    y = gemm_reduce_scatter(x[:, rank * kl:(rank + 1) * kl], w[:, rank * kl:(rank + 1) * kl], tp,
+                            residual=res[rank * rpr:(rank + 1) * rpr], keep_padding=True)
+    xl = torch.randn(128, 64, generator=torch.Generator().manual_seed(50 + rank)).to(torch.bfloat16)
+    wl = (torch.randn(32, 64, generator=torch.Generator().manual_seed(7)) * 0.1).to(torch.bfloat16)
+    z, gathered = all_gather_gemm(xl, wl, tp, return_gathered=True)
+    # a tiny tensor-parallel model: every rank's rows of the final hidden states
+    cfg = _cfg()
+    model = LlamaModel(cfg, tp=tp, seed=1, device=CPU)
+    ids = torch.randint(0, cfg.vocab_size, (2, 40), generator=torch.Generator().manual_seed(2))
+    h = model.hidden_states(ids)
+    torch.save({"y": y, "z": z, "gathered": gathered, "h": h}, os.path.join(out_dir, f"r{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2])
+def test_cpu_tensor_parallel_paths_match_single_rank(tmp_path, world):
+    mp.spawn(_tp_worker, args=(world, 29760 + world, str(tmp_path)), nprocs=world, join=True)
+    outs = [torch.load(tmp_path / f"r{r}.pt") for r in range(world)]
+    # single-rank results of the same problems
+    tp1 = TPContext.__new__(TPContext)
+    tp1.group, tp1.rank, tp1.world, tp1.device, tp1._arenas = None, 0, 1, CPU, {}
+    g = torch.Generator().manual_seed(5)
+    m, k, n = 200, 1024, 96
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(n, k, generator=g) * 0.05).to(torch.bfloat16)
+    res = torch.randn(rows_per_rank(m, world) * world, n, generator=g).to(torch.bfloat16)
+    rpr = rows_per_rank(m, world)
+    full = gemm_reduce_scatter(x, w, tp1, residual=res[: rows_per_rank(m, 1)], keep_padding=True)
+    for r in range(world):
+        lo = r * rpr
+        valid = max(0, min(rpr, m - lo))
+        # the reduction over K uses the same 8 slices and tree at every rank count: bit for bit
+        assert torch.equal(outs[r]["y"][:valid], full[lo:lo + valid])
+    xs = [torch.randn(128, 64, generator=torch.Generator().manual_seed(50 + r)).to(torch.bfloat16) for r in range(world)]
+    wl = (torch.randn(32, 64, generator=torch.Generator().manual_seed(7)) * 0.1).to(torch.bfloat16)
+    want = (torch.cat(xs).float() @ wl.float().t())
+    for r in range(world):
+        assert torch.equal(outs[r]["gathered"], torch.cat(xs))
+        assert (outs[r]["z"].float() - want).abs().max().item() < 0.02 * want.abs().max().item() + 1e-3
+    # the tensor-parallel model agrees with the single-rank model (to rounding: the column-parallel
+    # products run on library matmuls of different shapes)
+    cfg = _cfg()
+    model = LlamaModel(cfg, tp=tp1, seed=1, device=CPU)
+    ids = torch.randint(0, cfg.vocab_size, (2, 40), generator=torch.Generator().manual_seed(2))
+    h1 = model.hidden_states(ids)[:80].float()
+    h_tp = torch.cat([o["h"] for o in outs])[:80].float()
+    assert (h_tp - h1).abs().max().item() < 0.05 * h1.abs().max().item()
+
+
+def _dp_worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.set_num_threads(2)
+    cfg = _cfg()
+
+    def reward(prompts, new_tokens):
+        return (new_tokens % 5 == 0).float().mean(1) + 0.1 * (new_tokens[:, 0] % 3).float()
+
+    solo = TPContext.__new__(TPContext)
+    solo.group, solo.rank, solo.world, solo.device, solo._arenas = None, 0, 1, CPU, {}
+    model = LlamaModel(cfg, tp=solo, seed=4, device=CPU)
+    trainer = GRPOTrainer(model, reward, group_size=2, max_new_tokens=4, temperature=1.0, top_k=50, lr=1e-3, seed=3,
+                          data_parallel=True)
+    prompts = torch.randint(0, cfg.vocab_size, (2, 8), generator=torch.Generator().manual_seed(20 + rank))
+    losses = [trainer.train_step(prompts)["loss"].item() for _ in range(2)]
+    torch.save({"losses": losses, "w": model.layers[0].wqkv.detach().clone(), "head": model.lm_head.detach().clone()},
+               os.path.join(out_dir, f"r{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_cpu_data_parallel_grpo_keeps_ranks_in_step(tmp_path):
+    """Two gloo ranks with different prompts: after the fixed-order gradient all-reduce and the
+    optimizer step both hold bit-identical weights, and the weights moved."""
+    mp.spawn(_dp_worker, args=(2, 29775, str(tmp_path)), nprocs=2, join=True)
+    a, b = (torch.load(tmp_path / f"r{r}.pt") for r in range(2))
+    assert all(math.isfinite(v) for v in a["losses"] + b["losses"])
+    assert torch.equal(a["w"], b["w"]) and torch.equal(a["head"], b["head"])
+    fresh = LlamaModel(_cfg(), seed=4, device=CPU)
+    assert not torch.equal(fresh.layers[0].wqkv.detach(), a["w"])

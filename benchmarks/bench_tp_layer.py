@@ -54,19 +54,38 @@ def torch_layer(layer, tp, world):
     def rms(v, w):
         return F.rms_norm(v, (v.shape[-1],), w, cfg.rms_eps)
 
+    # differentiable collectives: the adjoint of an all-gather is a reduce-scatter and vice versa
+    class _Gather(torch.autograd.Function):
+        @staticmethod
+        def forward(ctx, x):
+            out = torch.empty(world * x.shape[0], x.shape[1], dtype=x.dtype, device=x.device)
+            dist.all_gather_into_tensor(out, x.contiguous())
+            return out
+
+        @staticmethod
+        def backward(ctx, g):
+            out = torch.empty(g.shape[0] // world, g.shape[1], dtype=g.dtype, device=g.device)
+            dist.reduce_scatter_tensor(out, g.contiguous())
+            return out
+
+    class _ScatterSum(torch.autograd.Function):
+        @staticmethod
+        def forward(ctx, y):
+            out = torch.empty(y.shape[0] // world, y.shape[1], dtype=y.dtype, device=y.device)
+            dist.reduce_scatter_tensor(out, y.contiguous())
+            return out
+
+        @staticmethod
+        def backward(ctx, g):
+            out = torch.empty(world * g.shape[0], g.shape[1], dtype=g.dtype, device=g.device)
+            dist.all_gather_into_tensor(out, g.contiguous())
+            return out
+
     def gather(x):
-        if world == 1:
-            return x
-        out = torch.empty(world * x.shape[0], x.shape[1], dtype=x.dtype, device=x.device)
-        dist.all_gather_into_tensor(out, x)
-        return out
+        return x if world == 1 else _Gather.apply(x)
 
     def scatter_sum(y):
-        if world == 1:
-            return y
-        out = torch.empty(y.shape[0] // world, y.shape[1], dtype=y.dtype, device=y.device)
-        dist.reduce_scatter_tensor(out, y)
-        return out
+        return y if world == 1 else _ScatterSum.apply(y)
 
     def fwd(x_local, batch, seq_len, cos, sin):
         tokens = batch * seq_len

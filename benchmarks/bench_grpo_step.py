@@ -5,6 +5,7 @@ forward/backward on the native kernels -> deterministic gradient all-reduce (dat
 
     python benchmarks/bench_grpo_step.py --layers 4 --prompts 8 --group 8
     torchrun --nproc-per-node 8 benchmarks/bench_grpo_step.py --layers 32 --prompts 1 --group 64
+    RL_ENGINE_PROFILE=basic python benchmarks/bench_grpo_step.py ...      # adds a per-operator table
 """
 from __future__ import annotations
 
@@ -73,6 +74,12 @@ def main():
            "rollouts": args.prompts * args.group * world, "new_tokens": args.new_tokens,
            "step_s": min(timings), "tokens_per_s": tokens / min(timings),
            "loss_run0": losses[0], "loss_run1": losses[1], "bitwise_equal": losses[0] == losses[1]}
+    from kernel_align_b200.utils.profiler import profiler
+
+    if profiler.enabled:      # RL_ENGINE_PROFILE=basic|detailed: per-operator device time, slowest rank
+        table = profiler.report(across_ranks=world > 1)
+        if rank == 0:
+            print(table)
     if rank == 0:
         print(json.dumps(res))
         write_json(args.json_out, res)

@@ -102,6 +102,37 @@ def build_cpu(force: bool = False) -> Path | None:
     return CPU_LIB
 
 
+def build_cpu_sanitized(force: bool = False) -> Path | None:
+    """The CPU library once more with AddressSanitizer and UndefinedBehaviorSanitizer
+    (``libka_cpu_asan.so``): the sanitizer tier of the tests loads it in a child process that
+    preloads the sanitizer runtime. Not used by the package itself."""
+    srcs = sorted((CSRC / "cpu").glob("*.cpp"))
+    cxx = shutil.which("g++")
+    if not srcs or cxx is None:
+        return None
+    flags = [f for f in CXX_FLAGS if not f.startswith("-O")] + ["-O1", "-g", "-fno-omit-frame-pointer",
+                                                                 "-fsanitize=address,undefined",
+                                                                 "-fno-sanitize-recover=undefined"]
+    deps = srcs + sorted((CSRC / "cpu").rglob("*.h"))
+    digest = _digest(deps, flags)
+    lib = LIB_DIR / "libka_cpu_asan.so"
+    if not force and _stamp_ok(lib, digest):
+        return lib
+    LIB_DIR.mkdir(parents=True, exist_ok=True)
+    _run([cxx, *flags, "-shared", "-o", str(lib), *[str(s) for s in srcs]])
+    lib.with_suffix(".hash").write_text(digest)
+    return lib
+
+
+def sanitizer_runtime() -> str | None:
+    """Path of the AddressSanitizer runtime to preload, or None without g++."""
+    cxx = shutil.which("g++")
+    if cxx is None:
+        return None
+    out = subprocess.run([cxx, "-print-file-name=libasan.so"], capture_output=True, text=True).stdout.strip()
+    return out if out and os.path.exists(out) else None
+
+
 def build_all(force: bool = False, verbose: bool = False) -> None:
     build_cpu(force)
     build_cuda(force, verbose)

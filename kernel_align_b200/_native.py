@@ -7,6 +7,7 @@ hand-written kernels are the only code path, there is no silent PyTorch fallback
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_char_p, c_float, c_int, c_longlong, c_size_t, c_uint, c_ulonglong, c_void_p
 from functools import lru_cache
 
@@ -71,6 +72,11 @@ def dtype_code(dtype) -> int:
 
 @lru_cache(maxsize=None)
 def cpu() -> ctypes.CDLL:
+    # KA_CPU_LIB points the process at another build of the same library (the sanitizer tier
+    # of the tests runs the CPU operators on an ASan / UBSan build in a child process)
+    override = os.environ.get("KA_CPU_LIB")
+    if override:
+        return ctypes.CDLL(override)
     path = _build.build_cpu()
     if path is None or not path.exists():
         raise NativeLibraryMissing("libka_cpu.so is not built and no C++ compiler is available")

@@ -21,6 +21,7 @@ from ..ops.decode import FusedAdamW
 from ..ops.fused_logp import lmhead_logp
 from ..ops.grpo_loss import group_advantages, grpo_loss
 from ..utils.logger import logger
+from ..utils.profiler import profile_range
 from .generation import generate
 
 
@@ -70,27 +71,32 @@ class GRPOTrainer:
 
     def train_step(self, prompts: torch.Tensor) -> dict:
         prompt_len = prompts.shape[1]
-        roll = self.rollout(prompts)
+        dev = prompts.device
+        with profile_range("grpo/rollout", dev):
+            roll = self.rollout(prompts)
         if self.reducer is not None:
             self.reducer.zero_grad()
         else:
             self.optimizer.zero_grad(set_to_none=True)
-        logp_new = self.policy_logp(roll["sequences"], prompt_len)
-        loss, stats = grpo_loss(logp_new, roll["logp"], roll["advantages"], eps_low=self.eps_clip, beta=self.beta,
-                                logp_ref=roll["logp"] if self.beta > 0 else None, return_stats=True)
-        loss.backward()
-        if self.reducer is not None:
-            self.reducer.finish()
-        elif self.dp:
-            # CPU ranks (gloo): the same fixed-order sum, one tensor at a time, no overlap
-            from ..parallel.collectives import all_reduce_det
+        with profile_range("grpo/policy_forward", dev):
+            logp_new = self.policy_logp(roll["sequences"], prompt_len)
+            loss, stats = grpo_loss(logp_new, roll["logp"], roll["advantages"], eps_low=self.eps_clip, beta=self.beta,
+                                    logp_ref=roll["logp"] if self.beta > 0 else None, return_stats=True)
+        with profile_range("grpo/backward_and_grad_reduce", dev):
+            loss.backward()
+            if self.reducer is not None:
+                self.reducer.finish()
+            elif self.dp:
+                # CPU ranks (gloo): the same fixed-order sum, one tensor at a time, no overlap
+                from ..parallel.collectives import all_reduce_det
 
-            world = dist.get_world_size()
-            for p in self.model.parameters():
-                if p.grad is not None:
-                    all_reduce_det(p.grad)
-                    p.grad.div_(world)
-        self.optimizer.step()
+                world = dist.get_world_size()
+                for p in self.model.parameters():
+                    if p.grad is not None:
+                        all_reduce_det(p.grad)
+                        p.grad.div_(world)
+        with profile_range("grpo/optimizer", dev):
+            self.optimizer.step()
         self.step_index += 1
         tokens = roll["new_tokens"].numel()
         return {"loss": loss.detach(), "clip_fraction": stats[1], "tokens": tokens,

@@ -12,11 +12,14 @@ from typing import Optional
 
 import torch
 
+from ..utils.profiler import profiled
+
 from .. import _native
 from .fused_logp import default_timeout_ns
 from .gemm import status_buffer
 
 
+@profiled("attention")
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool = True,
               scale: Optional[float] = None, return_lse: bool = False):
     """q ``[B, L, Hq, D]``, k / v ``[B, L, Hkv, D]`` -> ``[B, L, Hq, D]``.
@@ -66,6 +69,7 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool
     return (out, lse) if return_lse else out
 
 
+@profiled("attention_backward")
 def attention_backward(q, k, v, out, d_out, lse, *, causal: bool = True, scale: Optional[float] = None):
     """``(dq, dk, dv)`` from the saved forward results. CUDA: the tcgen05 kernels of
     ``csrc/sm100/attention_bwd.cu`` (a dQ kernel and a dK/dV kernel, no atomics, fixed

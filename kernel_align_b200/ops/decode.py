@@ -9,9 +9,12 @@ from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
 
+from ..utils.profiler import profiled
+
 from .. import _native
 
 
+@profiled("attention_decode")
 def attention_decode(q: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.Tensor, lens: torch.Tensor,
                      scale: float | None = None) -> torch.Tensor:
     """q ``[B, Hq, D]``; caches ``[B, max_len, Hkv, D]``; ``lens [B]`` int32 = keys to attend to."""

@@ -20,6 +20,8 @@ from typing import Optional
 
 import torch
 
+from ..utils.profiler import profiled
+
 from .. import _native
 
 N_SLICES = 8
@@ -286,6 +288,7 @@ class _LmheadLogpFn(torch.autograd.Function):
         return (d_hidden.reshape(hidden.shape) if need_dh else None), d_weight, None, None, None, None, None, None
 
 
+@profiled("lmhead_logp")
 def lmhead_logp(hidden: torch.Tensor, weight: torch.Tensor, ids: torch.Tensor, *, scale: float = 1.0,
                 vocab: Optional[int] = None, group: Optional[VocabParallel] = None, return_lse: bool = False,
                 panel_rows: int = DEFAULT_PANEL_ROWS, cta_group: int = 2, out: Optional[torch.Tensor] = None,

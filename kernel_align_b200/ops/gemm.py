@@ -22,6 +22,8 @@ from ctypes import c_int, c_longlong, c_ulonglong, c_void_p
 
 import torch
 
+from ..utils.profiler import profiled
+
 from .. import _native
 from .fused_logp import default_timeout_ns
 
@@ -63,6 +65,7 @@ def _skinny_fn():
     return fn
 
 
+@profiled("gemm_skinny")
 def gemm_skinny(a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     """``a [M <= 64, K] @ w[N, K].T`` on the weight-streaming kernel (bf16 in, bf16 out)."""
     m, k = a.shape
@@ -80,6 +83,7 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     return out
 
 
+@profiled("gemm_bi")
 def gemm_bi(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bool = False,
             out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
     """``op(a) @ op(b).T`` with ``op(a) = a.T if trans_a`` (a stored ``[K, M]``) and

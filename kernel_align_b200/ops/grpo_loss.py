@@ -11,6 +11,8 @@ from typing import Optional
 
 import torch
 
+from ..utils.profiler import profiled
+
 from .. import _native
 
 
@@ -98,6 +100,7 @@ class _GrpoLossFn(torch.autograd.Function):
         return grad, None, None, None, None, None, None, None, None
 
 
+@profiled("grpo_loss")
 def grpo_loss(logp_new: torch.Tensor, logp_old: torch.Tensor, advantages: torch.Tensor, *,
               mask: Optional[torch.Tensor] = None, logp_ref: Optional[torch.Tensor] = None, eps_low: float = 0.2,
               eps_high: Optional[float] = None, beta: float = 0.0, reduction: str = "token_mean",

@@ -13,6 +13,8 @@ from typing import Optional
 
 import torch
 
+from ..utils.profiler import profiled
+
 from .. import _native
 
 
@@ -29,6 +31,7 @@ def _check(rc: int, name: str) -> None:
         raise RuntimeError(f"{name} failed ({rc})")
 
 
+@profiled("rmsnorm")
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5, residual: Optional[torch.Tensor] = None):
     """``y = rmsnorm(x + residual) * weight``. With ``residual`` returns ``(y, x + residual)``."""
     d = x.shape[-1]
@@ -72,6 +75,7 @@ def rope_tables(max_pos: int, head_dim: int, theta: float = 500000.0, device="cp
     return ang.cos().float().to(device), ang.sin().float().to(device)
 
 
+@profiled("rope")
 def rope_(x: torch.Tensor, positions: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
     """Rotate ``x`` ``[tokens, heads, head_dim]`` in place ("rotate half" convention)."""
     tokens, heads, hd = x.shape
@@ -97,6 +101,7 @@ def rope_(x: torch.Tensor, positions: torch.Tensor, cos: torch.Tensor, sin: torc
     return x
 
 
+@profiled("swiglu")
 def swiglu(gate_up: torch.Tensor, up: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``silu(gate) * up``. Either one ``[..., 2F]`` tensor holding ``[gate | up]`` or two ``[..., F]``."""
     if up is None:

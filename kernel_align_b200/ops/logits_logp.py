@@ -9,9 +9,12 @@ from __future__ import annotations
 
 import torch
 
+from ..utils.profiler import profiled
+
 from .. import _native
 
 
+@profiled("logits_logp")
 def logits_logp(logits: torch.Tensor, ids: torch.Tensor, *, scale: float = 1.0, return_lse: bool = False):
     """logits ``[..., V]`` (fp32 / bf16 / fp16), ids ``[...]`` -> fp32 ``[...]``.
 

@@ -14,9 +14,12 @@ from typing import Optional
 
 import torch
 
+from ..utils.profiler import profiled
+
 from .. import _native
 
 
+@profiled("sample")
 def sample(
     logits: torch.Tensor,
     *,

@@ -20,6 +20,8 @@ from ctypes import c_int, c_longlong, c_size_t, c_uint, c_ulonglong, c_void_p
 from typing import Iterable, Optional, Sequence
 
 import torch
+
+from ..utils.profiler import profiled
 import torch.distributed as dist
 
 from .. import _native
@@ -89,6 +91,7 @@ class SymmetricVector:
 _scratch: dict = {}
 
 
+@profiled("all_reduce_det")
 def all_reduce_det(tensor: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
     """Fixed-order sum of ``tensor`` over ``group``, in place; every rank gets the same bits."""
     if not (dist.is_available() and dist.is_initialized()):

@@ -21,6 +21,8 @@ from ctypes import c_int, c_longlong, c_size_t, c_uint, c_ulonglong, c_void_p
 from typing import Optional
 
 import torch
+
+from ..utils.profiler import profiled
 import torch.distributed as dist
 
 from .. import _native
@@ -122,6 +124,7 @@ def _gemm_reduce_scatter_cpu(x, w_shard, ctx, residual, trans_b, keep_padding):
     return out if keep_padding else out[:rows_valid]
 
 
+@profiled("gemm_reduce_scatter")
 def gemm_reduce_scatter(x: torch.Tensor, w_shard: torch.Tensor, ctx: TPContext,
                         residual: Optional[torch.Tensor] = None, trans_b: bool = False,
                         keep_padding: bool = False) -> torch.Tensor:
@@ -167,6 +170,7 @@ def rows_per_rank(m: int, world: int) -> int:
     return (per + 127) // 128 * 128
 
 
+@profiled("all_gather_gemm")
 def all_gather_gemm(x_local: torch.Tensor, w_shard: torch.Tensor, ctx: TPContext, trans_b: bool = False,
                     return_gathered: bool = False):
     """``all_gather(x_local, dim=0) @ w_shard.T``; ``x_local`` rows must be a multiple of 128.

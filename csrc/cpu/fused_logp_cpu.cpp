@@ -54,33 +54,35 @@ inline void merge(State& a, const State& b) {
   a.m = mn;
 }
 
-// log-sum-exp of one row of scaled logits given through a column accessor
+// State of canonical slice `sl` of one row of scaled logits given through a column accessor:
+// 1792-column sub-slices, each folded in groups of 32 columns, merged left to right.
 template <typename LogitAt>
-inline float row_lse(int v, LogitAt&& at) {
+inline State slice_state(int v, int sl, LogitAt&& at) {
   const int vs = (v + kSlices - 1) / kSlices;
-  State slice[kSlices];
+  const int s_begin = std::min(v, sl * vs), s_end = std::min(v, (sl + 1) * vs);
   float buf[kGroup];
-  for (int sl = 0; sl < kSlices; ++sl) {
-    const int s_begin = std::min(v, sl * vs), s_end = std::min(v, (sl + 1) * vs);
-    State acc;
-    bool first = true;
-    for (int c0 = s_begin; c0 < s_end; c0 += kSubCols) {
-      State sub;
-      const int c1 = std::min(c0 + kSubCols, s_end);
-      for (int g = c0; g < c1; g += kGroup) {
-        const int n = std::min(kGroup, c1 - g);
-        for (int j = 0; j < n; ++j) buf[j] = at(g + j);
-        fold_group(sub, buf, n);
-      }
-      if (first) {
-        acc = sub;
-        first = false;
-      } else {
-        merge(acc, sub);
-      }
+  State acc;
+  bool first = true;
+  for (int c0 = s_begin; c0 < s_end; c0 += kSubCols) {
+    State sub;
+    const int c1 = std::min(c0 + kSubCols, s_end);
+    for (int g = c0; g < c1; g += kGroup) {
+      const int n = std::min(kGroup, c1 - g);
+      for (int j = 0; j < n; ++j) buf[j] = at(g + j);
+      fold_group(sub, buf, n);
     }
-    slice[sl] = acc;
+    if (first) {
+      acc = sub;
+      first = false;
+    } else {
+      merge(acc, sub);
+    }
   }
+  return acc;
+}
+
+// The eight slice states of a row -> its log-sum-exp, by the balanced tree.
+inline float tree_lse(State (&slice)[kSlices]) {
   for (int w = kSlices; w > 1; w >>= 1)
     for (int i = 0; i < w / 2; ++i) {
       State a = slice[2 * i];
@@ -88,6 +90,14 @@ inline float row_lse(int v, LogitAt&& at) {
       slice[i] = a;
     }
   return slice[0].m + std::log(slice[0].l);
+}
+
+// log-sum-exp of one row of scaled logits given through a column accessor
+template <typename LogitAt>
+inline float row_lse(int v, LogitAt&& at) {
+  State slice[kSlices];
+  for (int sl = 0; sl < kSlices; ++sl) slice[sl] = slice_state(v, sl, at);
+  return tree_lse(slice);
 }
 
 template <typename F>
@@ -150,5 +160,57 @@ extern "C" int ka_cpu_logits_logp(const float* logits, long long row_stride, int
       logp[r] = (id >= 0 && id < v) ? x[id] * scale - row_l : 0.f;
     }
   });
+  return 0;
+}
+
+// Vocabulary-parallel form, one shard: weight_shard holds rows [v_lo, v_lo + v_local) of the
+// LM head, which must be whole canonical slices of the v_global-column vocabulary (slices
+// slice0 .. slice0 + n_slices - 1). Writes, per row, the (max, sum) state of each of those
+// slices into states[m][n_slices][2] and the scaled logit of the row's id into target[m] when
+// the id lies in this shard (0 otherwise). The arithmetic is the single-process one.
+extern "C" int ka_cpu_lmhead_logp_shard(const float* hidden, const float* weight_shard, const long long* ids,
+                                        float* states, float* target, int m, int k, int v_global, int v_lo,
+                                        int v_local, float scale, int threads) {
+  if (m <= 0) return 0;
+  if (k <= 0 || v_global <= 0 || v_local < 0 || !(scale > 0.f)) return -1;
+  const int vs = (v_global + kSlices - 1) / kSlices;
+  if (v_lo % vs != 0) return -2;
+  const int slice0 = v_lo / vs;
+  const int n_slices = (v_local + vs - 1) / vs;
+  if (v_lo + v_local != std::min(v_global, (slice0 + n_slices) * vs) && v_local != 0) return -2;
+  parallel_rows(m, threads, [&](int lo, int hi) {
+    std::vector<float> logits(static_cast<size_t>(std::max(1, v_local)));
+    for (int r = lo; r < hi; ++r) {
+      const float* h = hidden + static_cast<size_t>(r) * k;
+      for (int c = 0; c < v_local; ++c)
+        logits[c] = dot_fixed(h, weight_shard + static_cast<size_t>(c) * k, k) * scale;
+      for (int i = 0; i < n_slices; ++i) {
+        const State st = slice_state(v_global, slice0 + i, [&](int c) { return logits[c - v_lo]; });
+        states[(static_cast<size_t>(r) * n_slices + i) * 2] = st.m;
+        states[(static_cast<size_t>(r) * n_slices + i) * 2 + 1] = st.l;
+      }
+      const long long id = ids[r];
+      target[r] = (id >= v_lo && id < v_lo + v_local) ? logits[id - v_lo] : 0.f;
+    }
+  });
+  return 0;
+}
+
+// Merge step of the vocabulary-parallel form: states[m][8][2] in slice order (every rank's
+// slices, concatenated in rank order), target[m] = sum over ranks of their target logits (only
+// one is non-zero) -> logp, lse. Ids outside [0, v_global) give logp = 0.
+extern "C" int ka_cpu_lmhead_logp_merge(const float* states, const float* target, const long long* ids, float* logp,
+                                        float* lse, int m, int v_global) {
+  for (int r = 0; r < m; ++r) {
+    State slice[kSlices];
+    for (int i = 0; i < kSlices; ++i) {
+      slice[i].m = states[(static_cast<size_t>(r) * kSlices + i) * 2];
+      slice[i].l = states[(static_cast<size_t>(r) * kSlices + i) * 2 + 1];
+    }
+    const float row_l = tree_lse(slice);
+    if (lse) lse[r] = row_l;
+    const long long id = ids[r];
+    logp[r] = (id >= 0 && id < v_global) ? target[r] - row_l : 0.f;
+  }
   return 0;
 }

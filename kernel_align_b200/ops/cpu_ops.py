@@ -42,6 +42,47 @@ def lmhead_logp_cpu(hidden, weight, ids, *, scale: float = 1.0, chunk_rows: int 
     return (logp, lse) if return_lse else logp
 
 
+def lmhead_logp_shard_cpu(hidden, weight_shard, ids, *, vocab: int, v_lo: int, scale: float = 1.0):
+    """One rank's part of the vocabulary-parallel log-prob: ``(states [m, n_slices, 2], target [m])``,
+    the (max, sum) state of each canonical slice this shard holds and the scaled logit of the
+    row's id when it lies in the shard (see ``ka_cpu_lmhead_logp_shard``)."""
+    lib = _native.cpu()
+    h, w, i64 = _f32(hidden), _f32(weight_shard), _i64(ids)
+    m, k = h.shape
+    v_local = w.shape[0]
+    vs = -(-vocab // 8)
+    n_slices = -(-v_local // vs) if v_local else 0
+    states = torch.empty(m, n_slices, 2, dtype=torch.float32)
+    target = torch.empty(m, dtype=torch.float32)
+    fn = lib.ka_cpu_lmhead_logp_shard
+    fn.restype = c_int
+    fn.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int]
+    rc = fn(h.data_ptr(), w.data_ptr(), i64.data_ptr(), states.data_ptr(), target.data_ptr(), m, k, int(vocab),
+            int(v_lo), v_local, float(scale), _threads())
+    if rc != 0:
+        raise RuntimeError(f"ka_cpu_lmhead_logp_shard failed ({rc}): the shard must be whole canonical slices")
+    return states, target
+
+
+def lmhead_logp_merge_cpu(states, target, ids, *, vocab: int, return_lse: bool = False):
+    """Merge the eight slice states of every row (``states [m, 8, 2]`` in slice order) by the
+    canonical tree and subtract from the target logit: the last step of the vocabulary-parallel
+    log-prob, the same arithmetic as the single-process path."""
+    lib = _native.cpu()
+    st, tg, i64 = _f32(states), _f32(target), _i64(ids)
+    m = st.shape[0]
+    if st.shape[1:] != (8, 2):
+        raise ValueError("states must be [m, 8, 2]")
+    logp = torch.empty(m, dtype=torch.float32)
+    lse = torch.empty(m, dtype=torch.float32)
+    fn = lib.ka_cpu_lmhead_logp_merge
+    fn.restype = c_int
+    fn.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int]
+    if fn(st.data_ptr(), tg.data_ptr(), i64.data_ptr(), logp.data_ptr(), lse.data_ptr(), m, int(vocab)) != 0:
+        raise RuntimeError("ka_cpu_lmhead_logp_merge failed")
+    return (logp, lse) if return_lse else logp
+
+
 def logits_logp_cpu(logits, ids, *, scale: float = 1.0, return_lse: bool = False):
     lib = _native.cpu()
     x = _f32(logits)

@@ -106,6 +106,7 @@ class VocabParallel:
     exchange_ptrs: list[int] = field(default_factory=list)
     epoch: int = 1
     panel_rows: int = DEFAULT_PANEL_ROWS
+    process_group: object = None   # torch.distributed group (None: the default group); CPU path and backward
 
 
 def _lmhead_logp_forward(
@@ -146,7 +147,31 @@ def _lmhead_logp_forward(
         from . import cpu_ops
 
         if world != 1:
-            raise ValueError("the CPU path computes the full vocabulary in one process")
+            # vocabulary parallel over the CPU backend of torch.distributed (gloo): every rank
+            # computes the states of its canonical slices, all ranks gather the eight of them in
+            # slice order and merge them with the same tree as a single process would
+            import torch.distributed as dist
+
+            pg = getattr(group, "process_group", None)
+            states, target = cpu_ops.lmhead_logp_shard_cpu(h2, weight, ids.reshape(-1), vocab=v_global, v_lo=lo,
+                                                           scale=scale)
+            per = N_SLICES // world
+            if states.shape[1] < per:      # a trailing shard with fewer (or no) columns: empty slices
+                pad = torch.zeros(m, per - states.shape[1], 2)
+                pad[..., 0] = float("-inf")
+                states = torch.cat([states, pad], 1)
+            all_states = [torch.empty_like(states) for _ in range(world)]
+            all_targets = [torch.empty_like(target) for _ in range(world)]
+            dist.all_gather(all_states, states.contiguous(), group=pg)
+            dist.all_gather(all_targets, target, group=pg)
+            tsum = all_targets[0].clone()
+            for t in all_targets[1:]:
+                tsum += t
+            res = cpu_ops.lmhead_logp_merge_cpu(torch.cat(all_states, 1), tsum, ids.reshape(-1), vocab=v_global,
+                                                return_lse=return_lse)
+            if return_lse:
+                return res[0].reshape(lead), res[1].reshape(lead)
+            return res.reshape(lead)
         res = cpu_ops.lmhead_logp_cpu(h2, weight, ids.reshape(-1), scale=scale, return_lse=return_lse)
         if return_lse:
             return res[0].reshape(lead), res[1].reshape(lead)

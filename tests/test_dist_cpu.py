@@ -119,3 +119,54 @@ def test_tree_sum_order():
     assert tree_sum(parts).item() == ((torch.tensor(1e8) + 1.0) + (torch.tensor(-1e8) + 1.0)).item()
     with pytest.raises(ValueError):
         tree_sum(parts[:3])
+
+
+def _vp_worker(rank, world, port, out_dir):
+    _init(rank, world, port)
+    from kernel_align_b200.ops.fused_logp import VocabParallel, lmhead_logp, vocab_shard_range
+
+    g = torch.Generator().manual_seed(11)
+    m, k, v = 21, 72, 1003
+    hidden = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    weight = (torch.randn(v, k, generator=g) * 0.1).to(torch.bfloat16)
+    ids = torch.randint(-1, v + 1, (m,), generator=g)
+    lo, hi = vocab_shard_range(v, rank, world)
+    group = VocabParallel(rank=rank, world=world)
+    logp, lse = lmhead_logp(hidden, weight[lo:hi], ids, vocab=v, group=group, scale=1.3, return_lse=True)
+    # gradients: every rank gets the complete d_hidden (fixed-order sum over the shards)
+    h = hidden.clone().requires_grad_()
+    w = weight[lo:hi].clone().requires_grad_()
+    lmhead_logp(h, w, ids, vocab=v, group=group, scale=1.3).sum().backward()
+    torch.save({"logp": logp, "lse": lse, "dh": h.grad, "dw": w.grad, "lo": lo, "hi": hi},
+               os.path.join(out_dir, f"r{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_vocab_parallel_logp_gloo_bitwise_equals_single_process(tmp_path, world):
+    """The (max, sum-exp, target) merge across vocabulary shards, run by gloo ranks on the CPU
+    library: every world size gives the bits of a single process."""
+    from kernel_align_b200.ops.fused_logp import lmhead_logp
+
+    mp.spawn(_vp_worker, args=(world, 29720 + world, str(tmp_path)), nprocs=world, join=True)
+    g = torch.Generator().manual_seed(11)
+    m, k, v = 21, 72, 1003
+    hidden = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    weight = (torch.randn(v, k, generator=g) * 0.1).to(torch.bfloat16)
+    ids = torch.randint(-1, v + 1, (m,), generator=g)
+    logp, lse = lmhead_logp(hidden, weight, ids, scale=1.3, return_lse=True)
+    h = hidden.clone().requires_grad_()
+    w = weight.clone().requires_grad_()
+    lmhead_logp(h, w, ids, scale=1.3).sum().backward()
+    outs = [torch.load(tmp_path / f"r{r}.pt") for r in range(world)]
+    for o in outs:
+        assert torch.equal(o["logp"], logp) and torch.equal(o["lse"], lse)
+        assert (o["dh"].float() - h.grad.float()).abs().max().item() <= 0.02 * h.grad.float().abs().max().item() + 1e-3
+        assert torch.equal(o["dh"], outs[0]["dh"])            # identical on every rank
+        assert (o["dw"].float() - w.grad[o["lo"]:o["hi"]].float()).abs().max().item() <= \
+            0.02 * w.grad.float().abs().max().item() + 1e-3
+    ref = torch.log_softmax(1.3 * hidden.float() @ weight.float().t(), -1)
+    valid = (ids >= 0) & (ids < v)
+    want = torch.where(valid, ref.gather(1, ids.clamp(0, v - 1)[:, None])[:, 0], torch.zeros(()))
+    assert (logp - want).abs().max().item() < 1e-4

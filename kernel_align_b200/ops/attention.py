@@ -12,11 +12,10 @@ from typing import Optional
 
 import torch
 
-from ..utils.profiler import profiled
-
 from .. import _native
 from .fused_logp import default_timeout_ns
 from .gemm import status_buffer
+from ..utils.profiler import profiled
 
 
 @profiled("attention")

@@ -9,9 +9,8 @@ from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
 
-from ..utils.profiler import profiled
-
 from .. import _native
+from ..utils.profiler import profiled
 
 
 @profiled("attention_decode")

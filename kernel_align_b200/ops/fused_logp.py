@@ -20,9 +20,8 @@ from typing import Optional
 
 import torch
 
-from ..utils.profiler import profiled
-
 from .. import _native
+from ..utils.profiler import profiled
 
 N_SLICES = 8
 DEFAULT_PANEL_ROWS = 32768

@@ -22,10 +22,9 @@ from ctypes import c_int, c_longlong, c_ulonglong, c_void_p
 
 import torch
 
-from ..utils.profiler import profiled
-
 from .. import _native
 from .fused_logp import default_timeout_ns
+from ..utils.profiler import profiled
 
 _status: dict[int, torch.Tensor] = {}
 

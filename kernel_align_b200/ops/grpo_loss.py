@@ -11,9 +11,8 @@ from typing import Optional
 
 import torch
 
-from ..utils.profiler import profiled
-
 from .. import _native
+from ..utils.profiler import profiled
 
 
 def group_advantages(rewards: torch.Tensor, group_size: int, eps: float = 1e-4) -> torch.Tensor:

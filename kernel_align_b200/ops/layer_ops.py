@@ -13,9 +13,8 @@ from typing import Optional
 
 import torch
 
-from ..utils.profiler import profiled
-
 from .. import _native
+from ..utils.profiler import profiled
 
 
 def _sms(t: torch.Tensor) -> int:
@@ -184,8 +183,7 @@ class _RopeFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, positions, cos, sin):
         ctx.save_for_backward(positions, cos, sin)
-        out = x.clone() if not x.is_contiguous() else x.clone()
-        return rope_(out, positions, cos, sin)
+        return rope_(x.clone(memory_format=torch.contiguous_format), positions, cos, sin)
 
     @staticmethod
     def backward(ctx, dy):

@@ -9,9 +9,8 @@ from __future__ import annotations
 
 import torch
 
-from ..utils.profiler import profiled
-
 from .. import _native
+from ..utils.profiler import profiled
 
 
 @profiled("logits_logp")

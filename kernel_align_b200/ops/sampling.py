@@ -14,9 +14,8 @@ from typing import Optional
 
 import torch
 
-from ..utils.profiler import profiled
-
 from .. import _native
+from ..utils.profiler import profiled
 
 
 @profiled("sample")

@@ -20,12 +20,11 @@ from ctypes import c_int, c_longlong, c_size_t, c_uint, c_ulonglong, c_void_p
 from typing import Iterable, Optional, Sequence
 
 import torch
-
-from ..utils.profiler import profiled
 import torch.distributed as dist
 
 from .. import _native
 from ..ops.fused_logp import default_timeout_ns
+from ..utils.profiler import profiled
 
 
 def tree_sum(parts: Sequence[torch.Tensor]) -> torch.Tensor:

@@ -21,13 +21,12 @@ from ctypes import c_int, c_longlong, c_size_t, c_uint, c_ulonglong, c_void_p
 from typing import Optional
 
 import torch
-
-from ..utils.profiler import profiled
 import torch.distributed as dist
 
 from .. import _native
 from ..ops.fused_logp import default_timeout_ns
 from ..ops.gemm import status_buffer
+from ..utils.profiler import profiled
 
 
 class _LocalArena:

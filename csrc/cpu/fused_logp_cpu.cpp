@@ -100,6 +100,21 @@ inline float row_lse(int v, LogitAt&& at) {
   return tree_lse(slice);
 }
 
+// out[r][c] = scale * <h_r, w_c> for nr rows and v columns. Columns are the outer loop so that a
+// weight row is read once per chunk of rows; every dot product is still dot_fixed, so the
+// result does not depend on nr. Compiled once more for AVX2 hosts (the eight accumulation
+// lanes become one vector; the arithmetic and its order are the same, there is no FMA).
+#if defined(__GNUC__) && defined(__x86_64__)
+__attribute__((target_clones("avx2", "default")))
+#endif
+void logits_chunk(const float* h, const float* w, float* out, int nr, int k, int v, int out_stride, float scale) {
+  for (int c = 0; c < v; ++c) {
+    const float* wc = w + static_cast<size_t>(c) * k;
+    for (int r = 0; r < nr; ++r)
+      out[static_cast<size_t>(r) * out_stride + c] = dot_fixed(h + static_cast<size_t>(r) * k, wc, k) * scale;
+  }
+}
+
 template <typename F>
 void parallel_rows(int rows, int threads, F&& f) {
   threads = std::max(1, std::min(threads, rows));
@@ -129,11 +144,7 @@ extern "C" int ka_cpu_lmhead_logp(const float* hidden, const float* weight, cons
     std::vector<float> logits(static_cast<size_t>(chunk_rows) * v);
     for (int r0 = lo; r0 < hi; r0 += chunk_rows) {
       const int nr = std::min(chunk_rows, hi - r0);
-      for (int r = 0; r < nr; ++r) {
-        const float* h = hidden + static_cast<size_t>(r0 + r) * k;
-        float* out = logits.data() + static_cast<size_t>(r) * v;
-        for (int c = 0; c < v; ++c) out[c] = dot_fixed(h, weight + static_cast<size_t>(c) * k, k) * scale;
-      }
+      logits_chunk(hidden + static_cast<size_t>(r0) * k, weight, logits.data(), nr, k, v, v, scale);
       for (int r = 0; r < nr; ++r) {
         const float* x = logits.data() + static_cast<size_t>(r) * v;
         const float row_l = row_lse(v, [&](int c) { return x[c]; });
@@ -182,8 +193,7 @@ extern "C" int ka_cpu_lmhead_logp_shard(const float* hidden, const float* weight
     std::vector<float> logits(static_cast<size_t>(std::max(1, v_local)));
     for (int r = lo; r < hi; ++r) {
       const float* h = hidden + static_cast<size_t>(r) * k;
-      for (int c = 0; c < v_local; ++c)
-        logits[c] = dot_fixed(h, weight_shard + static_cast<size_t>(c) * k, k) * scale;
+      logits_chunk(h, weight_shard, logits.data(), 1, k, v_local, v_local, scale);
       for (int i = 0; i < n_slices; ++i) {
         const State st = slice_state(v_global, slice0 + i, [&](int c) { return logits[c - v_lo]; });
         states[(static_cast<size_t>(r) * n_slices + i) * 2] = st.m;

@@ -88,9 +88,13 @@ def gemm_bi(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b:
     """``op(a) @ op(b).T`` with ``op(a) = a.T if trans_a`` (a stored ``[K, M]``) and
     ``op(b) = b.T if trans_b`` (b stored ``[K, N]``). 2-D bf16 inputs, row-major."""
     if a.device.type != "cuda":
+        # the C++ library's GEMM: every dot product in one fixed order, so a row's result does not
+        # depend on the batch here either (a BLAS call may block differently for different M)
+        from . import cpu_ops
+
         af = a.float().t() if trans_a else a.float()
         bf = b.float().t() if trans_b else b.float()
-        return (af @ bf.t()).to(out_dtype)
+        return cpu_ops.gemm_cpu(af.contiguous(), bf.contiguous()).to(out_dtype)
     if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
         raise TypeError("gemm_bi takes bf16 operands")
     a = a if a.stride(-1) == 1 else a.contiguous()

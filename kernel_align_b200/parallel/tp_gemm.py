@@ -102,7 +102,10 @@ def _gemm_reduce_scatter_cpu(x, w_shard, ctx, residual, trans_b, keep_padding):
     s_local = 8 // ctx.world
     ks = k_local // s_local
     xf = x.float()
-    parts = torch.stack([(xf[:, i * ks:(i + 1) * ks] @ wf[:, i * ks:(i + 1) * ks].t()).to(torch.bfloat16).float()
+    from ..ops import cpu_ops
+
+    parts = torch.stack([cpu_ops.gemm_cpu(xf[:, i * ks:(i + 1) * ks].contiguous(),
+                                          wf[:, i * ks:(i + 1) * ks].contiguous()).to(torch.bfloat16).float()
                          for i in range(s_local)])                       # this rank's slices, rounded
     if ctx.world > 1:
         gathered = [torch.empty_like(parts) for _ in range(ctx.world)]

@@ -18,7 +18,6 @@ import torch.distributed as dist
 
 from ..kernels.sampling import SamplerBackend
 from ..ops.decode import FusedAdamW
-from ..ops.fused_logp import lmhead_logp
 from ..ops.grpo_loss import group_advantages, grpo_loss
 from ..utils.logger import logger
 from ..utils.profiler import profile_range
@@ -30,7 +29,7 @@ class GRPOTrainer:
                  group_size: int = 8, max_new_tokens: int = 16, temperature: float = 1.0, top_k: Optional[int] = None,
                  top_p: Optional[float] = None, eps_clip: float = 0.2, beta: float = 0.0, lr: float = 1e-6,
                  weight_decay: float = 0.0, seed: int = 0, data_parallel: bool = False,
-                 bucket_bytes: int = 64 << 20):
+                 bucket_bytes: int = 64 << 20, dp_group: Optional["dist.ProcessGroup"] = None):
         self.model = model
         self.reward_fn = reward_fn
         self.group_size, self.max_new_tokens = group_size, max_new_tokens
@@ -38,14 +37,17 @@ class GRPOTrainer:
         self.eps_clip, self.beta = eps_clip, beta
         self.sampler = SamplerBackend(seed=seed)
         self.step_index = 0
-        self.dp = data_parallel and dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1
-        self.dp_rank = dist.get_rank() if self.dp else 0
+        self.dp_group = dp_group
+        self.dp = data_parallel and dist.is_available() and dist.is_initialized() and \
+            dist.get_world_size(dp_group) > 1
+        self.dp_rank = dist.get_rank(dp_group) if self.dp else 0
+        self.dp_world = dist.get_world_size(dp_group) if self.dp else 1
         self.reducer = None
         self.on_cuda = next(model.parameters()).device.type == "cuda"
         if self.dp and self.on_cuda:
             from ..parallel.collectives import GradReducer
 
-            self.reducer = GradReducer(model.parameters(), bucket_bytes=bucket_bytes, average=True)
+            self.reducer = GradReducer(model.parameters(), group=dp_group, bucket_bytes=bucket_bytes, average=True)
         self.optimizer = FusedAdamW(model.parameters(), lr=lr, weight_decay=weight_decay)
 
     # ------------------------------------------------------------------ phases
@@ -61,27 +63,27 @@ class GRPOTrainer:
         return out
 
     def policy_logp(self, sequences: torch.Tensor, prompt_len: int) -> torch.Tensor:
-        """Log-probability of every generated token under the current policy, with autograd."""
+        """Log-probability of every generated token under the current policy, with autograd.
+        Works for a tensor-parallel model as well (``LlamaModel.token_logp``)."""
         inputs, targets = sequences[:, :-1], sequences[:, 1:]
-        hidden = self.model.hidden_states(inputs)
-        tokens = inputs.numel()
-        logp = lmhead_logp(hidden[:tokens], self.model.lm_head, targets.reshape(-1),
-                           scale=1.0 / self.temperature if self.temperature > 0 else 1.0)
-        return logp.view(inputs.shape)[:, prompt_len - 1:]
+        logp = self.model.token_logp(inputs, targets, scale=1.0 / self.temperature if self.temperature > 0 else 1.0)
+        return logp[:, prompt_len - 1:]
 
-    def train_step(self, prompts: torch.Tensor) -> dict:
-        prompt_len = prompts.shape[1]
-        dev = prompts.device
-        with profile_range("grpo/rollout", dev):
-            roll = self.rollout(prompts)
+    def policy_update(self, sequences: torch.Tensor, logp_old: torch.Tensor, advantages: torch.Tensor,
+                      prompt_len: int):
+        """The learner half of a step on given rollouts: policy forward, clipped-ratio loss,
+        backward, gradient all-reduce over the data-parallel group, optimizer. The model may be
+        tensor parallel (DP x TP: pass its data-parallel group as ``dp_group``); rollouts then come
+        from elsewhere, since generation runs on an unsharded model. Returns ``(loss, stats)``."""
+        dev = sequences.device
         if self.reducer is not None:
             self.reducer.zero_grad()
         else:
             self.optimizer.zero_grad(set_to_none=True)
         with profile_range("grpo/policy_forward", dev):
-            logp_new = self.policy_logp(roll["sequences"], prompt_len)
-            loss, stats = grpo_loss(logp_new, roll["logp"], roll["advantages"], eps_low=self.eps_clip, beta=self.beta,
-                                    logp_ref=roll["logp"] if self.beta > 0 else None, return_stats=True)
+            logp_new = self.policy_logp(sequences, prompt_len)
+            loss, stats = grpo_loss(logp_new, logp_old, advantages, eps_low=self.eps_clip, beta=self.beta,
+                                    logp_ref=logp_old if self.beta > 0 else None, return_stats=True)
         with profile_range("grpo/backward_and_grad_reduce", dev):
             loss.backward()
             if self.reducer is not None:
@@ -90,13 +92,19 @@ class GRPOTrainer:
                 # CPU ranks (gloo): the same fixed-order sum, one tensor at a time, no overlap
                 from ..parallel.collectives import all_reduce_det
 
-                world = dist.get_world_size()
                 for p in self.model.parameters():
                     if p.grad is not None:
-                        all_reduce_det(p.grad)
-                        p.grad.div_(world)
+                        all_reduce_det(p.grad, self.dp_group)
+                        p.grad.div_(self.dp_world)
         with profile_range("grpo/optimizer", dev):
             self.optimizer.step()
+        return loss, stats
+
+    def train_step(self, prompts: torch.Tensor) -> dict:
+        prompt_len = prompts.shape[1]
+        with profile_range("grpo/rollout", prompts.device):
+            roll = self.rollout(prompts)
+        loss, stats = self.policy_update(roll["sequences"], roll["logp"], roll["advantages"], prompt_len)
         self.step_index += 1
         tokens = roll["new_tokens"].numel()
         return {"loss": loss.detach(), "clip_fraction": stats[1], "tokens": tokens,
@@ -106,14 +114,14 @@ class GRPOTrainer:
     def save(self, path: str) -> str:
         from ..utils.checkpoint import save_checkpoint
 
-        world = dist.get_world_size() if self.dp else 1
+        world = self.dp_world
         return save_checkpoint(path, self.model, self.optimizer, self.sampler, self.step_index, rank=self.dp_rank,
                                world=world)
 
     def load(self, path: str) -> None:
         from ..utils.checkpoint import load_checkpoint
 
-        world = dist.get_world_size() if self.dp else 1
+        world = self.dp_world
         info = load_checkpoint(path, self.model, self.optimizer, self.sampler, rank=self.dp_rank, world=world)
         self.step_index = info["step"]
         logger.info_on_rank(f"resumed from {path} at step {self.step_index}")

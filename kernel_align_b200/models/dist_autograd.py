@@ -12,6 +12,10 @@ class _AllGatherRows(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x_local, tp):
         ctx.rank, ctx.rows = tp.rank, x_local.shape[0]
+        if x_local.device.type != "cuda":
+            pieces = [torch.empty_like(x_local) for _ in range(tp.world)]
+            dist.all_gather(pieces, x_local.contiguous(), group=tp.group)
+            return torch.cat(pieces)
         out = torch.empty(tp.world * x_local.shape[0], *x_local.shape[1:], dtype=x_local.dtype, device=x_local.device)
         dist.all_gather_into_tensor(out, x_local.contiguous(), group=tp.group)
         return out

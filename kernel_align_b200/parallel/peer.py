@@ -60,5 +60,6 @@ def vocab_parallel_group(vocab: int, panel_rows: int = 32768, group: Optional[di
         vp = fused_logp.VocabParallel(rank=arena.rank, world=world, exchange_ptrs=arena.ptrs, epoch=1,
                                       panel_rows=panel_rows)
         vp.arena = arena  # keep the mapping alive
+        vp.process_group = g
         _vp_groups[key] = vp
     return vp

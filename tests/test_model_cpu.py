@@ -305,3 +305,55 @@ def test_cpu_pipeline_parallel_equals_the_unsplit_model(tmp_path, stages):
             ref = want[name].float()
             assert (g.float() - ref).abs().max().item() <= 0.03 * ref.abs().max().item() + 1e-6, name
     assert seen == set(want)
+
+
+def _hybrid_worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.set_num_threads(2)
+    # ranks (0, 1) and (2, 3) are tensor-parallel pairs; (0, 2) and (1, 3) hold the same shards
+    tp_groups = [dist.new_group([0, 1]), dist.new_group([2, 3])]
+    dp_groups = [dist.new_group([0, 2]), dist.new_group([1, 3])]
+    replica, shard = rank // 2, rank % 2
+    tp = TPContext(group=tp_groups[replica], device=CPU)
+    cfg = _cfg()
+    model = LlamaModel(cfg, tp=tp, seed=1, device=CPU)
+    trainer = GRPOTrainer(model, lambda p, t: t.float().mean(1), group_size=2, max_new_tokens=4, lr=1e-3, seed=3,
+                          data_parallel=True, dp_group=dp_groups[shard])
+    g = torch.Generator().manual_seed(40 + replica)          # each replica learns from its own rollouts
+    seqs = torch.randint(0, cfg.vocab_size, (4, 12), generator=g)
+    logp_old = -torch.rand(4, 4, generator=g) - 5.0
+    adv = torch.randn(4, generator=g)
+    with torch.no_grad():
+        logp0 = model.token_logp(seqs[:, :-1], seqs[:, 1:])
+    loss, _ = trainer.policy_update(seqs, logp_old, adv, prompt_len=8)
+    torch.save({"logp0": logp0, "loss": loss.detach(), "wqkv": model.layers[0].wqkv.detach().clone(),
+                "head": model.lm_head.detach().clone(), "seqs": seqs}, os.path.join(out_dir, f"r{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_cpu_hybrid_data_and_tensor_parallel_policy_update(tmp_path):
+    """DP x TP on four gloo ranks: the tensor-parallel forward (sequence-sharded layers,
+    vocabulary-parallel LM head) gives every rank of a replica the same log-probs, bitwise
+    equal to one process for the LM-head part and to rounding overall; after the update both
+    replicas hold bit-identical shards."""
+    mp.spawn(_hybrid_worker, args=(4, 29795, str(tmp_path)), nprocs=4, join=True)
+    o = [torch.load(tmp_path / f"r{r}.pt") for r in range(4)]
+    assert torch.equal(o[0]["logp0"], o[1]["logp0"]) and torch.equal(o[2]["logp0"], o[3]["logp0"])
+    assert torch.equal(o[0]["loss"], o[1]["loss"]) and torch.equal(o[2]["loss"], o[3]["loss"])
+    assert not torch.equal(o[0]["seqs"], o[2]["seqs"])
+    single = LlamaModel(_cfg(), seed=1, device=CPU)
+    for rep in (0, 2):
+        seqs = o[rep]["seqs"]
+        with torch.no_grad():
+            want = single.token_logp(seqs[:, :-1], seqs[:, 1:])
+        assert (o[rep]["logp0"] - want).abs().max().item() < 0.05
+    # same shard on both replicas after the data-parallel gradient all-reduce and AdamW
+    assert torch.equal(o[0]["wqkv"], o[2]["wqkv"]) and torch.equal(o[1]["wqkv"], o[3]["wqkv"])
+    assert torch.equal(o[0]["head"], o[2]["head"]) and torch.equal(o[1]["head"], o[3]["head"])
+    assert not torch.equal(o[0]["wqkv"], o[1]["wqkv"])          # different shards of the layer
+    fresh = LlamaModel(_cfg(), seed=1, device=CPU)
+    assert not torch.equal(o[0]["head"], fresh.lm_head.detach()[: o[0]["head"].shape[0]])   # and they moved

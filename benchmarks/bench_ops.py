@@ -32,6 +32,67 @@ def peaks():
     return 6650.0, 1590.0, 1400.0, "of fallback"
 
 
+def small_op_cases(dev, g, rows=32768, hidden=4096, groups=256, seq=512, batch=64, ctx=512, params=1 << 28):
+    """The operators that are not GEMM-shaped and have no row of their own above: RoPE, the GRPO
+    loss (forward + backward), decode attention, the fused AdamW step and the fused log-prob
+    backward. Returns ``[(name, fn, baseline_fn or None, bytes moved)]``; sizes are arguments
+    so that a CPU run can exercise the same calls on small shapes."""
+    from kernel_align_b200.ops.decode import FusedAdamW, attention_decode
+    from kernel_align_b200.ops.fused_logp import lmhead_logp
+    from kernel_align_b200.ops.grpo_loss import grpo_loss
+    from kernel_align_b200.ops.layer_ops import rope_, rope_tables
+
+    cases = []
+    heads = max(1, hidden // 128)
+    q = torch.randn(rows, heads, 128, device=dev, generator=g).to(torch.bfloat16)
+    pos = torch.arange(seq, device=dev).repeat(rows // seq + 1)[:rows]
+    cos, sin = rope_tables(max(seq, 8), 128, 500000.0, device=dev)
+    cases.append((f"rope {rows}x{heads}x128", lambda: rope_(q, pos, cos, sin), None, q.numel() * 2 * 2))
+
+    new = (torch.randn(groups, seq, device=dev, generator=g) * 0.1 - 2).requires_grad_()
+    old = torch.randn(groups, seq, device=dev, generator=g) * 0.1 - 2
+    adv = torch.randn(groups, device=dev, generator=g)
+
+    def loss_fb():
+        new.grad = None
+        grpo_loss(new, old, adv).backward()
+
+    def loss_torch():
+        n = new.detach().requires_grad_()
+        r = torch.exp(n - old)
+        a = adv[:, None]
+        (-torch.minimum(r * a, r.clamp(0.8, 1.2) * a).mean()).backward()
+
+    cases.append((f"grpo_loss fwd+bwd {groups}x{seq}", loss_fb, loss_torch, groups * seq * 4 * 4))
+
+    hq, hkv = heads, max(1, heads // 4)
+    qd = torch.randn(batch, hq, 128, device=dev, generator=g).to(torch.bfloat16)
+    ck = torch.randn(batch, ctx, hkv, 128, device=dev, generator=g).to(torch.bfloat16)
+    cv = torch.randn(batch, ctx, hkv, 128, device=dev, generator=g).to(torch.bfloat16)
+    lens = torch.full((batch,), ctx, dtype=torch.int32, device=dev)
+    cases.append((f"decode attention B={batch} ctx={ctx}", lambda: attention_decode(qd, ck, cv, lens), None,
+                  (ck.numel() + cv.numel()) * 2))
+
+    w = torch.nn.Parameter((torch.randn(params, device=dev, generator=g) * 0.02).to(torch.bfloat16))
+    w.grad = torch.randn(params, device=dev, generator=g).to(torch.bfloat16)
+    opt = FusedAdamW([w], lr=1e-5)
+    cases.append((f"fused AdamW {params} params", opt.step, None, params * (2 + 2 + 12 + 12 + 2)))
+
+    vocab = 128256 if rows >= 4096 else 512
+    m = min(rows, 8192)
+    hs = torch.randn(m, hidden, device=dev, generator=g).to(torch.bfloat16).requires_grad_()
+    wl = torch.nn.Parameter((torch.randn(vocab, hidden, device=dev, generator=g) * 0.02).to(torch.bfloat16))
+    ids = torch.randint(0, vocab, (m,), device=dev, generator=g)
+
+    def logp_fb():
+        hs.grad = None
+        wl.grad = None
+        lmhead_logp(hs, wl, ids).sum().backward()
+
+    cases.append((f"fused log-prob fwd+bwd {m}x{vocab}x{hidden}", logp_fb, None, 0))
+    return cases
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--json-out", default=None)
@@ -129,6 +190,15 @@ def main():
                 print("reference sampler unavailable:", type(e).__name__, str(e)[:200])
         by = lgs.numel() * 2
         rec(f"sampling G={gsz} V=128256 k=50 p=0.9", t, tb, by / t / 1e6 / hbm, f"{by / t / 1e6:.0f} GB/s of logits")
+    for name, fn, base, nbytes in small_op_cases(dev, g):
+        t = time_cuda(fn, iters=5)
+        tb = time_cuda(base, iters=5) if base is not None else None
+        if nbytes:
+            rec(name, t, tb, nbytes / t / 1e6 / hbm, f"{nbytes / t / 1e6:.0f} GB/s")
+        else:
+            m_, v_, k_ = 8192, 128256, 4096
+            tfl = 6.0 * m_ * v_ * k_ / t / 1e9 + 2.0 * m_ * v_ * k_ / t / 1e9     # forward, recompute, dH, dW
+            rec(name, t, tb, tfl / tf_burst, f"{tfl:.0f} TFLOP/s (4 GEMM-sized passes)")
     print(tabulate(rows, headers=["op", "ours", "baseline", "speedup", "roofline", "note"], tablefmt="github"))
     write_json(args.json_out, {"device": torch.cuda.get_device_name(), "peaks": {"hbm_gbs": hbm, "bf16_tflops": tf_burst,
                                                                                  "bf16_tflops_sustained": tf_sus}, "results": out})

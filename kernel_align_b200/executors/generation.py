@@ -1,9 +1,13 @@
 """Rollout generation: prefill the prompts, then decode token by token with a KV cache, drawing
 every token with the fused sampler and recording its log-probability.
 
-Runs per data-parallel rank (``tp.world == 1``): each rank generates for its own prompts. All
-heavy steps are the native kernels: GEMMs (``gemm_bi``), prefill attention, decode attention,
-RMSNorm, RoPE, SwiGLU, the sampler and the logits log-prob kernel.
+Each data-parallel rank generates for its own prompts. All heavy steps are the native kernels:
+GEMMs (``gemm_bi``), prefill attention, decode attention, RMSNorm, RoPE, SwiGLU, the sampler
+and the logits log-prob kernel. With a tensor-parallel model the activations stay replicated
+over the group (no sequence sharding for one token per sequence): every rank runs its heads
+and its slice of the FFN, the two row-parallel products are summed with the deterministic
+all-reduce, the LM-head shards are gathered into full logits, and every rank draws the same
+token from the same seeded stream.
 
 On CUDA the decode step (embedding -> every layer -> final norm -> LM-head logits: a few
 hundred small launches) is captured once in a CUDA graph and replayed per token; position,
@@ -47,10 +51,40 @@ def _layer_step(layer, x, batch, seq_len, positions, cos, sin, cache_k, cache_v,
     else:
         lens = torch.full((batch,), start + 1, dtype=torch.int32, device=x.device)
         a = attention_decode(q.view(batch, hq, hd), cache_k, cache_v, lens).reshape(batch, hq * hd)
-    x = x + gemm_bi(a, layer.wo)
+    x = x + _tp_sum(gemm_bi(a, layer.wo), layer.tp)
     h = rmsnorm(x, layer.norm2, cfg.rms_eps)
-    x = x + gemm_bi(swiglu(gemm_bi(h, layer.wgu)), layer.wdown)
+    x = x + _tp_sum(gemm_bi(swiglu(gemm_bi(h, layer.wgu)), layer.wdown), layer.tp)
     return x
+
+
+def _tp_sum(t: torch.Tensor, tp) -> torch.Tensor:
+    """Sum of the ranks' partial products in the fixed tree order (in place)."""
+    if tp.world > 1:
+        from ..parallel.collectives import all_reduce_det
+
+        all_reduce_det(t, tp.group)
+    return t
+
+
+def _full_logits(model, h: torch.Tensor) -> torch.Tensor:
+    """``[batch, vocab]`` logits from the (vocabulary-sharded) LM head."""
+    local = gemm_bi(h, model.lm_head)
+    tp = model.tp
+    if tp.world == 1:
+        return local
+    import torch.distributed as dist
+
+    from ..ops.fused_logp import vocab_shard_range
+
+    width = vocab_shard_range(model.cfg.vocab_size, 0, tp.world)[1]       # the widest shard (rank 0's)
+    padded = local if local.shape[1] == width else torch.cat([local, local.new_zeros(local.shape[0], width - local.shape[1])], 1)
+    pieces = [torch.empty_like(padded) for _ in range(tp.world)]
+    dist.all_gather(pieces, padded.contiguous(), group=tp.group)
+    cols = []
+    for r, piece in enumerate(pieces):
+        lo, hi = vocab_shard_range(model.cfg.vocab_size, r, tp.world)
+        cols.append(piece[:, : hi - lo])
+    return torch.cat(cols, 1).contiguous()
 
 
 @torch.no_grad()
@@ -132,8 +166,6 @@ def generate(model, prompts: torch.Tensor, sampler: Optional[SamplerBackend] = N
     Random streams are keyed by ``row_id_offset + row``, so a row's completion does not depend
     on which other rows are generated with it.
     """
-    if model.tp.world != 1:
-        raise ValueError("generation runs per data-parallel rank (tensor-parallel world size 1)")
     sampler = sampler if sampler is not None else SamplerBackend()
     cfg = model.cfg
     dev = model.embed.device
@@ -151,9 +183,11 @@ def generate(model, prompts: torch.Tensor, sampler: Optional[SamplerBackend] = N
     for layer, (ck, cv) in zip(model.layers, caches):
         x = _layer_step(layer, x, batch, lp, pos, model.rope_cos, model.rope_sin, ck, cv, 0)
     last = x.view(batch, lp, -1)[:, -1].contiguous()
-    logits = gemm_bi(rmsnorm(last, model.norm, cfg.rms_eps), model.lm_head)       # [batch, vocab] bf16
+    logits = _full_logits(model, rmsnorm(last, model.norm, cfg.rms_eps))           # [batch, vocab] bf16
+    # the graph path is for the unsharded model: the deterministic all-reduce of a tensor-parallel
+    # step carries a host-side epoch per call, which a replayed graph could not advance
     use_graph = cuda_graph and dev.type == "cuda" and max_new_tokens > 3
-    dec = _DecodeGraph(model, caches, batch, lp) if dev.type == "cuda" else None
+    dec = _DecodeGraph(model, caches, batch, lp) if dev.type == "cuda" and model.tp.world == 1 else None
     for t in range(max_new_tokens):
         tok = sampler.sample(logits, top_k=top_k, top_p=top_p, temperature=temperature, row_ids=row_ids).long()
         out_tokens[:, t] = tok
@@ -168,5 +202,5 @@ def generate(model, prompts: torch.Tensor, sampler: Optional[SamplerBackend] = N
         pos = torch.full((batch,), lp + t, dtype=torch.int64, device=dev)
         for layer, (ck, cv) in zip(model.layers, caches):
             x = _layer_step(layer, x, batch, 1, pos, model.rope_cos, model.rope_sin, ck, cv, lp + t)
-        logits = gemm_bi(rmsnorm(x, model.norm, cfg.rms_eps), model.lm_head)
+        logits = _full_logits(model, rmsnorm(x, model.norm, cfg.rms_eps))
     return {"sequences": torch.cat([seqs, out_tokens], 1), "new_tokens": out_tokens, "logp": out_logp}

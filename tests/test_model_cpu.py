@@ -357,3 +357,42 @@ def test_cpu_hybrid_data_and_tensor_parallel_policy_update(tmp_path):
     assert not torch.equal(o[0]["wqkv"], o[1]["wqkv"])          # different shards of the layer
     fresh = LlamaModel(_cfg(), seed=1, device=CPU)
     assert not torch.equal(o[0]["head"], fresh.lm_head.detach()[: o[0]["head"].shape[0]])   # and they moved
+
+
+def _tp_generate_worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.set_num_threads(2)
+    from kernel_align_b200.executors.generation import generate
+    from kernel_align_b200.kernels.sampling import SamplerBackend
+
+    cfg = _cfg()
+    model = LlamaModel(cfg, tp=TPContext(device=CPU), seed=1, device=CPU)
+    prompts = torch.randint(0, cfg.vocab_size, (3, 10), generator=torch.Generator().manual_seed(3))
+    out = generate(model, prompts, sampler=SamplerBackend(seed=5), max_new_tokens=5, temperature=0.8, top_k=50,
+                   top_p=0.95, group_size=2)
+    # and a whole GRPO step with the sharded model (rollout + policy update)
+    trainer = GRPOTrainer(model, lambda p, t: (t % 7 == 0).float().mean(1), group_size=2, max_new_tokens=4, lr=1e-3,
+                          seed=3, top_k=50)
+    step = trainer.train_step(prompts[:2])
+    torch.save({"seq": out["sequences"], "logp": out["logp"], "loss": step["loss"]}, os.path.join(out_dir, f"r{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_cpu_tensor_parallel_generation_and_grpo_step(tmp_path):
+    """Generation with a model sharded over two gloo ranks: both ranks produce the same tokens
+    and log-probs, the log-probs agree with the unsharded model's view of those tokens, and a
+    whole GRPO step runs on the sharded model with the same loss on both ranks."""
+    mp.spawn(_tp_generate_worker, args=(2, 29799, str(tmp_path)), nprocs=2, join=True)
+    a, b = (torch.load(tmp_path / f"r{r}.pt") for r in range(2))
+    assert torch.equal(a["seq"], b["seq"]) and torch.equal(a["logp"], b["logp"])
+    assert torch.equal(a["loss"], b["loss"]) and torch.isfinite(a["loss"])
+    assert a["seq"].shape == (6, 15)
+    single = LlamaModel(_cfg(), seed=1, device=CPU)
+    seq = a["seq"]
+    with torch.no_grad():
+        lp = single.token_logp(seq[:, :-1], seq[:, 1:], scale=1 / 0.8)[:, 9:]
+    assert (lp - a["logp"]).abs().max().item() < 0.1

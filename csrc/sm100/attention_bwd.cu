@@ -12,6 +12,9 @@
 // (K and Q as [d, rows], dO as [d, rows]) are read through MN-major descriptors from the same
 // TMA tiles, so nothing is transposed in memory. Every accumulation order is fixed, so the
 // gradients are bitwise reproducible and independent of the batch.
+//
+// The reference has no attention kernel and no backward pass of any kind: it routes the op
+// type "attention" to a backend name (rl_engine/kernels/registry.py:41-55).
 #include <cstdint>
 #include <cuda_bf16.h>
 #include <math_constants.h>

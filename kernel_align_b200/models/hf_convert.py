@@ -1,0 +1,83 @@
+"""Loading Hugging Face Llama weights into :class:`LlamaModel`.
+
+``config_from_hf(hf_config)`` maps a ``transformers.LlamaConfig`` to :class:`LlamaConfig`;
+``load_hf_state_dict(model, state_dict)`` copies a ``LlamaForCausalLM`` state dict into a model
+of any tensor-parallel degree: the q / k / v projections are fused per rank (this rank's heads),
+gate and up are fused per rank (this rank's slice of the FFN), ``o_proj`` and ``down_proj`` are
+split along their input dimension, and the LM head along the vocabulary in whole canonical
+slices. The rotary convention (rotate-half, pairs ``(i, i + head_dim / 2)``) and the RMSNorm
+are those of the Hugging Face implementation, so the two models compute the same function.
+
+The reference has no model and no checkpoint loading; ``CheckpointFormat`` is an unused enum
+(rl_engine/platforms/constants.py:69-73).
+"""
+from __future__ import annotations
+
+from typing import Mapping
+
+import torch
+
+from .llama import LlamaConfig, LlamaModel
+
+
+def config_from_hf(hf_config) -> LlamaConfig:
+    scaling = getattr(hf_config, "rope_scaling", None)
+    if scaling and scaling.get("rope_type", scaling.get("type", "default")) not in ("default", None):
+        raise ValueError("only the plain rotary embedding is implemented (no rope scaling)")
+    head_dim = getattr(hf_config, "head_dim", None) or hf_config.hidden_size // hf_config.num_attention_heads
+    theta = getattr(hf_config, "rope_theta", None)
+    if theta is None:
+        theta = (getattr(hf_config, "rope_parameters", None) or {}).get("rope_theta", 10000.0)
+    return LlamaConfig(vocab_size=hf_config.vocab_size, hidden=hf_config.hidden_size,
+                       n_layers=hf_config.num_hidden_layers, n_heads=hf_config.num_attention_heads,
+                       n_kv_heads=getattr(hf_config, "num_key_value_heads", hf_config.num_attention_heads),
+                       head_dim=head_dim, ffn=hf_config.intermediate_size, rope_theta=float(theta),
+                       rms_eps=float(hf_config.rms_norm_eps), max_pos=int(hf_config.max_position_embeddings))
+
+
+@torch.no_grad()
+def load_hf_state_dict(model: LlamaModel, state: Mapping[str, torch.Tensor]) -> None:
+    """Copy ``LlamaForCausalLM`` weights (names ``model.layers.N.self_attn.q_proj.weight`` ...)
+    into ``model``, taking this rank's shards. A tied head (no ``lm_head.weight``) uses the
+    embedding matrix."""
+    cfg, tp = model.cfg, model.tp
+    r, hd = tp.rank, cfg.head_dim
+
+    def get(name):
+        key = name if name in state else name.removeprefix("model.")
+        if key not in state:
+            raise KeyError(f"missing weight {name}")
+        return state[key]
+
+    def put(param, value):
+        if param.shape != value.shape:
+            raise ValueError(f"shape mismatch: model {tuple(param.shape)} vs checkpoint {tuple(value.shape)}")
+        param.copy_(value.to(device=param.device, dtype=param.dtype))
+
+    put(model.embed, get("model.embed_tokens.weight"))
+    put(model.norm, get("model.norm.weight"))
+    head = state["lm_head.weight"] if "lm_head.weight" in state else get("model.embed_tokens.weight")
+    lo, hi = model.vocab_range
+    put(model.lm_head, head[lo:hi])
+    for i, layer in enumerate(model.layers):
+        p = f"model.layers.{i}."
+        hq, hkv = layer.hq, layer.hkv
+        f = cfg.ffn // tp.world
+        q = get(p + "self_attn.q_proj.weight")[r * hq * hd:(r + 1) * hq * hd]
+        k = get(p + "self_attn.k_proj.weight")[r * hkv * hd:(r + 1) * hkv * hd]
+        v = get(p + "self_attn.v_proj.weight")[r * hkv * hd:(r + 1) * hkv * hd]
+        put(layer.wqkv, torch.cat([q, k, v]))
+        put(layer.wo, get(p + "self_attn.o_proj.weight")[:, r * hq * hd:(r + 1) * hq * hd])
+        gate = get(p + "mlp.gate_proj.weight")[r * f:(r + 1) * f]
+        up = get(p + "mlp.up_proj.weight")[r * f:(r + 1) * f]
+        put(layer.wgu, torch.cat([gate, up]))
+        put(layer.wdown, get(p + "mlp.down_proj.weight")[:, r * f:(r + 1) * f])
+        put(layer.norm1, get(p + "input_layernorm.weight"))
+        put(layer.norm2, get(p + "post_attention_layernorm.weight"))
+
+
+def from_hf(hf_model, tp=None, device=None) -> LlamaModel:
+    """A :class:`LlamaModel` with the architecture and weights of a ``LlamaForCausalLM``."""
+    model = LlamaModel(config_from_hf(hf_model.config), tp=tp, seed=0, device=device)
+    load_hf_state_dict(model, hf_model.state_dict())
+    return model

@@ -81,3 +81,54 @@ def from_hf(hf_model, tp=None, device=None) -> LlamaModel:
     model = LlamaModel(config_from_hf(hf_model.config), tp=tp, seed=0, device=device)
     load_hf_state_dict(model, hf_model.state_dict())
     return model
+
+
+@torch.no_grad()
+def to_hf_state_dict(model: LlamaModel) -> dict:
+    """The model's weights under ``LlamaForCausalLM`` names (the inverse of
+    :func:`load_hf_state_dict`), e.g. to hand a trained policy to an inference engine. With a
+    tensor-parallel model every rank gathers the other ranks' shards and returns the full
+    state dict."""
+    import torch.distributed as dist
+
+    cfg, tp = model.cfg, model.tp
+    hd = cfg.head_dim
+
+    def gather(t: torch.Tensor) -> list:
+        if tp.world == 1:
+            return [t]
+        parts = [torch.empty_like(t) for _ in range(tp.world)]
+        dist.all_gather(parts, t.contiguous(), group=tp.group)
+        return parts
+
+    out = {"model.embed_tokens.weight": model.embed.detach().clone(), "model.norm.weight": model.norm.detach().clone()}
+    if tp.world == 1:
+        out["lm_head.weight"] = model.lm_head.detach().clone()
+    else:
+        from ..ops.fused_logp import vocab_shard_range
+
+        width = vocab_shard_range(cfg.vocab_size, 0, tp.world)[1]
+        mine = model.lm_head.detach()
+        if mine.shape[0] < width:
+            mine = torch.cat([mine, mine.new_zeros(width - mine.shape[0], mine.shape[1])])
+        rows = []
+        for r, part in enumerate(gather(mine)):
+            lo, hi = vocab_shard_range(cfg.vocab_size, r, tp.world)
+            rows.append(part[: hi - lo])
+        out["lm_head.weight"] = torch.cat(rows)
+    for i, layer in enumerate(model.layers):
+        p = f"model.layers.{i}."
+        hq, hkv = layer.hq, layer.hkv
+        f = cfg.ffn // tp.world
+        qkv = gather(layer.wqkv.detach())
+        out[p + "self_attn.q_proj.weight"] = torch.cat([t[: hq * hd] for t in qkv])
+        out[p + "self_attn.k_proj.weight"] = torch.cat([t[hq * hd:(hq + hkv) * hd] for t in qkv])
+        out[p + "self_attn.v_proj.weight"] = torch.cat([t[(hq + hkv) * hd:] for t in qkv])
+        out[p + "self_attn.o_proj.weight"] = torch.cat(gather(layer.wo.detach()), 1)
+        gu = gather(layer.wgu.detach())
+        out[p + "mlp.gate_proj.weight"] = torch.cat([t[:f] for t in gu])
+        out[p + "mlp.up_proj.weight"] = torch.cat([t[f:] for t in gu])
+        out[p + "mlp.down_proj.weight"] = torch.cat(gather(layer.wdown.detach()), 1)
+        out[p + "input_layernorm.weight"] = layer.norm1.detach().clone()
+        out[p + "post_attention_layernorm.weight"] = layer.norm2.detach().clone()
+    return out

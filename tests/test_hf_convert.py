@@ -6,7 +6,7 @@ import torch
 
 transformers = pytest.importorskip("transformers")
 
-from kernel_align_b200.models.hf_convert import config_from_hf, from_hf  # noqa: E402
+from kernel_align_b200.models.hf_convert import config_from_hf, from_hf, to_hf_state_dict  # noqa: E402
 
 CPU = torch.device("cpu")
 
@@ -45,6 +45,11 @@ def test_loaded_model_matches_transformers_forward():
         mine_logp = model.token_logp(ids, ids)
     assert (mine_hidden - ref_hidden).abs().max().item() < 0.04 * ref_hidden.abs().max().item()
     assert (mine_logp - ref_logp).abs().max().item() < 0.05
+    # and back: the exported state dict is the one that was loaded
+    back = to_hf_state_dict(model)
+    ref_state = hf.state_dict()
+    assert set(back) == {k for k in ref_state if "rotary" not in k}
+    assert all(torch.equal(back[k].float(), ref_state[k].float()) for k in back)
 
 
 def _tp_worker(rank, world, port, out_dir):
@@ -64,6 +69,9 @@ def _tp_worker(rank, world, port, out_dir):
     ids = torch.randint(0, 512, (2, 40), generator=torch.Generator().manual_seed(1))
     with torch.no_grad():
         logp = model.token_logp(ids, ids)
+    full = to_hf_state_dict(model)                 # every rank reassembles the whole checkpoint
+    ref_state = _hf_model().state_dict()
+    assert all(torch.equal(full[k].float(), ref_state[k].float()) for k in full)
     torch.save(logp, os.path.join(out_dir, f"r{rank}.pt"))
     dist.barrier()
     dist.destroy_process_group()

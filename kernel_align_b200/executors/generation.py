@@ -158,11 +158,15 @@ class _DecodeGraph:
 @torch.no_grad()
 def generate(model, prompts: torch.Tensor, sampler: Optional[SamplerBackend] = None, max_new_tokens: int = 16,
              temperature: float = 1.0, top_k: Optional[int] = None, top_p: Optional[float] = None,
-             group_size: int = 1, row_id_offset: int = 0, cuda_graph: bool = True) -> dict:
+             group_size: int = 1, row_id_offset: int = 0, cuda_graph: bool = True,
+             eos_token_id: Optional[int] = None, pad_token_id: int = 0) -> dict:
     """``prompts [P, Lp]`` -> ``group_size`` completions each.
 
     Returns ``sequences [P * G, Lp + T]`` (int64), ``logp [P * G, T]`` (log-probability of each
-    sampled token under ``softmax(logits / temperature)``) and ``new_tokens [P * G, T]``.
+    sampled token under ``softmax(logits / temperature)``) and ``new_tokens [P * G, T]``. With
+    ``eos_token_id`` a completion ends at its first EOS token: later positions hold
+    ``pad_token_id`` with log-prob 0, and ``mask [P * G, T]`` (1.0 up to and including the EOS)
+    says which positions count; the loop stops early once every row has ended.
     Random streams are keyed by ``row_id_offset + row``, so a row's completion does not depend
     on which other rows are generated with it.
     """
@@ -188,11 +192,23 @@ def generate(model, prompts: torch.Tensor, sampler: Optional[SamplerBackend] = N
     # step carries a host-side epoch per call, which a replayed graph could not advance
     use_graph = cuda_graph and dev.type == "cuda" and max_new_tokens > 3
     dec = _DecodeGraph(model, caches, batch, lp) if dev.type == "cuda" and model.tp.world == 1 else None
+    finished = torch.zeros(batch, dtype=torch.bool, device=dev) if eos_token_id is not None else None
+    mask = torch.zeros(batch, max_new_tokens, dtype=torch.float32, device=dev) if eos_token_id is not None else None
+    if eos_token_id is not None:
+        out_tokens.fill_(pad_token_id)
+        out_logp.zero_()
     for t in range(max_new_tokens):
         tok = sampler.sample(logits, top_k=top_k, top_p=top_p, temperature=temperature, row_ids=row_ids).long()
+        lp_t = logits_logp(logits, tok, scale=1.0 / temperature if temperature > 0 else 1.0)
+        if finished is not None:
+            alive = ~finished
+            mask[:, t] = alive.float()
+            tok = torch.where(alive, tok, torch.full_like(tok, pad_token_id))
+            lp_t = torch.where(alive, lp_t, torch.zeros_like(lp_t))
+            finished = finished | (tok == eos_token_id)
         out_tokens[:, t] = tok
-        out_logp[:, t] = logits_logp(logits, tok, scale=1.0 / temperature if temperature > 0 else 1.0)
-        if t + 1 == max_new_tokens:
+        out_logp[:, t] = lp_t
+        if t + 1 == max_new_tokens or (finished is not None and bool(finished.all())):
             break
         if dec is not None:
             # first decode step eager (loads every kernel at this shape), second one captured
@@ -203,4 +219,7 @@ def generate(model, prompts: torch.Tensor, sampler: Optional[SamplerBackend] = N
         for layer, (ck, cv) in zip(model.layers, caches):
             x = _layer_step(layer, x, batch, 1, pos, model.rope_cos, model.rope_sin, ck, cv, lp + t)
         logits = _full_logits(model, rmsnorm(x, model.norm, cfg.rms_eps))
-    return {"sequences": torch.cat([seqs, out_tokens], 1), "new_tokens": out_tokens, "logp": out_logp}
+    out = {"sequences": torch.cat([seqs, out_tokens], 1), "new_tokens": out_tokens, "logp": out_logp}
+    if mask is not None:
+        out["mask"] = mask
+    return out

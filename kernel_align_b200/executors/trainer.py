@@ -29,12 +29,19 @@ class GRPOTrainer:
                  group_size: int = 8, max_new_tokens: int = 16, temperature: float = 1.0, top_k: Optional[int] = None,
                  top_p: Optional[float] = None, eps_clip: float = 0.2, beta: float = 0.0, lr: float = 1e-6,
                  weight_decay: float = 0.0, seed: int = 0, data_parallel: bool = False,
-                 bucket_bytes: int = 64 << 20, dp_group: Optional["dist.ProcessGroup"] = None):
+                 bucket_bytes: int = 64 << 20, dp_group: Optional["dist.ProcessGroup"] = None,
+                 ref_model=None, updates_per_rollout: int = 1, eos_token_id: Optional[int] = None,
+                 pad_token_id: int = 0):
         self.model = model
         self.reward_fn = reward_fn
         self.group_size, self.max_new_tokens = group_size, max_new_tokens
         self.temperature, self.top_k, self.top_p = temperature, top_k, top_p
         self.eps_clip, self.beta = eps_clip, beta
+        # ref_model: a frozen policy for the KL term (beta > 0); without one the KL is taken to the
+        # policy that produced the rollouts. updates_per_rollout: optimizer steps on one batch of
+        # rollouts (after the first the ratio moves away from 1 and the clipping becomes active).
+        self.ref_model, self.updates_per_rollout = ref_model, max(1, int(updates_per_rollout))
+        self.eos_token_id, self.pad_token_id = eos_token_id, pad_token_id
         self.sampler = SamplerBackend(seed=seed)
         self.step_index = 0
         self.dp_group = dp_group
@@ -56,7 +63,8 @@ class GRPOTrainer:
         p = prompts.shape[0]
         out = generate(self.model, prompts, sampler=self.sampler, max_new_tokens=self.max_new_tokens,
                        temperature=self.temperature, top_k=self.top_k, top_p=self.top_p, group_size=self.group_size,
-                       row_id_offset=self.dp_rank * p * self.group_size)
+                       row_id_offset=self.dp_rank * p * self.group_size, eos_token_id=self.eos_token_id,
+                       pad_token_id=self.pad_token_id)
         rewards = self.reward_fn(prompts.repeat_interleave(self.group_size, 0), out["new_tokens"]).float()
         out["rewards"] = rewards
         out["advantages"] = group_advantages(rewards, self.group_size)
@@ -70,7 +78,7 @@ class GRPOTrainer:
         return logp[:, prompt_len - 1:]
 
     def policy_update(self, sequences: torch.Tensor, logp_old: torch.Tensor, advantages: torch.Tensor,
-                      prompt_len: int):
+                      prompt_len: int, mask: Optional[torch.Tensor] = None, logp_ref: Optional[torch.Tensor] = None):
         """The learner half of a step on given rollouts: policy forward, clipped-ratio loss,
         backward, gradient all-reduce over the data-parallel group, optimizer. The model may be
         tensor parallel (DP x TP: pass its data-parallel group as ``dp_group``); rollouts then come
@@ -82,8 +90,9 @@ class GRPOTrainer:
             self.optimizer.zero_grad(set_to_none=True)
         with profile_range("grpo/policy_forward", dev):
             logp_new = self.policy_logp(sequences, prompt_len)
-            loss, stats = grpo_loss(logp_new, logp_old, advantages, eps_low=self.eps_clip, beta=self.beta,
-                                    logp_ref=logp_old if self.beta > 0 else None, return_stats=True)
+            ref = (logp_ref if logp_ref is not None else logp_old) if self.beta > 0 else None
+            loss, stats = grpo_loss(logp_new, logp_old, advantages, mask=mask, eps_low=self.eps_clip, beta=self.beta,
+                                    logp_ref=ref, return_stats=True)
         with profile_range("grpo/backward_and_grad_reduce", dev):
             loss.backward()
             if self.reducer is not None:
@@ -104,7 +113,15 @@ class GRPOTrainer:
         prompt_len = prompts.shape[1]
         with profile_range("grpo/rollout", prompts.device):
             roll = self.rollout(prompts)
-        loss, stats = self.policy_update(roll["sequences"], roll["logp"], roll["advantages"], prompt_len)
+        logp_ref = None
+        if self.ref_model is not None and self.beta > 0:
+            with torch.no_grad():
+                seq = roll["sequences"]
+                scale = 1.0 / self.temperature if self.temperature > 0 else 1.0
+                logp_ref = self.ref_model.token_logp(seq[:, :-1], seq[:, 1:], scale=scale)[:, prompt_len - 1:]
+        for _ in range(self.updates_per_rollout):
+            loss, stats = self.policy_update(roll["sequences"], roll["logp"], roll["advantages"], prompt_len,
+                                             mask=roll.get("mask"), logp_ref=logp_ref)
         self.step_index += 1
         tokens = roll["new_tokens"].numel()
         return {"loss": loss.detach(), "clip_fraction": stats[1], "tokens": tokens,

@@ -396,3 +396,48 @@ def test_cpu_tensor_parallel_generation_and_grpo_step(tmp_path):
     with torch.no_grad():
         lp = single.token_logp(seq[:, :-1], seq[:, 1:], scale=1 / 0.8)[:, 9:]
     assert (lp - a["logp"]).abs().max().item() < 0.1
+
+
+def test_cpu_generation_stops_at_eos_and_masks_the_rest():
+    from kernel_align_b200.executors.generation import generate
+    from kernel_align_b200.kernels.sampling import SamplerBackend
+
+    cfg = _cfg()
+    model = LlamaModel(cfg, seed=1, device=CPU)
+    prompts = torch.randint(0, cfg.vocab_size, (4, 6), generator=torch.Generator().manual_seed(3))
+    kw = dict(max_new_tokens=12, temperature=1.0, top_k=8, group_size=2)
+    plain = generate(model, prompts, sampler=SamplerBackend(seed=5), **kw)
+    eos = int(plain["new_tokens"][0, 3])                     # a token that row 0 certainly emits
+    out = generate(model, prompts, sampler=SamplerBackend(seed=5), eos_token_id=eos, pad_token_id=1, **kw)
+    toks, mask, lp = out["new_tokens"], out["mask"], out["logp"]
+    for r in range(toks.shape[0]):
+        hits = (plain["new_tokens"][r] == eos).nonzero().flatten()
+        end = int(hits[0]) + 1 if len(hits) and int(hits[0]) < toks.shape[1] else toks.shape[1]
+        assert torch.equal(toks[r, :end], plain["new_tokens"][r, :end])     # same stream up to the EOS
+        assert torch.equal(lp[r, :end], plain["logp"][r, :end])
+        assert mask[r, :end].all() and not mask[r, end:].any()
+        assert (toks[r, end:] == 1).all() and (lp[r, end:] == 0).all()
+    assert mask[0].sum().item() <= 4
+
+
+def test_cpu_grpo_with_reference_policy_eos_mask_and_several_updates():
+    cfg = _cfg()
+
+    def reward(prompts, new_tokens):
+        return (new_tokens % 5 == 0).float().mean(1)
+
+    prompts = torch.randint(0, cfg.vocab_size, (2, 8), generator=torch.Generator().manual_seed(9))
+    ref = LlamaModel(cfg, seed=2, device=CPU)
+    for p in ref.parameters():
+        p.requires_grad_(False)
+
+    def fresh(**kw):
+        return GRPOTrainer(LlamaModel(cfg, seed=2, device=CPU), reward, group_size=2, max_new_tokens=6, temperature=1.0,
+                           top_k=50, lr=1e-3, seed=3, **kw)
+
+    a = fresh(beta=0.1, ref_model=ref, updates_per_rollout=2, eos_token_id=7)
+    b = fresh(beta=0.1, ref_model=ref, updates_per_rollout=2, eos_token_id=7)
+    la = [a.train_step(prompts)["loss"].item() for _ in range(2)]
+    lb = [b.train_step(prompts)["loss"].item() for _ in range(2)]
+    assert la == lb and all(math.isfinite(v) for v in la)
+    assert a.optimizer.step_count == 4 and not any(p.grad is not None for p in ref.parameters())

@@ -25,6 +25,14 @@ w = torch.randn(1003, 72, generator=g) * 0.05
 ids = torch.randint(-2, 1005, (37,), generator=g)
 lp, lse = cpu_ops.lmhead_logp_cpu(h, w, ids, return_lse=True)
 assert torch.isfinite(lp).all()
+# the vocabulary-parallel form: two shards of whole canonical slices, then the tree merge
+vs = -(-1003 // 8)
+states, targets = [], []
+for lo, hi in ((0, 4 * vs), (4 * vs, 1003)):
+    st, tg = cpu_ops.lmhead_logp_shard_cpu(h, w[lo:hi], ids, vocab=1003, v_lo=lo)
+    states.append(st); targets.append(tg)
+merged = cpu_ops.lmhead_logp_merge_cpu(torch.cat(states, 1), targets[0] + targets[1], ids, vocab=1003)
+assert torch.equal(merged, lp)
 # log-prob from logits, three dtypes
 for dt in (torch.float32, torch.bfloat16, torch.float16):
     lg = (torch.randn(19, 1003, generator=g) * 2).to(dt)

@@ -128,17 +128,23 @@ class GRPOTrainer:
                 "reward_mean": roll["rewards"].mean(), "step": self.step_index}
 
     # ------------------------------------------------------------------ checkpoint / resume
+    def _shard_id(self) -> tuple[int, int]:
+        """(index, count) of this process's checkpoint file: one per (data-parallel rank,
+        tensor-parallel rank), since every such process holds different state or shards."""
+        tp = getattr(self.model, "tp", None)
+        tp_rank, tp_world = (tp.rank, tp.world) if tp is not None else (0, 1)
+        return self.dp_rank * tp_world + tp_rank, self.dp_world * tp_world
+
     def save(self, path: str) -> str:
         from ..utils.checkpoint import save_checkpoint
 
-        world = self.dp_world
-        return save_checkpoint(path, self.model, self.optimizer, self.sampler, self.step_index, rank=self.dp_rank,
-                               world=world)
+        rank, world = self._shard_id()
+        return save_checkpoint(path, self.model, self.optimizer, self.sampler, self.step_index, rank=rank, world=world)
 
     def load(self, path: str) -> None:
         from ..utils.checkpoint import load_checkpoint
 
-        world = self.dp_world
-        info = load_checkpoint(path, self.model, self.optimizer, self.sampler, rank=self.dp_rank, world=world)
+        rank, world = self._shard_id()
+        info = load_checkpoint(path, self.model, self.optimizer, self.sampler, rank=rank, world=world)
         self.step_index = info["step"]
         logger.info_on_rank(f"resumed from {path} at step {self.step_index}")

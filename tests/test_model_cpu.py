@@ -377,7 +377,18 @@ def _tp_generate_worker(rank, world, port, out_dir):
     trainer = GRPOTrainer(model, lambda p, t: (t % 7 == 0).float().mean(1), group_size=2, max_new_tokens=4, lr=1e-3,
                           seed=3, top_k=50)
     step = trainer.train_step(prompts[:2])
-    torch.save({"seq": out["sequences"], "logp": out["logp"], "loss": step["loss"]}, os.path.join(out_dir, f"r{rank}.pt"))
+    # every tensor-parallel rank writes its own shard file, and a fresh trainer resumes from them
+    ckpt = trainer.save(os.path.join(out_dir, "ckpt.pt"))
+    assert ckpt.endswith(f"rank{rank}of{world}")
+    dist.barrier()
+    resumed = GRPOTrainer(LlamaModel(cfg, tp=TPContext(device=CPU), seed=9, device=CPU),
+                          lambda p, t: (t % 7 == 0).float().mean(1), group_size=2, max_new_tokens=4, lr=1e-3, seed=3,
+                          top_k=50)
+    resumed.load(os.path.join(out_dir, "ckpt.pt"))
+    same = resumed.step_index == 1 and torch.equal(resumed.model.lm_head, model.lm_head) and \
+        resumed.train_step(prompts[:2])["loss"].item() == trainer.train_step(prompts[:2])["loss"].item()
+    torch.save({"seq": out["sequences"], "logp": out["logp"], "loss": step["loss"], "resume_ok": bool(same)},
+               os.path.join(out_dir, f"r{rank}.pt"))
     dist.barrier()
     dist.destroy_process_group()
 
@@ -390,6 +401,7 @@ def test_cpu_tensor_parallel_generation_and_grpo_step(tmp_path):
     a, b = (torch.load(tmp_path / f"r{r}.pt") for r in range(2))
     assert torch.equal(a["seq"], b["seq"]) and torch.equal(a["logp"], b["logp"])
     assert torch.equal(a["loss"], b["loss"]) and torch.isfinite(a["loss"])
+    assert a["resume_ok"] and b["resume_ok"]
     assert a["seq"].shape == (6, 15)
     single = LlamaModel(_cfg(), seed=1, device=CPU)
     seq = a["seq"]

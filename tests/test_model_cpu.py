@@ -453,3 +453,53 @@ def test_cpu_grpo_with_reference_policy_eos_mask_and_several_updates():
     lb = [b.train_step(prompts)["loss"].item() for _ in range(2)]
     assert la == lb and all(math.isfinite(v) for v in la)
     assert a.optimizer.step_count == 4 and not any(p.grad is not None for p in ref.parameters())
+
+
+def _layout_worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.set_num_threads(2)
+    from kernel_align_b200.parallel.strategy import build_model, make_layout
+
+    rec = {}
+    for name, kw in (("data_parallel", {}), ("model_parallel", {}), ("pipeline_parallel", {}),
+                     ("hybrid", {"tp_size": 2}), ("hybrid", {"tp_size": 1, "pp_size": 2})):
+        lay = make_layout(name, **kw)
+        key = name + str(sorted(kw.items()))
+        rec[key] = (lay.tp_size, lay.pp_size, lay.dp_size, lay.tp_rank, lay.pp_rank, lay.dp_rank)
+        # every group really connects the ranks it should: sum of ranks over the group
+        for gname, g, size in (("tp", lay.tp_group, lay.tp_size), ("pp", lay.pp_group, lay.pp_size),
+                               ("dp", lay.dp_group, lay.dp_size)):
+            t = torch.tensor([float(rank)])
+            if size > 1:
+                dist.all_reduce(t, group=g)
+            rec[key + gname] = t.item()
+    lay = make_layout("hybrid", tp_size=2)
+    model = build_model(_cfg(), lay, seed=1, device=CPU)
+    ids = torch.randint(0, 512, (2, 20), generator=torch.Generator().manual_seed(30 + lay.dp_rank))
+    with torch.no_grad():
+        rec["logp"] = model.token_logp(ids, ids)
+    torch.save(rec, os.path.join(out_dir, f"r{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_cpu_strategy_layouts_build_the_right_groups(tmp_path):
+    mp.spawn(_layout_worker, args=(4, 29815, str(tmp_path)), nprocs=4, join=True)
+    o = [torch.load(tmp_path / f"r{r}.pt") for r in range(4)]
+    for r in range(4):
+        assert o[r]["data_parallel[]"] == (1, 1, 4, 0, 0, r) and o[r]["data_parallel[]dp"] == 6.0
+        assert o[r]["model_parallel[]"] == (4, 1, 1, r, 0, 0) and o[r]["model_parallel[]tp"] == 6.0
+        assert o[r]["pipeline_parallel[]"] == (1, 4, 1, 0, r, 0) and o[r]["pipeline_parallel[]pp"] == 6.0
+        k = "hybrid[('tp_size', 2)]"
+        assert o[r][k] == (2, 1, 2, r % 2, 0, r // 2)
+        assert o[r][k + "tp"] == (1.0 if r < 2 else 5.0)            # {0, 1} and {2, 3}
+        assert o[r][k + "dp"] == (2.0 if r % 2 == 0 else 4.0)       # {0, 2} and {1, 3}
+        k = "hybrid[('pp_size', 2), ('tp_size', 1)]"
+        assert o[r][k] == (1, 2, 2, 0, r % 2, r // 2)
+        assert o[r][k + "pp"] == (1.0 if r < 2 else 5.0)
+    # the tensor-parallel pairs agree with each other and differ across data-parallel replicas
+    assert torch.equal(o[0]["logp"], o[1]["logp"]) and torch.equal(o[2]["logp"], o[3]["logp"])
+    assert not torch.equal(o[0]["logp"], o[2]["logp"])

@@ -60,6 +60,24 @@ class SamplerBackend(nn.Module):
         return out
 
     @torch.inference_mode()
+    def sample_with(self, method, logits, *, top_k: int = 50, top_p: float = 0.9, temperature: float = 1.0,
+                    **kw) -> torch.Tensor:
+        """``sample`` selected by a ``SamplingMethod`` value (``constants.SamplingMethod``):
+        ``greedy`` takes the arg-max, ``temperature`` draws from the full distribution,
+        ``top_k`` / ``top_p`` (= ``nucleus``) / ``top_k_top_p`` apply the named filters."""
+        from ..platforms.constants import SamplingMethod
+
+        m = method if isinstance(method, SamplingMethod) else SamplingMethod(str(method).lower())
+        if m == SamplingMethod.GREEDY:
+            return self.sample(logits, top_k=1, temperature=temperature, **kw)
+        if m == SamplingMethod.TEMPERATURE:
+            return self.sample(logits, temperature=temperature, **kw)
+        if m == SamplingMethod.TOP_K:
+            return self.sample(logits, top_k=top_k, temperature=temperature, **kw)
+        if m in (SamplingMethod.TOP_P, SamplingMethod.NUCLEUS):
+            return self.sample(logits, top_p=top_p, temperature=temperature, **kw)
+        return self.sample(logits, top_k=top_k, top_p=top_p, temperature=temperature, **kw)
+
     def compute_logp(self, logits, token_ids, temperature: float = 1.0) -> torch.Tensor:
         """Log-probability of ``token_ids`` under ``softmax(logits / temperature)``.
 

@@ -70,6 +70,19 @@ class DeviceContext:
     def is_blackwell(self) -> bool:
         return self.capability is not None and self.capability[0] == 10
 
+    @staticmethod
+    def dtype_of(precision) -> torch.dtype:
+        """The torch dtype of a ``PrecisionType`` value (fp32 / fp16 / bf16 / int8); ``int4`` has
+        no torch dtype and is rejected."""
+        from .constants import PrecisionType
+
+        p = precision if isinstance(precision, PrecisionType) else PrecisionType(str(precision).lower())
+        table = {PrecisionType.FP32: torch.float32, PrecisionType.FP16: torch.float16,
+                 PrecisionType.BF16: torch.bfloat16, PrecisionType.INT8: torch.int8}
+        if p not in table:
+            raise ValueError(f"no tensor dtype for precision {p.value}")
+        return table[p]
+
     def get_preferred_dtype(self) -> torch.dtype:
         """bf16 on a GPU, fp32 on the CPU path."""
         return torch.bfloat16 if self.device.type == "cuda" else torch.float32

@@ -98,3 +98,29 @@ def test_packages_are_real_packages():
     for sub in ("utils", "platforms", "kernels", "executors", "ops", "parallel", "models"):
         mod = importlib.import_module(f"kernel_align_b200.{sub}")
         assert mod.__file__ and mod.__file__.endswith("__init__.py")
+
+
+def test_sampling_method_and_precision_enums_are_wired():
+    import torch
+
+    from kernel_align_b200.kernels.sampling import SamplerBackend
+    from kernel_align_b200.platforms.constants import constants
+    from kernel_align_b200.platforms.device import device_ctx
+
+    logits = torch.randn(5, 300, generator=torch.Generator().manual_seed(0))
+    s = SamplerBackend(seed=2)
+    greedy = s.sample_with(constants.SamplingMethod.GREEDY, logits)
+    assert torch.equal(greedy.long(), logits.argmax(-1))
+    a = s.sample_with("top_k_top_p", logits, top_k=20, top_p=0.8, temperature=0.7, step=3)
+    b = s.sample(logits, top_k=20, top_p=0.8, temperature=0.7, step=3)
+    assert torch.equal(a, b)
+    assert torch.equal(s.sample_with("nucleus", logits, top_p=0.5, step=1), s.sample(logits, top_p=0.5, step=1))
+    assert torch.equal(s.sample_with("top_k", logits, top_k=7, step=1), s.sample(logits, top_k=7, step=1))
+    assert torch.equal(s.sample_with("temperature", logits, temperature=1.3, step=1),
+                       s.sample(logits, temperature=1.3, step=1))
+    assert device_ctx.dtype_of(constants.PrecisionType.BF16) is torch.bfloat16
+    assert device_ctx.dtype_of("float16") is torch.float16
+    import pytest
+
+    with pytest.raises(ValueError):
+        device_ctx.dtype_of(constants.PrecisionType.INT4)

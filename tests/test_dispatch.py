@@ -124,3 +124,13 @@ def test_sampling_method_and_precision_enums_are_wired():
 
     with pytest.raises(ValueError):
         device_ctx.dtype_of(constants.PrecisionType.INT4)
+
+
+def test_doctor_reports_and_self_tests():
+    from kernel_align_b200 import doctor
+
+    info = doctor.collect()
+    assert info["libka_cpu"] and info["distributed"]["gloo"]
+    st = doctor.self_test()
+    assert st["logp_max_abs_err"] < 1e-4 and st["logp_batch_invariant"] and st["sampler_batch_invariant"]
+    assert doctor.main(["--json"]) == 0

@@ -9,6 +9,7 @@ the CPU path works.
 from __future__ import annotations
 
 import json
+import os
 import shutil
 import sys
 
@@ -19,7 +20,7 @@ def collect() -> dict:
     from . import __version__, _build
 
     info: dict = {"version": __version__, "torch": torch.__version__, "cuda_runtime": torch.version.cuda}
-    info["nvcc"] = shutil.which("nvcc") or ("/usr/local/cuda/bin/nvcc" if shutil.os.path.exists("/usr/local/cuda/bin/nvcc") else None)
+    info["nvcc"] = shutil.which("nvcc") or ("/usr/local/cuda/bin/nvcc" if os.path.exists("/usr/local/cuda/bin/nvcc") else None)
     info["cxx"] = shutil.which("g++")
     info["libka_sm100"] = str(_build.CUDA_LIB) if _build.CUDA_LIB.exists() else None
     info["libka_cpu"] = str(_build.CPU_LIB) if _build.CPU_LIB.exists() else None

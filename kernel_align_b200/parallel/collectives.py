@@ -28,12 +28,17 @@ from ..utils.profiler import profiled
 
 
 def tree_sum(parts: Sequence[torch.Tensor]) -> torch.Tensor:
-    """Balanced pairwise sum in fp32, left to right at every level: the canonical order."""
+    """Balanced pairwise sum in fp32, left to right at every level: the canonical order. With a
+    count that is not a power of two the odd element of a level moves up unchanged (still one
+    fixed order per count; used after a job has shrunk to the surviving ranks)."""
     level = [p.float() for p in parts]
-    if len(level) & (len(level) - 1):
-        raise ValueError("tree_sum needs a power-of-two number of parts")
+    if not level:
+        raise ValueError("tree_sum needs at least one part")
     while len(level) > 1:
-        level = [level[i] + level[i + 1] for i in range(0, len(level), 2)]
+        nxt = [level[i] + level[i + 1] for i in range(0, len(level) - 1, 2)]
+        if len(level) & 1:
+            nxt.append(level[-1])
+        level = nxt
     return level[0]
 
 

@@ -59,3 +59,53 @@ class PeerMonitor:
             except Exception as e:  # noqa: BLE001  (c10d raises DistStoreError / RuntimeError on timeout)
                 reason = "announced that it left" if self._left(r) else f"no heartbeat within {self.timeout.total_seconds():.1f} s"
                 raise PeerLost(r, step, reason) from e
+
+
+    # ------------------------------------------------------------------ elastic shrink
+    def survivors(self, step: int) -> list[int]:
+        """Ranks that have reached ``step`` (this one included); never raises. A rank counts as
+        gone when it announced that it left or shows no heartbeat within the limit."""
+        self.store.set(f"alive/{self.rank}/{step}", b"1")
+        alive = []
+        for r in range(self.world):
+            if r == self.rank:
+                alive.append(r)
+                continue
+            if self._left(r):
+                continue
+            try:
+                self.store.wait([f"alive/{r}/{step}"], self.timeout)
+                alive.append(r)
+            except Exception:  # noqa: BLE001
+                pass
+        return alive
+
+    def agree_on_survivors(self, step: int) -> list[int]:
+        """One list for every surviving rank: the lowest-ranked survivor (in each rank's own
+        view) publishes its view, the others adopt it. Raises :class:`PeerLost` if this rank is
+        not in the agreed list (it was too slow and has been dropped)."""
+        mine = self.survivors(step)
+        leader = mine[0]
+        key = f"decision/{step}"
+        if leader == self.rank:
+            self.store.set(key, ",".join(str(r) for r in mine).encode())
+            return mine
+        try:
+            self.store.wait([key], self.timeout * 3)
+        except Exception as e:  # noqa: BLE001
+            raise PeerLost(leader, step, "the lowest surviving rank published no decision") from e
+        agreed = [int(x) for x in self.store.get(key).decode().split(",")]
+        if self.rank not in agreed:
+            raise PeerLost(self.rank, step, "this rank was dropped from the job by the survivors")
+        return agreed
+
+
+def shrink_group(monitor: PeerMonitor, step: int):
+    """After a :class:`PeerLost`: agree on the surviving ranks and build a process group of
+    them without the ones that are gone (``new_group`` with local synchronisation, so the
+    departed ranks need not take part). Returns ``(group, ranks)``. Call it between steps, with
+    no collective in flight. The deterministic all-reduce accepts any number of CPU ranks; its
+    CUDA kernel takes 1, 2, 4 or 8, so a GPU job continues on the largest such prefix."""
+    ranks = monitor.agree_on_survivors(step)
+    group = dist.new_group(ranks, use_local_synchronization=True)
+    return group, ranks

@@ -117,8 +117,10 @@ def test_tree_sum_order():
     parts = [torch.tensor([1e8]), torch.tensor([1.0]), torch.tensor([-1e8]), torch.tensor([1.0])]
     # ((1e8 + 1) + (-1e8 + 1)) in fp32: 1e8 + 1 rounds to 1e8
     assert tree_sum(parts).item() == ((torch.tensor(1e8) + 1.0) + (torch.tensor(-1e8) + 1.0)).item()
+    # a count that is not a power of two: the odd element moves up a level unchanged
+    assert tree_sum(parts[:3]).item() == ((torch.tensor(1e8) + 1.0) + torch.tensor(-1e8)).item()
     with pytest.raises(ValueError):
-        tree_sum(parts[:3])
+        tree_sum([])
 
 
 def _vp_worker(rank, world, port, out_dir):
@@ -170,3 +172,46 @@ def test_vocab_parallel_logp_gloo_bitwise_equals_single_process(tmp_path, world)
     valid = (ids >= 0) & (ids < v)
     want = torch.where(valid, ref.gather(1, ids.clamp(0, v - 1)[:, None])[:, 0], torch.zeros(()))
     assert (logp - want).abs().max().item() < 1e-4
+
+
+def _elastic_worker(rank, world, port, out_dir):
+    _init(rank, world, port, timeout_s=30)
+    from kernel_align_b200.parallel.collectives import all_reduce_det
+    from kernel_align_b200.parallel.health import PeerLost, PeerMonitor, shrink_group
+
+    mon = PeerMonitor(timeout_s=2.0)
+    x = torch.full((8,), float(rank + 1))
+    mon.check(0)
+    all_reduce_det(x)                                  # step 0: all four ranks, sum = 10
+    if rank == 3:
+        mon.announce_leave()                           # leaves between steps, nothing in flight
+        time.sleep(8)
+        return
+    try:
+        mon.check(1)
+        outcome = "no loss seen"
+        group, ranks = None, list(range(world))
+    except PeerLost as e:
+        outcome = f"lost {e.rank}"
+        group, ranks = shrink_group(mon, 1)
+    y = torch.full((8,), float(rank + 1))
+    all_reduce_det(y, group)                           # step 1 on the survivors: 1 + 2 + 3 = 6
+    torch.save({"outcome": outcome, "ranks": ranks, "x": x, "y": y}, os.path.join(out_dir, f"r{rank}.pt"))
+    time.sleep(1)
+
+
+def test_job_shrinks_to_the_survivors_and_keeps_reducing(tmp_path):
+    """Elastic recovery on the host: a rank leaves between steps, the others notice it, agree
+    on the survivor list, form a group without it and keep running the fixed-order all-reduce
+    (three ranks: the tree carries the odd element up)."""
+    from kernel_align_b200.parallel.collectives import tree_sum
+
+    mp.spawn(_elastic_worker, args=(4, 29731, str(tmp_path)), nprocs=4, join=True)
+    outs = [torch.load(tmp_path / f"r{r}.pt") for r in range(3)]
+    for o in outs:
+        assert o["outcome"] == "lost 3" and o["ranks"] == [0, 1, 2]
+        assert torch.equal(o["x"], torch.full((8,), 10.0)) and torch.equal(o["y"], torch.full((8,), 6.0))
+    parts = [torch.tensor([0.1]), torch.tensor([0.2]), torch.tensor([0.3])]
+    assert torch.equal(tree_sum(parts), (parts[0] + parts[1]) + parts[2])
+    five = [torch.tensor([float(i)]) for i in range(5)]
+    assert tree_sum(five).item() == 10.0

@@ -50,12 +50,29 @@ class GRPOTrainer:
         self.dp_rank = dist.get_rank(dp_group) if self.dp else 0
         self.dp_world = dist.get_world_size(dp_group) if self.dp else 1
         self.reducer = None
+        self._bucket_bytes = bucket_bytes
         self.on_cuda = next(model.parameters()).device.type == "cuda"
         if self.dp and self.on_cuda:
             from ..parallel.collectives import GradReducer
 
             self.reducer = GradReducer(model.parameters(), group=dp_group, bucket_bytes=bucket_bytes, average=True)
         self.optimizer = FusedAdamW(model.parameters(), lr=lr, weight_decay=weight_decay)
+
+    def rebind_data_parallel(self, group) -> None:
+        """Continue on another data-parallel group (after ``parallel.health.shrink_group``: the
+        ranks that are left). Call between steps."""
+        self.dp_group = group
+        self.dp_world = dist.get_world_size(group)
+        self.dp_rank = dist.get_rank(group)
+        self.dp = self.dp_world > 1
+        if self.reducer is not None:
+            self.reducer.close()
+            self.reducer = None
+        if self.dp and self.on_cuda:
+            from ..parallel.collectives import GradReducer
+
+            self.reducer = GradReducer(self.model.parameters(), group=group, bucket_bytes=self._bucket_bytes,
+                                       average=True)
 
     # ------------------------------------------------------------------ phases
     def rollout(self, prompts: torch.Tensor) -> dict:

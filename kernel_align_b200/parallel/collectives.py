@@ -199,3 +199,12 @@ class GradReducer:
     def check(self) -> None:
         for b in self.buckets:
             b["vec"].check()
+
+    def close(self) -> None:
+        """Detach from the parameters (before a reducer over another group replaces this one):
+        the hooks are removed and the gradients stop being views of the buckets."""
+        for h in self._hooks:
+            h.remove()
+        self._hooks = []
+        for p in self.params:
+            p.grad = None

@@ -503,3 +503,46 @@ def test_cpu_strategy_layouts_build_the_right_groups(tmp_path):
     # the tensor-parallel pairs agree with each other and differ across data-parallel replicas
     assert torch.equal(o[0]["logp"], o[1]["logp"]) and torch.equal(o[2]["logp"], o[3]["logp"])
     assert not torch.equal(o[0]["logp"], o[2]["logp"])
+
+
+def _elastic_dp_worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    import datetime
+    import time
+
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=30))
+    torch.set_num_threads(2)
+    from kernel_align_b200.parallel.health import PeerLost, PeerMonitor, shrink_group
+
+    cfg = _cfg()
+    solo = TPContext.__new__(TPContext)
+    solo.group, solo.rank, solo.world, solo.device, solo._arenas = None, 0, 1, CPU, {}
+    model = LlamaModel(cfg, tp=solo, seed=4, device=CPU)
+    trainer = GRPOTrainer(model, lambda p, t: (t % 5 == 0).float().mean(1), group_size=2, max_new_tokens=3, lr=1e-3,
+                          seed=3, top_k=50, data_parallel=True)
+    prompts = torch.randint(0, cfg.vocab_size, (2, 8), generator=torch.Generator().manual_seed(20 + rank))
+    mon = PeerMonitor(timeout_s=2.0)
+    mon.check(0)
+    trainer.train_step(prompts)
+    if rank == 2:
+        mon.announce_leave()
+        time.sleep(8)
+        return
+    try:
+        mon.check(1)
+    except PeerLost:
+        group, ranks = shrink_group(mon, 1)
+        trainer.rebind_data_parallel(group)
+    loss = trainer.train_step(prompts)["loss"]
+    torch.save({"w": model.lm_head.detach().clone(), "loss": loss, "dp_world": trainer.dp_world},
+               os.path.join(out_dir, f"r{rank}.pt"))
+    time.sleep(1)
+
+
+def test_cpu_data_parallel_training_continues_after_a_rank_leaves(tmp_path):
+    mp.spawn(_elastic_dp_worker, args=(3, 29821, str(tmp_path)), nprocs=3, join=True)
+    a, b = torch.load(tmp_path / "r0.pt"), torch.load(tmp_path / "r1.pt")
+    assert a["dp_world"] == 2 and b["dp_world"] == 2
+    assert torch.equal(a["w"], b["w"]) and torch.isfinite(a["loss"]) and torch.isfinite(b["loss"])

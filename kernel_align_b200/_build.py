@@ -62,6 +62,8 @@ def build_cuda(force: bool = False, verbose: bool = False) -> Path | None:
     """Compile every ``csrc/sm100/*.cu`` for sm_100a and link ``libka_sm100.so``."""
     nvcc = _nvcc()
     srcs = sorted((CSRC / "sm100").glob("*.cu"))
+    if not srcs:      # an installed wheel carries the built library, not the sources
+        return CUDA_LIB if CUDA_LIB.exists() else None
     deps = srcs + sorted((CSRC / "sm100").rglob("*.cuh")) + sorted((CSRC / "sm100").rglob("*.h"))
     digest = _digest(deps, NVCC_FLAGS)
     if not force and _stamp_ok(CUDA_LIB, digest):
@@ -88,7 +90,7 @@ def build_cpu(force: bool = False) -> Path | None:
     """Compile ``csrc/cpu/*.cpp`` into ``libka_cpu.so`` (the CPU oracle and CPU code path)."""
     srcs = sorted((CSRC / "cpu").glob("*.cpp"))
     if not srcs:
-        return None
+        return CPU_LIB if CPU_LIB.exists() else None
     deps = srcs + sorted((CSRC / "cpu").rglob("*.h"))
     digest = _digest(deps, CXX_FLAGS)
     if not force and _stamp_ok(CPU_LIB, digest):

@@ -42,6 +42,10 @@ class OpBackend(Enum, metaclass=_LookupMeta):
     SM100_ALLREDUCE = "kernel_align_b200.parallel.collectives.all_reduce_det"
     SM100_GEMM_RS = "kernel_align_b200.parallel.tp_gemm.gemm_reduce_scatter"
     SM100_AG_GEMM = "kernel_align_b200.parallel.tp_gemm.all_gather_gemm"
+    SM100_ATTENTION_BWD = "kernel_align_b200.ops.attention.attention_backward"
+    SM100_ATTENTION_DECODE = "kernel_align_b200.ops.decode.attention_decode"
+    SM100_GEMM_SKINNY = "kernel_align_b200.ops.gemm.gemm_skinny"
+    SM100_ADVANTAGES = "kernel_align_b200.ops.grpo_loss.group_advantages"
     # names the reference exposes: enum aliases of the native operators above (same value),
     # so OpBackend["FLASHINFER"] is OpBackend.SM100_FUSED_LOGP
     FLASH_ATTN = "kernel_align_b200.ops.attention.attention"
@@ -62,6 +66,12 @@ _ROUTES: list[tuple[str, OpBackend]] = [
     ("ag_gemm", OpBackend.SM100_AG_GEMM),
     ("all_reduce", OpBackend.SM100_ALLREDUCE),
     ("allreduce", OpBackend.SM100_ALLREDUCE),
+    ("attention_backward", OpBackend.SM100_ATTENTION_BWD),
+    ("attention_bwd", OpBackend.SM100_ATTENTION_BWD),
+    ("decode_attention", OpBackend.SM100_ATTENTION_DECODE),
+    ("attention_decode", OpBackend.SM100_ATTENTION_DECODE),
+    ("skinny", OpBackend.SM100_GEMM_SKINNY),
+    ("advantage", OpBackend.SM100_ADVANTAGES),
     ("rmsnorm", OpBackend.SM100_RMSNORM),
     ("norm", OpBackend.SM100_RMSNORM),
     ("rope", OpBackend.SM100_ROPE),

@@ -134,3 +134,15 @@ def test_doctor_reports_and_self_tests():
     st = doctor.self_test()
     assert st["logp_max_abs_err"] < 1e-4 and st["logp_batch_invariant"] and st["sampler_batch_invariant"]
     assert doctor.main(["--json"]) == 0
+
+
+def test_every_registered_operator_resolves_to_a_callable():
+    from kernel_align_b200.kernels.registry import OpBackend, kernel_registry
+
+    for backend in OpBackend:
+        assert callable(kernel_registry.resolve(backend)), backend
+    assert kernel_registry.dispatch("attention_backward") == "SM100_ATTENTION_BWD"
+    assert kernel_registry.dispatch("decode_attention") == "SM100_ATTENTION_DECODE"
+    assert kernel_registry.dispatch("skinny_gemm") == "SM100_GEMM_SKINNY"
+    assert kernel_registry.dispatch("group_advantages") == "SM100_ADVANTAGES"
+    assert kernel_registry.dispatch("attention") == "SM100_ATTENTION"

@@ -12,6 +12,12 @@ from .. import _native
 
 
 def _threads() -> int:
+    """Worker threads of the C++ library: ``KA_CPU_THREADS`` or up to 16 cores. Rows are split
+    over the threads and a row's arithmetic is done by one thread, so the count never changes
+    a result."""
+    env = os.environ.get("KA_CPU_THREADS")
+    if env:
+        return max(1, int(env))
     return max(1, min(16, os.cpu_count() or 1))
 
 

@@ -149,3 +149,22 @@ def test_cpu_gemm_and_rank_emulator():
         assert torch.equal(o, outs[0])  # the emulated rank count never enters the arithmetic
     want = (ref.bfloat16().float() + r.float()).bfloat16().float()
     assert (outs[0] - want).abs().max().item() <= 0.05 * want.abs().max().item()
+
+
+def test_results_do_not_depend_on_the_thread_count(monkeypatch):
+    import torch
+
+    from kernel_align_b200.ops import cpu_ops
+
+    g = torch.Generator().manual_seed(4)
+    h, w = torch.randn(37, 96, generator=g), torch.randn(700, 96, generator=g) * 0.1
+    ids = torch.randint(0, 700, (37,), generator=g)
+    logits = torch.randn(23, 900, generator=g) * 2
+    outs = []
+    for n in ("1", "3", "8"):
+        monkeypatch.setenv("KA_CPU_THREADS", n)
+        outs.append((cpu_ops.lmhead_logp_cpu(h, w, ids), cpu_ops.logits_logp_cpu(logits, ids[:23] % 900),
+                     cpu_ops.sample_cpu(logits, inv_temperature=1.2, top_k=40, top_p=0.9, seed=5, step=2),
+                     cpu_ops.gemm_cpu(h, w)))
+    for o in outs[1:]:
+        assert all(torch.equal(a, b) for a, b in zip(o, outs[0]))

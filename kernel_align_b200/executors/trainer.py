@@ -31,7 +31,7 @@ class GRPOTrainer:
                  weight_decay: float = 0.0, seed: int = 0, data_parallel: bool = False,
                  bucket_bytes: int = 64 << 20, dp_group: Optional["dist.ProcessGroup"] = None,
                  ref_model=None, updates_per_rollout: int = 1, eos_token_id: Optional[int] = None,
-                 pad_token_id: int = 0):
+                 pad_token_id: int = 0, micro_batch: Optional[int] = None):
         self.model = model
         self.reward_fn = reward_fn
         self.group_size, self.max_new_tokens = group_size, max_new_tokens
@@ -42,6 +42,9 @@ class GRPOTrainer:
         # rollouts (after the first the ratio moves away from 1 and the clipping becomes active).
         self.ref_model, self.updates_per_rollout = ref_model, max(1, int(updates_per_rollout))
         self.eos_token_id, self.pad_token_id = eos_token_id, pad_token_id
+        # micro_batch: sequences per backward pass of the policy update (gradient accumulation);
+        # with model.checkpoint_layers it bounds the activation memory of a large rollout batch
+        self.micro_batch = micro_batch
         self.sampler = SamplerBackend(seed=seed)
         self.step_index = 0
         self.dp_group = dp_group
@@ -105,13 +108,34 @@ class GRPOTrainer:
             self.reducer.zero_grad()
         else:
             self.optimizer.zero_grad(set_to_none=True)
-        with profile_range("grpo/policy_forward", dev):
-            logp_new = self.policy_logp(sequences, prompt_len)
-            ref = (logp_ref if logp_ref is not None else logp_old) if self.beta > 0 else None
-            loss, stats = grpo_loss(logp_new, logp_old, advantages, mask=mask, eps_low=self.eps_clip, beta=self.beta,
-                                    logp_ref=ref, return_stats=True)
+        n_seq = sequences.shape[0]
+        mb = n_seq if not self.micro_batch else max(1, min(int(self.micro_batch), n_seq))
+        chunks = [(i, min(n_seq, i + mb)) for i in range(0, n_seq, mb)]
+        # the loss is a mean over all valid tokens: a chunk enters with the share of tokens it holds
+        if mask is not None:
+            valid = mask.float().sum(1)
+            total_valid = valid.sum().clamp_min(1.0)
+        loss, stats = None, None
+        for ci, (lo, hi) in enumerate(chunks):
+            last = ci == len(chunks) - 1
+            if self.reducer is not None:
+                self.reducer.hold = not last
+            with profile_range("grpo/policy_forward", dev):
+                logp_new = self.policy_logp(sequences[lo:hi], prompt_len)
+                ref = (logp_ref if logp_ref is not None else logp_old) if self.beta > 0 else None
+                part, st = grpo_loss(logp_new, logp_old[lo:hi], advantages[lo:hi],
+                                     mask=mask[lo:hi] if mask is not None else None, eps_low=self.eps_clip,
+                                     beta=self.beta, logp_ref=ref[lo:hi] if ref is not None else None,
+                                     return_stats=True)
+                if len(chunks) > 1:
+                    share = (valid[lo:hi].sum() / total_valid) if mask is not None else (hi - lo) / n_seq
+                    part = part * share
+                    st = torch.stack([st[0] * share, st[1] * share, st[2]])     # loss, clip fraction, tokens
+            with profile_range("grpo/backward_and_grad_reduce", dev):
+                part.backward()
+            loss = part.detach() if loss is None else loss + part.detach()
+            stats = st if stats is None else stats + st
         with profile_range("grpo/backward_and_grad_reduce", dev):
-            loss.backward()
             if self.reducer is not None:
                 self.reducer.finish()
             elif self.dp:

@@ -25,6 +25,7 @@ from typing import Optional
 
 import torch
 import torch.nn as nn
+import torch.utils.checkpoint
 
 from ..ops.attention import attention_fn
 from ..ops.layer_ops import rmsnorm_fn, rope_fn, rope_tables, swiglu_fn
@@ -130,6 +131,9 @@ class LlamaModel(nn.Module):
 
         self.cfg = cfg
         self.tp = tp if tp is not None else TPContext(device=device)
+        # activation checkpointing: set to True to store one tensor per layer instead of every
+        # intermediate (about 17 tensors per layer) at the price of a second forward
+        self.checkpoint_layers = False
         dev = self.tp.device
         self.embed = nn.Parameter(_full_weight(cfg.vocab_size, cfg.hidden, cfg.init_std, seed * 1000 + 1, dev))
         self.layers = nn.ModuleList([DecoderLayer(cfg, self.tp, seed * 1000 + 10 + i, dev) for i in range(cfg.n_layers)])
@@ -158,8 +162,15 @@ class LlamaModel(nn.Module):
         if hi - lo < rpr:
             x = torch.cat([x, x.new_zeros(rpr - (hi - lo), x.shape[1])])
         positions = torch.arange(seq_len, device=flat.device).repeat(batch)
+        recompute = self.checkpoint_layers and torch.is_grad_enabled()
         for layer in self.layers:
-            x = layer(x, batch, seq_len, positions, self.rope_cos, self.rope_sin)
+            if recompute:
+                # keep only the layer's input; its activations are recomputed in backward (the
+                # operators are deterministic, so the recomputed values are the same bits)
+                x = torch.utils.checkpoint.checkpoint(layer, x, batch, seq_len, positions, self.rope_cos,
+                                                      self.rope_sin, use_reentrant=False)
+            else:
+                x = layer(x, batch, seq_len, positions, self.rope_cos, self.rope_sin)
         return rmsnorm_fn(x, self.norm, self.cfg.rms_eps)
 
     def token_logp(self, input_ids: torch.Tensor, targets: torch.Tensor, scale: float = 1.0) -> torch.Tensor:

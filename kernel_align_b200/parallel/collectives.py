@@ -153,6 +153,7 @@ class GradReducer:
             cur_bytes += nbytes
         if cur:
             self._make_bucket(cur)
+        self.hold = False      # set while gradients of all but the last micro-batch accumulate
         self._hooks = [p.register_post_accumulate_grad_hook(self._on_grad) for p in self.params]
 
     def _make_bucket(self, plist):
@@ -172,6 +173,8 @@ class GradReducer:
         self.buckets.append(bucket)
 
     def _on_grad(self, p):
+        if self.hold:      # a micro-batch that is not the last: keep accumulating into the buckets
+            return
         b = p._ka_bucket
         b["pending"] -= 1
         if b["pending"] == 0:

@@ -563,3 +563,38 @@ def test_cpu_grpo_learns_the_synthetic_task():
     finally:
         sys.argv = argv
     assert first < 0.4 and last > 0.6
+
+
+def test_cpu_activation_checkpointing_and_micro_batches():
+    cfg = _cfg(layers=2)
+    ids = torch.randint(0, cfg.vocab_size, (2, 40), generator=torch.Generator().manual_seed(2))
+
+    def grads(checkpoint):
+        model = LlamaModel(cfg, seed=1, device=CPU)
+        model.checkpoint_layers = checkpoint
+        (-model.token_logp(ids, ids).mean()).backward()
+        return [p.grad.clone() for p in model.parameters()]
+
+    # recomputed activations are the same bits, so the gradients are too
+    assert all(torch.equal(a, b) for a, b in zip(grads(False), grads(True)))
+
+    def reward(prompts, new_tokens):
+        return (new_tokens % 5 == 0).float().mean(1)
+
+    prompts = torch.randint(0, cfg.vocab_size, (2, 8), generator=torch.Generator().manual_seed(9))
+
+    def run(**kw):
+        model = LlamaModel(cfg, seed=2, device=CPU)
+        model.checkpoint_layers = kw.pop("checkpoint", False)
+        t = GRPOTrainer(model, reward, group_size=4, max_new_tokens=4, temperature=1.0, top_k=50, lr=1e-3, seed=3, **kw)
+        out = t.train_step(prompts)
+        return out["loss"].item(), model.lm_head.detach().float().clone(), float(out["clip_fraction"])
+
+    full = run()
+    micro = run(micro_batch=3, checkpoint=True)           # 8 sequences as 3 + 3 + 2
+    assert abs(full[0] - micro[0]) < 1e-5 * max(1.0, abs(full[0])) + 1e-6
+    # the first AdamW step moves every weight by about +-lr: the two runs may disagree only where a
+    # gradient is so close to zero that accumulating in three pieces flips its sign
+    moved_apart = ((full[1] - micro[1]).abs() > 1e-4).float().mean().item()
+    assert moved_apart < 0.02
+    assert run(micro_batch=3, checkpoint=True)[0] == micro[0]       # and it is repeatable

@@ -33,6 +33,7 @@ def main():
     ap.add_argument("--tiny", action="store_true", help="hidden 1024 instead of the 8B layer shapes")
     ap.add_argument("--micro-batch", type=int, default=None, help="sequences per backward pass of the policy update")
     ap.add_argument("--checkpoint-layers", action="store_true", help="recompute layer activations in backward")
+    ap.add_argument("--zero", type=int, default=0, choices=[0, 1], help="1: shard the optimizer state over the ranks")
     ap.add_argument("--json-out", default=None)
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -58,7 +59,7 @@ def main():
         model = LlamaModel(cfg, tp=solo, seed=1, device=dev)
         model.checkpoint_layers = args.checkpoint_layers
         trainer = GRPOTrainer(model, reward, group_size=args.group, max_new_tokens=args.new_tokens, temperature=1.0,
-                              top_k=50, top_p=0.95, lr=1e-6, seed=5, data_parallel=world > 1, micro_batch=args.micro_batch)
+                              top_k=50, top_p=0.95, lr=1e-6, seed=5, data_parallel=world > 1, micro_batch=args.micro_batch, zero_stage=args.zero)
         prompts = torch.randint(0, cfg.vocab_size, (args.prompts, args.prompt_len), device=dev,
                                 generator=torch.Generator(device=dev).manual_seed(100 + rank))
         run_losses = []

@@ -31,7 +31,7 @@ class GRPOTrainer:
                  weight_decay: float = 0.0, seed: int = 0, data_parallel: bool = False,
                  bucket_bytes: int = 64 << 20, dp_group: Optional["dist.ProcessGroup"] = None,
                  ref_model=None, updates_per_rollout: int = 1, eos_token_id: Optional[int] = None,
-                 pad_token_id: int = 0, micro_batch: Optional[int] = None):
+                 pad_token_id: int = 0, micro_batch: Optional[int] = None, zero_stage: int = 0):
         self.model = model
         self.reward_fn = reward_fn
         self.group_size, self.max_new_tokens = group_size, max_new_tokens
@@ -59,7 +59,15 @@ class GRPOTrainer:
             from ..parallel.collectives import GradReducer
 
             self.reducer = GradReducer(model.parameters(), group=dp_group, bucket_bytes=bucket_bytes, average=True)
-        self.optimizer = FusedAdamW(model.parameters(), lr=lr, weight_decay=weight_decay)
+        if zero_stage == 1 and self.dp:
+            # optimizer state sharded over the data-parallel ranks (parallel/zero.py)
+            from ..parallel.zero import ShardedAdamW
+
+            self.optimizer = ShardedAdamW(model.parameters(), group=dp_group, lr=lr, weight_decay=weight_decay)
+        elif zero_stage not in (0, 1):
+            raise ValueError("zero_stage must be 0 or 1")
+        else:
+            self.optimizer = FusedAdamW(model.parameters(), lr=lr, weight_decay=weight_decay)
 
     def rebind_data_parallel(self, group) -> None:
         """Continue on another data-parallel group (after ``parallel.health.shrink_group``: the

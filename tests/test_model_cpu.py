@@ -598,3 +598,44 @@ def test_cpu_activation_checkpointing_and_micro_batches():
     moved_apart = ((full[1] - micro[1]).abs() > 1e-4).float().mean().item()
     assert moved_apart < 0.02
     assert run(micro_batch=3, checkpoint=True)[0] == micro[0]       # and it is repeatable
+
+
+def _zero_worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.set_num_threads(2)
+    cfg = _cfg()
+    solo = TPContext.__new__(TPContext)
+    solo.group, solo.rank, solo.world, solo.device, solo._arenas = None, 0, 1, CPU, {}
+    prompts = torch.randint(0, cfg.vocab_size, (2, 8), generator=torch.Generator().manual_seed(20 + rank))
+    res = {}
+    for stage in (0, 1):
+        model = LlamaModel(cfg, tp=solo, seed=4, device=CPU)
+        trainer = GRPOTrainer(model, lambda p, t: (t % 5 == 0).float().mean(1), group_size=2, max_new_tokens=3,
+                              lr=1e-3, seed=3, top_k=50, data_parallel=True, zero_stage=stage, weight_decay=0.01)
+        losses = [trainer.train_step(prompts)["loss"].item() for _ in range(3)]
+        if stage == 1:                                   # a shard checkpoint restores into a fresh optimizer
+            sd = trainer.optimizer.state_dict()
+            trainer.optimizer.load_state_dict(sd)
+            res["state_bytes"] = trainer.optimizer.state_bytes()
+        else:
+            res["full_state_bytes"] = sum(t.numel() * 4 for st in trainer.optimizer.state for t in st.values())
+        res[stage] = {"losses": losses, "head": model.lm_head.detach().clone(), "wqkv": model.layers[0].wqkv.detach().clone(),
+                      "norm": model.norm.detach().clone()}
+    torch.save(res, os.path.join(out_dir, f"r{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_cpu_sharded_optimizer_state_gives_the_same_weights(tmp_path):
+    """ZeRO stage 1 over two gloo ranks: losses and weights after three steps are bitwise those
+    of the unsharded AdamW, with half the optimizer state per rank."""
+    mp.spawn(_zero_worker, args=(2, 29831, str(tmp_path)), nprocs=2, join=True)
+    for r in range(2):
+        o = torch.load(tmp_path / f"r{r}.pt")
+        assert o[0]["losses"] == o[1]["losses"]
+        for k in ("head", "wqkv", "norm"):
+            assert torch.equal(o[0][k], o[1][k]), k
+        assert o["state_bytes"] <= o["full_state_bytes"] // 2 + 64

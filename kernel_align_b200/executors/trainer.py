@@ -31,7 +31,8 @@ class GRPOTrainer:
                  weight_decay: float = 0.0, seed: int = 0, data_parallel: bool = False,
                  bucket_bytes: int = 64 << 20, dp_group: Optional["dist.ProcessGroup"] = None,
                  ref_model=None, updates_per_rollout: int = 1, eos_token_id: Optional[int] = None,
-                 pad_token_id: int = 0, micro_batch: Optional[int] = None, zero_stage: int = 0):
+                 pad_token_id: int = 0, micro_batch: Optional[int] = None, zero_stage: int = 0,
+                 max_grad_norm: Optional[float] = None):
         self.model = model
         self.reward_fn = reward_fn
         self.group_size, self.max_new_tokens = group_size, max_new_tokens
@@ -45,6 +46,10 @@ class GRPOTrainer:
         # micro_batch: sequences per backward pass of the policy update (gradient accumulation);
         # with model.checkpoint_layers it bounds the activation memory of a large rollout batch
         self.micro_batch = micro_batch
+        # max_grad_norm: clip the global gradient norm (computed in a fixed order, over the
+        # tensor-parallel shards too); applied as a scale inside the fused optimizer kernel
+        self.max_grad_norm = max_grad_norm
+        self.last_grad_norm: Optional[torch.Tensor] = None
         self.sampler = SamplerBackend(seed=seed)
         self.step_index = 0
         self.dp_group = dp_group
@@ -154,9 +159,42 @@ class GRPOTrainer:
                     if p.grad is not None:
                         all_reduce_det(p.grad, self.dp_group)
                         p.grad.div_(self.dp_world)
+            if getattr(self.model, "tp", None) is not None and self.model.tp.world > 1:
+                self.model.reduce_replicated_grads()     # norm and embedding weights of a sharded model
         with profile_range("grpo/optimizer", dev):
-            self.optimizer.step()
+            self.optimizer.step(grad_scale=self._clip_scale())
         return loss, stats
+
+    def _clip_scale(self) -> float:
+        if self.max_grad_norm is None:
+            return 1.0
+        tp = getattr(self.model, "tp", None)
+        sharded_model = tp is not None and tp.world > 1
+        replicated = {id(p) for p in self.model.replicated_parameters()} if sharded_model else set()
+        zero = None
+        sq_shard, sq_repl = zero, zero
+        for p in self.model.parameters():              # parameter order: a fixed summation order
+            if p.grad is None:
+                continue
+            term = p.grad.float().pow(2).sum()
+            if id(p) in replicated:
+                sq_repl = term if sq_repl is None else sq_repl + term
+            else:
+                sq_shard = term if sq_shard is None else sq_shard + term
+        if sq_shard is None and sq_repl is None:
+            return 1.0
+        if sharded_model and sq_shard is not None:
+            # shards of a tensor-parallel model: sum the ranks' parts in the fixed tree order;
+            # replicated tensors (embedding, norms) are counted once
+            from ..parallel.collectives import all_reduce_det
+
+            sq_shard = sq_shard.reshape(1).clone()
+            all_reduce_det(sq_shard, tp.group)
+            sq_shard = sq_shard[0]
+        sq = sq_shard if sq_repl is None else (sq_repl if sq_shard is None else sq_shard + sq_repl)
+        norm = sq.sqrt()
+        self.last_grad_norm = norm.detach()
+        return float(min(1.0, self.max_grad_norm / (norm.item() + 1e-6)))
 
     def train_step(self, prompts: torch.Tensor) -> dict:
         prompt_len = prompts.shape[1]

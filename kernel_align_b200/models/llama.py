@@ -146,6 +146,30 @@ class LlamaModel(nn.Module):
         self.register_buffer("rope_cos", cos, persistent=False)
         self.register_buffer("rope_sin", sin, persistent=False)
 
+    def replicated_parameters(self) -> list:
+        """Parameters that every tensor-parallel rank holds in full (embedding and norm weights);
+        all others are shards."""
+        out = [self.embed, self.norm]
+        for layer in self.layers:
+            out += [layer.norm1, layer.norm2]
+        return out
+
+    def reduce_replicated_grads(self) -> None:
+        """Sum the gradients of the replicated parameters over the tensor-parallel group (call
+        after backward, before the optimizer). Each rank normalises and embeds only its own token
+        rows, so its gradient of a norm weight or of the embedding is a partial sum; without
+        this step the copies of those parameters would drift apart. Fixed tree order."""
+        if self.tp.world == 1:
+            return
+        from ..parallel.collectives import all_reduce_det
+
+        for p in self.replicated_parameters():
+            if not p.requires_grad:
+                continue
+            if p.grad is None:
+                p.grad = torch.zeros_like(p)
+            all_reduce_det(p.grad, self.tp.group)
+
     def rows_per_rank(self, tokens: int) -> int:
         return rows_per_rank(tokens, self.tp.world)
 

@@ -722,3 +722,19 @@ def test_cpu_tensor_parallel_gradients_match_the_unsharded_model(tmp_path):
         close(o["wgu"], torch.cat([gu[r * f:(r + 1) * f], gu[cfg.ffn + r * f: cfg.ffn + (r + 1) * f]]), "wgu")
     for k in ("embed", "norm", "norm1", "norm2"):
         assert torch.equal(outs[0][k], outs[1][k]), k
+
+
+@pytest.mark.parametrize("strategy,extra", [("hybrid", ["--tp", "2"]), ("pipeline_parallel", []), ("data_parallel", [])])
+def test_cpu_parallel_layouts_example_runs_under_torchrun(strategy, extra):
+    import re
+    import subprocess
+
+    port = 29850 + len(strategy)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), os.path.join(ROOT, "examples", "parallel_layouts.py"), "--strategy", strategy, *extra]
+    env = dict(os.environ, OMP_NUM_THREADS="2", CUDA_VISIBLE_DEVICES="")
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert res.returncode == 0, (res.stdout + res.stderr)[-2000:]
+    m = re.search(r"sum of log-probs = (-?[0-9.]+)", res.stdout)
+    assert m, res.stdout[-500:]
+    assert abs(float(m.group(1)) - (-4.0 * 24 * 6.24)) < 60.0       # about -ln(512) per token at random init

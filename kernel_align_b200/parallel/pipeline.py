@@ -42,14 +42,16 @@ def stage_layers(n_layers: int, stage: int, n_stages: int) -> range:
 
 class PipelineStage(nn.Module):
     def __init__(self, cfg: LlamaConfig, stage: int, n_stages: int, seed: int = 0, device=None,
-                 group: Optional[dist.ProcessGroup] = None):
+                 group: Optional[dist.ProcessGroup] = None, tp: Optional[TPContext] = None):
         super().__init__()
         if not 0 <= stage < n_stages or n_stages > cfg.n_layers:
             raise ValueError("need 0 <= stage < n_stages <= n_layers")
         dev = torch.device(device) if device is not None else \
             (torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu"))
         self.cfg, self.stage, self.n_stages, self.group = cfg, stage, n_stages, group
-        self.tp = _solo_context(dev)
+        # tp: shard this stage's layers over a tensor-parallel group as well (3-D layouts); the
+        # pipeline group then links the ranks with the same tensor-parallel rank
+        self.tp = tp if tp is not None else _solo_context(dev)
         self.first, self.last = stage == 0, stage == n_stages - 1
         self.layer_ids = stage_layers(cfg.n_layers, stage, n_stages)
         # the seeds of LlamaModel: embedding seed * 1000 + 1, head + 2, layer i + 10 + i
@@ -57,8 +59,12 @@ class PipelineStage(nn.Module):
         if self.first:
             self.embed = nn.Parameter(_full_weight(cfg.vocab_size, cfg.hidden, cfg.init_std, seed * 1000 + 1, dev))
         if self.last:
+            from ..ops.fused_logp import vocab_shard_range
+
             self.norm = nn.Parameter(torch.ones(cfg.hidden, dtype=torch.bfloat16, device=dev))
-            self.lm_head = nn.Parameter(_full_weight(cfg.vocab_size, cfg.hidden, cfg.init_std, seed * 1000 + 2, dev))
+            head = _full_weight(cfg.vocab_size, cfg.hidden, cfg.init_std, seed * 1000 + 2, dev)
+            lo, hi = vocab_shard_range(cfg.vocab_size, self.tp.rank, self.tp.world)
+            self.lm_head = nn.Parameter(head[lo:hi].contiguous())
         cos, sin = rope_tables(cfg.max_pos, cfg.head_dim, cfg.rope_theta, device=dev)
         self.register_buffer("rope_cos", cos, persistent=False)
         self.register_buffer("rope_sin", sin, persistent=False)
@@ -74,12 +80,56 @@ class PipelineStage(nn.Module):
         return x
 
     def embed_tokens(self, input_ids: torch.Tensor) -> torch.Tensor:
+        """This tensor-parallel rank's token rows of the embedded micro-batch (zero padded)."""
         tokens = input_ids.numel()
-        rpr = rows_per_rank(tokens, 1)
-        x = torch.nn.functional.embedding(input_ids.reshape(-1), self.embed)
-        if tokens < rpr:
-            x = torch.cat([x, x.new_zeros(rpr - tokens, x.shape[1])])
+        rpr = rows_per_rank(tokens, self.tp.world)
+        flat = input_ids.reshape(-1)
+        lo, hi = min(tokens, self.tp.rank * rpr), min(tokens, (self.tp.rank + 1) * rpr)
+        x = torch.nn.functional.embedding(flat[lo:hi], self.embed)
+        if hi - lo < rpr:
+            x = torch.cat([x, x.new_zeros(rpr - (hi - lo), x.shape[1])])
         return x
+
+    def token_logp(self, x_local: torch.Tensor, targets: torch.Tensor, scale: float) -> torch.Tensor:
+        """Last stage: final norm and the LM head (vocabulary parallel over the tensor-parallel
+        group) on this stage's output rows."""
+        from ..ops.fused_logp import VocabParallel
+
+        tokens = targets.numel()
+        h = rmsnorm_fn(x_local, self.norm, self.cfg.rms_eps)
+        if self.tp.world == 1:
+            return lmhead_logp(h[:tokens], self.lm_head, targets.reshape(-1), scale=scale).view(targets.shape)
+        from ..models.dist_autograd import all_gather_rows
+
+        full = all_gather_rows(h, self.tp)[:tokens]
+        if full.device.type == "cuda":
+            from .peer import vocab_parallel_group
+
+            vp = vocab_parallel_group(self.cfg.vocab_size, group=self.tp.group)
+        else:
+            vp = VocabParallel(rank=self.tp.rank, world=self.tp.world, process_group=self.tp.group)
+        return lmhead_logp(full, self.lm_head, targets.reshape(-1), vocab=self.cfg.vocab_size, group=vp,
+                           scale=scale).view(targets.shape)
+
+    def replicated_parameters(self) -> list:
+        out = [self.embed] if self.first else []
+        if self.last:
+            out.append(self.norm)
+        for layer in self.layers:
+            out += [layer.norm1, layer.norm2]
+        return out
+
+    def reduce_replicated_grads(self) -> None:
+        """As ``LlamaModel.reduce_replicated_grads``: sum the partial gradients of the weights
+        that the tensor-parallel ranks of this stage hold in full."""
+        if self.tp.world == 1:
+            return
+        from .collectives import all_reduce_det
+
+        for p in self.replicated_parameters():
+            if p.grad is None:
+                p.grad = torch.zeros_like(p)
+            all_reduce_det(p.grad, self.tp.group)
 
 
 def _peer(stage_model: PipelineStage, stage: int) -> int:
@@ -103,7 +153,7 @@ def pipeline_logp_step(model: PipelineStage, input_ids: torch.Tensor, targets: t
     mb = b // n_micro
     dev = model.device
     cfg = model.cfg
-    rpr = rows_per_rank(mb * seq_len, 1)
+    rpr = rows_per_rank(mb * seq_len, model.tp.world)
     train = loss_fn is not None
     saved = []          # per micro-batch: (input activation that needs a gradient, output or loss)
     logps = []
@@ -122,9 +172,8 @@ def pipeline_logp_step(model: PipelineStage, input_ids: torch.Tensor, targets: t
                 x = x_in
             x = model.run_layers(x, mb, seq_len)
             if model.last:
-                h = rmsnorm_fn(x, model.norm, cfg.rms_eps)
                 tg = targets[m * mb:(m + 1) * mb].to(dev)
-                logp = lmhead_logp(h[: mb * seq_len], model.lm_head, tg.reshape(-1), scale=scale).view(mb, seq_len)
+                logp = model.token_logp(x, tg, scale)
                 logps.append(logp.detach())
                 if train:
                     part = loss_fn(logp, m)
@@ -146,6 +195,7 @@ def pipeline_logp_step(model: PipelineStage, input_ids: torch.Tensor, targets: t
             if not model.first:
                 dist.send(x_in.grad.contiguous(), dst=_peer(model, model.stage - 1), group=model.group)
             saved[m] = None
+        model.reduce_replicated_grads()
     if model.last:
         return torch.cat(logps), total
     return None, None

@@ -91,17 +91,16 @@ def make_layout(strategy, tp_size: Optional[int] = None, pp_size: Optional[int] 
 
 def build_model(cfg, layout: ParallelLayout, seed: int = 0, device=None):
     """The model object of this rank: a :class:`LlamaModel` over the tensor-parallel group, or,
-    with pipeline stages, the :class:`PipelineStage` of this rank (tensor parallelism inside a
-    pipeline stage is not implemented)."""
+    with pipeline stages, the :class:`PipelineStage` of this rank (its layers sharded over the
+    tensor-parallel group when there is one: tp x pp x dp)."""
     from ..models.llama import LlamaModel
     from .tp_gemm import TPContext
 
     if layout.pp_size > 1:
-        if layout.tp_size > 1:
-            raise NotImplementedError("pipeline stages are not tensor parallel")
         from .pipeline import PipelineStage
 
-        return PipelineStage(cfg, layout.pp_rank, layout.pp_size, seed=seed, device=device, group=layout.pp_group)
+        tp = TPContext(group=layout.tp_group, device=device) if layout.tp_size > 1 else None
+        return PipelineStage(cfg, layout.pp_rank, layout.pp_size, seed=seed, device=device, group=layout.pp_group, tp=tp)
     if layout.tp_size > 1:
         tp = TPContext(group=layout.tp_group, device=device)
     else:

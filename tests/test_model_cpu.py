@@ -738,3 +738,47 @@ def test_cpu_parallel_layouts_example_runs_under_torchrun(strategy, extra):
     m = re.search(r"sum of log-probs = (-?[0-9.]+)", res.stdout)
     assert m, res.stdout[-500:]
     assert abs(float(m.group(1)) - (-4.0 * 24 * 6.24)) < 60.0       # about -ln(512) per token at random init
+
+
+def _three_d_worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.set_num_threads(2)
+    from kernel_align_b200.parallel.pipeline import pipeline_logp_step
+    from kernel_align_b200.parallel.strategy import build_model, make_layout
+
+    lay = make_layout("hybrid", tp_size=2, pp_size=2)            # 4 ranks: tp 2 x pp 2 x dp 1
+    cfg = _cfg(layers=4)
+    stage = build_model(cfg, lay, seed=1, device=CPU)
+    ids = torch.randint(0, cfg.vocab_size, (4, 24), generator=torch.Generator().manual_seed(2))
+    n_tok = ids.numel()
+    logp, loss = pipeline_logp_step(stage, ids, ids, n_micro=2, loss_fn=lambda lp, m: -lp.sum() / n_tok)
+    norms = {f"{i}": layer.norm1.grad.clone() for i, layer in zip(stage.layer_ids, stage.layers)}
+    torch.save({"logp": logp, "loss": loss, "norm1": norms, "tp_rank": lay.tp_rank, "pp_rank": lay.pp_rank},
+               os.path.join(out_dir, f"r{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_cpu_three_dimensional_layout_matches_the_unsplit_model(tmp_path):
+    """tp 2 x pp 2 on four gloo ranks: the last stage's log-probs equal the single-process
+    model's (the CPU GEMM is fixed order, so even the column-parallel products agree bitwise),
+    and the norm-weight gradients (replicated inside a stage) agree with the unsplit backward."""
+    mp.spawn(_three_d_worker, args=(4, 29861, str(tmp_path)), nprocs=4, join=True)
+    o = [torch.load(tmp_path / f"r{r}.pt") for r in range(4)]
+    cfg = _cfg(layers=4)
+    model = LlamaModel(cfg, seed=1, device=CPU)
+    ids = torch.randint(0, cfg.vocab_size, (4, 24), generator=torch.Generator().manual_seed(2))
+    logp = model.token_logp(ids, ids)
+    (-logp.sum() / ids.numel()).backward()
+    last = [x for x in o if x["pp_rank"] == 1]
+    assert len(last) == 2 and all(x["logp"] is not None for x in last)
+    for x in last:
+        assert (x["logp"] - logp.detach()).abs().max().item() < 2e-2
+    assert torch.equal(last[0]["logp"], last[1]["logp"])
+    for x in o:
+        for i, g in x["norm1"].items():
+            ref = model.layers[int(i)].norm1.grad.float()
+            assert (g.float() - ref).abs().max().item() <= 0.05 * ref.abs().max().item() + 1e-6

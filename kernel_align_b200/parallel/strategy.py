@@ -63,8 +63,7 @@ def make_layout(strategy, tp_size: Optional[int] = None, pp_size: Optional[int] 
     must call it with the same arguments)."""
     strategy = strategy if isinstance(strategy, DistributedStrategy) else DistributedStrategy(str(strategy).lower())
     if not (dist.is_available() and dist.is_initialized()):
-        tp, pp, dp = _sizes(strategy, 1, 1, 1)
-        return ParallelLayout(strategy, 1, 1, 1, 0, 0, 0, None, None, None)
+        return ParallelLayout(strategy, 1, 1, 1, 0, 0, 0, None, None, None)      # a single process
     world, rank = dist.get_world_size(), dist.get_rank()
     tp, pp, dp = _sizes(strategy, world, tp_size, pp_size)
     tp_rank, pp_rank, dp_rank = rank % tp, (rank // tp) % pp, rank // (tp * pp)

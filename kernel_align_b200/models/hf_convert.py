@@ -132,3 +132,38 @@ def to_hf_state_dict(model: LlamaModel) -> dict:
         out[p + "input_layernorm.weight"] = layer.norm1.detach().clone()
         out[p + "post_attention_layernorm.weight"] = layer.norm2.detach().clone()
     return out
+
+
+def load_pretrained(path: str, tp=None, device=None) -> LlamaModel:
+    """Load a Llama checkpoint saved in Hugging Face format (``config.json`` + safetensors or
+    ``.bin`` shards in a local directory) into a :class:`LlamaModel`: the checkpoint is read on
+    the CPU with ``transformers`` and only this rank's shards are copied to ``device``."""
+    import transformers
+
+    hf = transformers.AutoModelForCausalLM.from_pretrained(path, torch_dtype=torch.bfloat16, low_cpu_mem_usage=True)
+    model = from_hf(hf, tp=tp, device=device)
+    del hf
+    return model
+
+
+def save_pretrained(model: LlamaModel, path: str) -> None:
+    """Write the model as a Hugging Face Llama checkpoint (rank 0 of the tensor-parallel group
+    writes; every rank takes part in gathering the shards)."""
+    import transformers
+
+    state = to_hf_state_dict(model)
+    if model.tp.rank != 0:
+        return
+    cfg = model.cfg
+    hf_cfg = transformers.LlamaConfig(hidden_size=cfg.hidden, intermediate_size=cfg.ffn, num_hidden_layers=cfg.n_layers,
+                                      num_attention_heads=cfg.n_heads, num_key_value_heads=cfg.n_kv_heads,
+                                      head_dim=cfg.head_dim, vocab_size=cfg.vocab_size, rms_norm_eps=cfg.rms_eps,
+                                      rope_theta=cfg.rope_theta, max_position_embeddings=cfg.max_pos,
+                                      tie_word_embeddings=False, attention_bias=False, mlp_bias=False,
+                                      torch_dtype="bfloat16")
+    hf = transformers.LlamaForCausalLM(hf_cfg).to(torch.bfloat16)
+    missing, unexpected = hf.load_state_dict({k: v.cpu() for k, v in state.items()}, strict=False)
+    missing = [k for k in missing if "rotary" not in k]
+    if missing or unexpected:
+        raise RuntimeError(f"state dict does not fit the Hugging Face model: missing {missing}, unexpected {unexpected}")
+    hf.save_pretrained(path)

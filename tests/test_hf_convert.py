@@ -88,3 +88,20 @@ def test_sharded_loading_matches_transformers_forward(tmp_path):
     with torch.no_grad():
         ref = torch.log_softmax(hf(input_ids=ids).logits.float(), -1).gather(-1, ids[..., None])[..., 0]
     assert (a - ref).abs().max().item() < 0.05
+
+
+def test_save_and_load_pretrained_directory(tmp_path):
+    from kernel_align_b200.models.hf_convert import load_pretrained, save_pretrained
+
+    hf = _hf_model()
+    model = from_hf(hf, device=CPU)
+    save_pretrained(model, str(tmp_path / "ckpt"))
+    again = load_pretrained(str(tmp_path / "ckpt"), device=CPU)
+    for (n1, p1), (n2, p2) in zip(model.named_parameters(), again.named_parameters()):
+        assert n1 == n2 and torch.equal(p1, p2), n1
+    reloaded = transformers.AutoModelForCausalLM.from_pretrained(str(tmp_path / "ckpt"))
+    ids = torch.randint(0, 512, (1, 16), generator=torch.Generator().manual_seed(4))
+    with torch.no_grad():
+        a = hf(input_ids=ids).logits.float()
+        b = reloaded(input_ids=ids).logits.float()
+    assert (a - b).abs().max().item() < 0.05

@@ -6,18 +6,24 @@
 
 One step = log-probabilities of G*L target tokens given hidden states [G*L, 4096] (bf16)
 and the LM-head weight [128256, 4096] (bf16), G=256, L=512, synthetic N(0,1) / N(0,0.02)
-data. Own arm: the fused tcgen05 LM-head+logprob kernel, vocabulary sharded over the N
-ranks, partial (max, sum-exp, target) exchanged inside the kernel over peer memory; every
-rank ends with all G*L results. Reference arm: `torch.matmul` (cuBLAS) feeding the
-reference's `SamplerBackend.compute_logp` from baseline/_ref, rows split over the ranks
-(the reference has no distributed code, so data parallelism over rows is the only way to
-use it unmodified on N GPUs).
+data. Own arm: the fused tcgen05 LM-head+logprob kernel; on N > 1 GPUs the vocabulary is
+sharded over the ranks and so are the rows: every rank receives G*L/N rows, the kernel pushes
+them to the peers over NVLink while it computes, exchanges the partial (max, sum-exp, target)
+triples the same way, and every rank ends with the results of its own rows. Reference arm:
+`torch.matmul` (cuBLAS) feeding the reference's `SamplerBackend.compute_logp` from
+baseline/_ref, rows split over the ranks (the reference has no distributed code, so data
+parallelism over rows is the only way to use it unmodified on N GPUs).
+
+Both arms stage their inputs the same way in the end-to-end loop and report, as a second
+record, the latency of one sampling call (bf16 logits [G, 128256] ~ N(0, 2), temperature 0.7,
+top-k 50, top-p 0.9, G = 64 / 128 / 256) through their own ``SamplerBackend.sample``.
 
 Prints one JSON line on rank 0.
 """
 from __future__ import annotations
 
 import argparse
+import datetime
 import json
 import os
 import statistics
@@ -94,7 +100,8 @@ def init_dist(n_gpus: int):
     torch.cuda.set_device(local)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local),
+                                timeout=datetime.timedelta(minutes=30))
     if world != n_gpus:
         raise SystemExit(f"--gpus {n_gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {n_gpus}")
     return rank, world, local
@@ -125,26 +132,11 @@ def make_inputs(rows: int, v_rows: int, seed: int):
     return hidden, weight, ids
 
 
-def run_own(args, rank, world, local):
-    sys.path.insert(0, ROOT)
-    from kernel_align_b200.kernels.sampling import SamplerBackend
-    from kernel_align_b200.ops import fused_logp
-
-    rows = args.g * args.seq_len
-    lo, hi = fused_logp.vocab_shard_range(VOCAB, rank, world)
-    hidden, weight, ids = make_inputs(rows, hi - lo, seed=1234)
-    sampler = SamplerBackend()
-    group = None
-    if world > 1:
-        from kernel_align_b200.parallel.peer import vocab_parallel_group
-
-        group = vocab_parallel_group(VOCAB)
-    kw = dict(vocab=VOCAB, group=group)
-    n_panels = -(-rows // fused_logp.DEFAULT_PANEL_ROWS)
-
-    # ---- device-timed kernel throughput
+def time_device(step, args, world, local):
+    """W warm-up calls, then K calls between two CUDA events; max over ranks, with the clocks
+    sampled while the timed calls run."""
     for _ in range(args.warmup):
-        out = sampler.fused_logp(hidden, weight, ids, **kw)
+        step()
     barrier_sync(world)
     clocks = ClockSampler(local)
     clocks.start()
@@ -152,19 +144,20 @@ def run_own(args, rank, world, local):
     barrier_sync(world)
     e0.record()
     for _ in range(args.steps):
-        out = sampler.fused_logp(hidden, weight, ids, **kw)
+        step()
     e1.record()
     barrier_sync(world)
     ms = max_over_ranks(e0.elapsed_time(e1), world) / args.steps
-    clock_info = clocks.stop()
-    fused_logp.check_status(fused_logp.last_status(hidden.device, VOCAB))
+    return ms, clocks.stop()
 
-    # ---- end to end through the public API: pinned host inputs in, log-probs out, per step
-    h_host = hidden.cpu().pin_memory()
-    ids_host = ids.cpu().pin_memory()
-    out_host = torch.empty(rows, dtype=torch.float32).pin_memory()
+
+def time_end_to_end(step, h_host, ids_host, out_host, args, world):
+    """The same staging for both arms: every step copies its inputs from pinned host memory to
+    one of two device buffers on a copy stream (so the copy of step i+1 overlaps the compute of
+    step i), runs ``step(hidden, ids)`` and copies the result to pinned host memory."""
     copy_stream = torch.cuda.Stream()
-    bufs = [(torch.empty_like(hidden), torch.empty_like(ids)) for _ in range(2)]
+    bufs = [(torch.empty(h_host.shape, dtype=h_host.dtype, device="cuda"),
+             torch.empty(ids_host.shape, dtype=ids_host.dtype, device="cuda")) for _ in range(2)]
     ready = [torch.cuda.Event() for _ in range(2)]
     done = [torch.cuda.Event() for _ in range(2)]
 
@@ -176,28 +169,97 @@ def run_own(args, rank, world, local):
             bufs[b][1].copy_(ids_host, non_blocking=True)
             ready[b].record(copy_stream)
 
-    def e2e_steps(n):
+    def run(n):
         stage(0)
         for i in range(n):
             b = i % 2
             if i + 1 < n:
                 stage(i + 1)
             torch.cuda.current_stream().wait_event(ready[b])
-            res = sampler.fused_logp(bufs[b][0], weight, bufs[b][1], **kw)
+            res = step(bufs[b][0], bufs[b][1])
             done[b].record()
-            out_host.copy_(res, non_blocking=True)
+            out_host.copy_(res.reshape(out_host.shape), non_blocking=True)
         torch.cuda.synchronize()
 
     for b in range(2):
         done[b].record()
-    e2e_steps(max(1, min(2, args.warmup)))
+    run(max(1, min(2, args.warmup)))
     barrier_sync(world)
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0.record()
-    e2e_steps(args.steps)
+    run(args.steps)
     t1.record()
     barrier_sync(world)
-    e2e_ms = max_over_ranks(t0.elapsed_time(t1), world) / args.steps
+    return max_over_ranks(t0.elapsed_time(t1), world) / args.steps
+
+
+SAMPLING_CONFIG = {"vocab": VOCAB, "dtype": "bf16", "logits": "N(0, 2)", "temperature": 0.7, "top_k": 50, "top_p": 0.9,
+                   "timing": "CUDA events around each call, L2 flushed between calls, median of 30 after 5 warm-ups"}
+
+
+def time_sampling(sample, calls: int = 30) -> dict:
+    """Latency of one fused sampling call at G = 64 / 128 / 256 (microseconds, median)."""
+    out = {}
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    gen = torch.Generator(device="cuda").manual_seed(99)
+    for g in (64, 128, 256):
+        logits = (torch.randn(g, VOCAB, device="cuda", generator=gen) * 2.0).to(torch.bfloat16)
+        for _ in range(5):
+            sample(logits)
+        times = []
+        for _ in range(calls):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            sample(logits)
+            e1.record()
+            e1.synchronize()
+            times.append(e0.elapsed_time(e1) * 1e3)
+        out[f"g{g}_us"] = statistics.median(times)
+        del logits
+    return out
+
+
+def run_own(args, rank, world, local):
+    sys.path.insert(0, ROOT)
+    from kernel_align_b200.kernels.sampling import SamplerBackend
+    from kernel_align_b200.ops import fused_logp
+
+    rows = args.g * args.seq_len
+    if rows % world:
+        raise SystemExit("G * L must be divisible by the number of GPUs")
+    rows_local = rows // world
+    lo, hi = fused_logp.vocab_shard_range(VOCAB, rank, world)
+    sampler = SamplerBackend()
+    sampling = None
+    if rank == 0:
+        sampling = time_sampling(lambda x: sampler.sample(x, top_k=50, top_p=0.9, temperature=0.7))
+    hidden, weight, ids = make_inputs(rows, hi - lo, seed=1234)
+    # every rank keeps only its rows of the batch; the kernel gathers the others over NVLink
+    hidden = hidden[rank * rows_local:(rank + 1) * rows_local].clone()
+    ids = ids[rank * rows_local:(rank + 1) * rows_local].clone()
+    group = None
+    extra = fused_logp.workspace_bytes(VOCAB)
+    kw = dict(vocab=VOCAB)
+    if world > 1:
+        from kernel_align_b200 import _native
+        from kernel_align_b200.parallel.peer import gather_arena_bytes, vocab_parallel_group
+
+        group = vocab_parallel_group(VOCAB)
+        kw.update(group=group, row_sharded=True)
+        extra += int(_native.cuda().ka_lmhead_logp_exchange_bytes(world, group.panel_rows))
+        extra += gather_arena_bytes(group, HIDDEN)
+    n_panels = -(-rows // fused_logp.DEFAULT_PANEL_ROWS)
+
+    ms, clock_info = time_device(lambda: sampler.fused_logp(hidden, weight, ids, **kw), args, world, local)
+    fused_logp.check_status(fused_logp.last_status(hidden.device, VOCAB))
+
+    # ---- end to end through the public API: pinned host inputs in, log-probs out, per step
+    h_host = hidden.cpu().pin_memory()
+    ids_host = ids.cpu().pin_memory()
+    out_host = torch.empty(rows_local, dtype=torch.float32).pin_memory()
+    e2e_ms = time_end_to_end(lambda h, i: sampler.fused_logp(h, weight, i, **kw), h_host, ids_host, out_host, args,
+                             world)
     fused_logp.check_status(fused_logp.last_status(hidden.device, VOCAB))
 
     value = rows / ms * 1e3
@@ -207,13 +269,16 @@ def run_own(args, rank, world, local):
         "scaling": "strong", "vs_baseline": (value / BASELINE_TOKENS_PER_S) if BASELINE_TOKENS_PER_S else None,
         "dtype": "bf16", "data": "synthetic",
         "config": {"model": "Llama-3-8B LM head (V=128256, d=4096)", "global_batch": args.g, "seq_len": args.seq_len,
-                   "parallelism": f"vp{world}" if world > 1 else "single",
-                   "l2": "inputs (1 GiB hidden + vocab shard) larger than the 126 MB L2",
-                   "extra_vram_bytes": fused_logp.workspace_bytes(VOCAB)},
+                   "parallelism": f"vp{world} (vocabulary sharded, rows sharded and gathered in-kernel)"
+                   if world > 1 else "single",
+                   "l2": "inputs (hidden rows + vocab shard) larger than the 126 MB L2",
+                   "extra_vram_bytes": extra},
         "clocks": clock_info,
         "e2e": {"value": rows / e2e_ms * 1e3, "unit": "tokens/s", "ms_per_step": e2e_ms,
-                "h2d_bytes_per_step": h_host.numel() * 2 + ids_host.numel() * 8,
-                "d2h_bytes_per_step": out_host.numel() * 4},
+                "h2d_bytes_per_step": (h_host.numel() * 2 + ids_host.numel() * 8) * world,
+                "d2h_bytes_per_step": out_host.numel() * 4 * world,
+                "staging": "double-buffered H2D on a copy stream, total bytes over all ranks"},
+        "sampling": sampling, "sampling_config": SAMPLING_CONFIG,
         "gpu_launches": args.steps * n_panels,
         "impl": "own",
     }
@@ -232,59 +297,46 @@ def run_reference(args, rank, world, local):
     rows = args.g * args.seq_len
     g_local = args.g // world
     rows_local = g_local * args.seq_len
-    hidden, weight, ids = make_inputs(rows, VOCAB, seed=1234)
-    hidden = hidden[rank * rows_local:(rank + 1) * rows_local]
-    ids = ids[rank * rows_local:(rank + 1) * rows_local].view(g_local, args.seq_len)
     sampler = RefSampler().to("cuda")
+    sampling = None
+    if rank == 0:
+        # the stock call as shipped (its fp32 copy and its second temperature division included);
+        # FlashInfer compiles its kernels during the warm-up calls, outside the timed ones
+        try:
+            sampling = time_sampling(lambda x: sampler.sample(x, top_k=50, top_p=0.9, temperature=0.7))
+        except Exception as e:  # noqa: BLE001
+            sampling = {"unavailable": f"{type(e).__name__}: {str(e)[:200]}"}
+    hidden, weight, ids = make_inputs(rows, VOCAB, seed=1234)
+    hidden = hidden[rank * rows_local:(rank + 1) * rows_local].clone()
+    ids = ids[rank * rows_local:(rank + 1) * rows_local].view(g_local, args.seq_len).clone()
 
     def step(h, i):
         logits = torch.matmul(h, weight.t()).view(g_local, args.seq_len, VOCAB)
         return sampler.compute_logp(logits, i)
 
-    for _ in range(args.warmup):
-        out = step(hidden, ids)
-    barrier_sync(world)
-    clocks = ClockSampler(local)
-    clocks.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier_sync(world)
-    e0.record()
-    for _ in range(args.steps):
-        out = step(hidden, ids)
-    e1.record()
-    barrier_sync(world)
-    ms = max_over_ranks(e0.elapsed_time(e1), world) / args.steps
-    clock_info = clocks.stop()
+    ms, clock_info = time_device(lambda: step(hidden, ids), args, world, local)
     peak = torch.cuda.max_memory_allocated()
 
     h_host = hidden.cpu().pin_memory()
     ids_host = ids.cpu().pin_memory()
-    out_host = torch.empty(g_local, args.seq_len, dtype=out.dtype).pin_memory()
-    barrier_sync(world)
-    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t0.record()
-    for _ in range(args.steps):
-        h_dev = h_host.to("cuda", non_blocking=True)
-        i_dev = ids_host.to("cuda", non_blocking=True)
-        out_host.copy_(step(h_dev, i_dev), non_blocking=True)
-    torch.cuda.synchronize()
-    t1.record()
-    barrier_sync(world)
-    e2e_ms = max_over_ranks(t0.elapsed_time(t1), world) / args.steps
+    out_host = torch.empty(g_local, args.seq_len, dtype=hidden.dtype).pin_memory()
+    e2e_ms = time_end_to_end(step, h_host, ids_host, out_host, args, world)
     value = rows / ms * 1e3
     return {
         "metric": "grpo_logp_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"model": "Llama-3-8B LM head (V=128256, d=4096)", "global_batch": args.g, "seq_len": args.seq_len,
-                   "parallelism": f"dp{world}" if world > 1 else "single",
+                   "parallelism": f"dp{world} (rows split, full vocabulary per rank)" if world > 1 else "single",
                    "l2": "inputs and logits larger than the 126 MB L2",
                    "path": "torch.matmul (cuBLAS) -> rl_engine SamplerBackend.compute_logp",
                    "peak_allocated_bytes": peak},
         "clocks": clock_info,
         "e2e": {"value": rows / e2e_ms * 1e3, "unit": "tokens/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": (h_host.numel() * 2 + ids_host.numel() * 8) * world,
-                "d2h_bytes_per_step": out_host.numel() * out_host.element_size() * world},
+                "d2h_bytes_per_step": out_host.numel() * out_host.element_size() * world,
+                "staging": "double-buffered H2D on a copy stream, total bytes over all ranks"},
+        "sampling": sampling, "sampling_config": SAMPLING_CONFIG,
         "gpu_launches": 0,
         "impl": "reference",
     }

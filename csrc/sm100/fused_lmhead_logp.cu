@@ -21,6 +21,14 @@
 // then releases a per-(source rank, block) flag; each rank finishes the blocks it pushed by
 // waiting (bounded) for the other ranks' flags and running the top of the tree.
 //
+// Row-sharded input (gather mode): a rank may hold only its 1/N of the rows. A seventh warp then
+// pushes the rank's rows of the panel (and their ids) into every peer's gather arena with bulk
+// copies staged through shared memory, 32 rows at a time, and raises a flag per (source rank,
+// 128-row block) when a block is complete; the TMA producer waits (bounded) for the flag of a
+// remote block and loads it from this GPU's own arena. Every rank walks its own rows first, so
+// the transfer hides behind the first 1/N of the panel's tensor work. The arithmetic per row
+// is the one above: the results equal the single-GPU ones bit for bit.
+//
 // Replaces the reference's `torch.matmul` + `SamplerBackend.compute_logp`
 // (rl_engine/kernels/sampling.py:91-112), which materialises [G, L, V] logits twice.
 
@@ -30,6 +38,7 @@
 #include <cstdlib>
 #include <cuda_bf16.h>
 #include <math_constants.h>
+#include <mutex>
 
 #include "common/bounded_wait.cuh"
 #include "common/ptx.cuh"
@@ -45,7 +54,9 @@ constexpr int kBK = 64;          // bf16 elements per 128-byte swizzled row
 constexpr int kUmmaK = 16;       // K per tcgen05.mma of kind::f16
 constexpr int kSubCols = 1792;   // columns per canonical sub-slice (7 tiles)
 constexpr int kSlices = 8;       // canonical slices of the global vocabulary
-constexpr int kThreads = 192;    // warps 0-3 epilogue, 4 TMA producer, 5 MMA issuer
+constexpr int kThreads = 224;    // warps 0-3 epilogue, 4 TMA producer, 5 MMA issuer, 6 row pusher
+constexpr int kPushChunk = 8192; // bytes per staged bulk copy of the row pusher (two buffers)
+constexpr int kPushRows = 32;    // rows per push unit
 constexpr int kMaxDeferred = 512;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
@@ -60,6 +71,7 @@ struct Cfg {
   static constexpr int kTxBytes = kStageBytes * G;       // bytes counted on the leader's barrier
   static constexpr int kTileBytes = kStages * kStageBytes;
   static constexpr int kSmemBytes = kTileBytes + 1024 /*alignment*/ + 2048 /*control*/;
+  static constexpr int kSmemBytesGather = kSmemBytes + 2 * kPushChunk;  // + the pusher's staging
 };
 
 struct Control {
@@ -67,6 +79,7 @@ struct Control {
   uint64_t empty[8];
   uint64_t tfull[2];
   uint64_t tempty[2];
+  uint64_t pbar[2];
   uint32_t tmem_base;
   int abort_flag;
   int is_last;
@@ -80,7 +93,9 @@ enum Where : int {
   kWhereMmaFull = 2,
   kWhereMmaTmemEmpty = 3,
   kWhereEpiTmemFull = 4,
-  kWherePeerFlag = 5
+  kWherePeerFlag = 5,
+  kWhereGatherFlag = 6,
+  kWherePushLoad = 7
 };
 
 struct Item {
@@ -101,7 +116,8 @@ __device__ __forceinline__ void decode_item(const LogpParams& p, int i, Item& it
   const int r2 = r - h * mg_sz * p.cg;
   const int m_local = r2 / cg_sz;
   const int c_local = r2 - m_local * cg_sz;
-  it.m_tile = g * p.mg + m_local;
+  it.m_tile = g * p.mg + m_local + p.mt_rot;
+  if (it.m_tile >= p.n_mtiles) it.m_tile -= p.n_mtiles;
   // Schedule position -> (slice, sub-slice): sub-slice major, so that the sub-slices that run
   // side by side have the same position inside their slices and therefore the same number of
   // tiles; CTAs that share W tiles through L2 then stay in step. The partials are stored
@@ -232,7 +248,7 @@ __device__ __forceinline__ void merge_local(const LogpParams& p, int rp, float s
   l_out = ll[0];
 }
 
-__device__ __forceinline__ void write_result(const LogpParams& p, int row, float m, float l, float t,
+__device__ __forceinline__ void write_result(const LogpParams& p, long long row, float m, float l, float t,
                                              bool has_t, bool id_ok) {
   // lse = scale*m + ln(l); logp = scale*t - lse
   const float lse = __fmaf_rn(lg2_approx(l), kLn2, __fmul_rn(m, p.scale));
@@ -240,10 +256,114 @@ __device__ __forceinline__ void write_result(const LogpParams& p, int row, float
   p.logp[row] = (id_ok && has_t) ? __fsub_rn(__fmul_rn(t, p.scale), lse) : 0.f;
 }
 
+// Where the rows of a 128-row block of the panel come from and go to.
+struct RowRef {
+  int src;            // rank that holds the row
+  int j;              // row inside the source's part of the panel (gather) or inside the panel
+  bool ok;            // a real row
+  long long out_row;  // index into logp / lse, or -1 if this rank does not write the row
+};
+
+__device__ __forceinline__ RowRef row_ref(const LogpParams& p, int blk, int tid) {
+  RowRef r;
+  if (p.gather) {
+    r.src = blk / p.bps;
+    r.j = (blk - r.src * p.bps) * kBM + tid;
+    r.ok = r.j < p.rows_local;
+    const long long lr = static_cast<long long>(p.local_row_begin) + r.j;
+    r.out_row = p.out_all ? static_cast<long long>(r.src) * p.m_local + lr : (r.src == p.rank ? lr : -1);
+  } else {
+    r.src = p.rank;
+    r.j = blk * kBM + tid;
+    r.ok = r.j < p.rows;
+    r.out_row = static_cast<long long>(p.row_begin) + r.j;
+  }
+  return r;
+}
+
+// Token id of a row. A remote row's id sits in this rank's gather arena and may only be read
+// once the block's flag has been seen (by this thread or by one it synchronised with).
+__device__ __forceinline__ long long load_id(const LogpParams& p, const RowRef& r) {
+  if (!r.ok) return -1;
+  if (!p.gather) return p.ids[static_cast<long long>(p.row_begin) + r.j];
+  if (r.src == p.rank) return p.ids[static_cast<long long>(p.local_row_begin) + r.j];
+  return ld_relaxed_sys_s64(p.gids[p.rank] +
+                            (static_cast<size_t>(p.epoch & 1u) * p.world + r.src) * p.pl + r.j);
+}
+
+// Row pusher (one warp, gather mode): copies this rank's rows of the panel, 32 rows per unit,
+// into every peer's gather arena. Lane 0 stages 8 KiB pieces through shared memory with bulk
+// copies (global -> shared -> peer global); all lanes forward the ids. The warp that completes
+// the last piece of a 128-row block raises the block's flag on every peer.
+__device__ __forceinline__ void push_rows(const LogpParams& p, Control* ctl, uint32_t stage_addr,
+                                          const WaitCtx& wctx, int lane) {
+  const int n_units = (p.rows_local + kPushRows - 1) / kPushRows;
+  const size_t row_bytes = static_cast<size_t>(p.k) * 2;
+  const size_t gen_src = static_cast<size_t>(p.epoch & 1u) * p.world + p.rank;
+  const int blocks_pl = p.pl / kBM;
+  uint32_t phases = 0;  // bit b: parity to wait for on pbar[b]
+  uint32_t n_chunks = 0;
+  bool ok = true;
+  for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+    const int j0 = u * kPushRows;
+    const int nrows = min(kPushRows, p.rows_local - j0);
+    if (lane == 0) {
+      const size_t bytes = static_cast<size_t>(nrows) * row_bytes;
+      const uint8_t* src = static_cast<const uint8_t*>(p.h_local) +
+                           (static_cast<size_t>(p.local_row_begin) + j0) * row_bytes;
+      const size_t dst_off = (gen_src * p.pl + j0) * row_bytes;
+      for (size_t off = 0; off < bytes; off += kPushChunk) {
+        const uint32_t n = static_cast<uint32_t>(min(static_cast<size_t>(kPushChunk), bytes - off));
+        const uint32_t b = n_chunks & 1u;
+        bulk_wait_group_read<1>();  // the stores that last read this buffer are done with it
+        const uint32_t bar = smem_u32(&ctl->pbar[b]);
+        const uint32_t buf = stage_addr + b * kPushChunk;
+        mbar_arrive_expect_tx(bar, n);
+        bulk_load(buf, src + off, n, bar);
+        ok = mbar_wait_bounded(bar, (phases >> b) & 1u, wctx, kWherePushLoad, static_cast<int>(b));
+        if (!ok) break;
+        phases ^= 1u << b;
+        for (int d = 1; d < p.world; ++d) {
+          const int dst = (p.rank - d + p.world) % p.world;  // the rank that needs these rows soonest first
+          bulk_store(p.gbuf[dst] + dst_off + off, buf, n);
+        }
+        bulk_commit_group();
+        ++n_chunks;
+      }
+      bulk_wait_group<0>();  // every piece of the unit has been written
+    }
+    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+    if (!ok) break;
+    if (lane < nrows) {
+      const long long id = p.ids[static_cast<long long>(p.local_row_begin) + j0 + lane];
+      for (int d = 1; d < p.world; ++d) {
+        const int dst = (p.rank - d + p.world) % p.world;
+        st_relaxed_sys_s64(p.gids[dst] + gen_src * p.pl + j0 + lane, id);
+      }
+    }
+    __threadfence_system();
+    __syncwarp();
+    if (lane == 0) {
+      const int blk = j0 / kBM;
+      const int units_in_blk = (min(kBM, p.rows_local - blk * kBM) + kPushRows - 1) / kPushRows;
+      const unsigned prev = atomicAdd(&p.pcount[blk], 1u);
+      if (prev + 1u == static_cast<unsigned>(units_in_blk)) {
+        p.pcount[blk] = 0u;  // self-cleaning for the next launch
+        __threadfence_system();
+        for (int d = 1; d < p.world; ++d) {
+          const int dst = (p.rank - d + p.world) % p.world;
+          st_release_sys_u32(p.gflag[dst] + static_cast<size_t>(p.rank) * blocks_pl + blk, p.epoch);
+        }
+      }
+    }
+  }
+}
+
 template <int G>
 __global__ void __launch_bounds__(kThreads, 1)
 fused_lmhead_logp_kernel(const __grid_constant__ CUtensorMap tm_h,
                          const __grid_constant__ CUtensorMap tm_w,
+                         const __grid_constant__ CUtensorMap tm_g,
                          const __grid_constant__ LogpParams p) {
   using C = Cfg<G>;
   extern __shared__ uint8_t smem_raw[];
@@ -272,6 +392,7 @@ fused_lmhead_logp_kernel(const __grid_constant__ CUtensorMap tm_h,
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&ctl->tfull[b]), 1);
       mbar_init(smem_u32(&ctl->tempty[b]), 4 * G);
+      mbar_init(smem_u32(&ctl->pbar[b]), 1);
     }
     ctl->abort_flag = 0;
     ctl->is_last = 0;
@@ -285,6 +406,7 @@ fused_lmhead_logp_kernel(const __grid_constant__ CUtensorMap tm_h,
   if (warp == 4 && lane == 0) {
     tma_prefetch_desc(&tm_h);
     tma_prefetch_desc(&tm_w);
+    if (p.gather) tma_prefetch_desc(&tm_g);
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -304,7 +426,26 @@ fused_lmhead_logp_kernel(const __grid_constant__ CUtensorMap tm_h,
       for (int i = pair_id; i < n_items && ok; i += n_pairs) {
         Item it;
         decode_item(p, i, it);
-        const int row0 = p.row_begin + it.m_tile * (kBM * G) + static_cast<int>(cta_rank) * kBM;
+        int row0 = p.row_begin + it.m_tile * (kBM * G) + static_cast<int>(cta_rank) * kBM;
+        const CUtensorMap* tm_a = &tm_h;
+        if (p.gather) {
+          const int blk = it.m_tile * G + static_cast<int>(cta_rank);
+          const int src = blk / p.bps;
+          const int j0 = (blk - src * p.bps) * kBM;
+          if (src == p.rank) {
+            row0 = p.local_row_begin + j0;  // own rows: straight from the caller's tensor
+          } else {
+            // another rank's rows: from this GPU's arena, once that rank has flagged the block
+            row0 = (static_cast<int>(p.epoch & 1u) * p.world + src) * p.pl + j0;
+            tm_a = &tm_g;
+            if (j0 < p.rows_local && it.n_tiles > 0) {
+              ok = flag_wait_bounded(p.gflag[p.rank] + static_cast<size_t>(src) * (p.pl / kBM) + j0 / kBM,
+                                     p.epoch, wctx, kWhereGatherFlag, blk);
+              if (!ok) break;
+              fence_proxy_async_global();
+            }
+          }
+        }
         for (int nt = 0; nt < it.n_tiles && ok; ++nt) {
           const int n0 = it.col_begin + nt * kBN;
           for (int kb = 0; kb < num_kb; ++kb) {
@@ -316,13 +457,13 @@ fused_lmhead_logp_kernel(const __grid_constant__ CUtensorMap tm_h,
             const uint32_t full = smem_u32(&ctl->full[stage]);
             if constexpr (G == 1) {
               mbar_arrive_expect_tx(full, C::kTxBytes);
-              tma_load_2d(a_dst, &tm_h, kb * kBK, row0, full);
+              tma_load_2d(a_dst, tm_a, kb * kBK, row0, full);
               tma_load_2d(b_dst, &tm_w, kb * kBK, n0, full);
               tma_load_2d(b_dst + 128 * kBK * 2, &tm_w, kb * kBK, n0 + 128, full);
             } else {
               if (leader) mbar_arrive_expect_tx(full, C::kTxBytes);
               const uint32_t full_leader = mapa_u32(full, 0);
-              tma_load_2d_pair(a_dst, &tm_h, kb * kBK, row0, full_leader);
+              tma_load_2d_pair(a_dst, tm_a, kb * kBK, row0, full_leader);
               tma_load_2d_pair(b_dst, &tm_w, kb * kBK, n0 + static_cast<int>(cta_rank) * C::kBRows,
                                full_leader);
             }
@@ -378,6 +519,9 @@ fused_lmhead_logp_kernel(const __grid_constant__ CUtensorMap tm_h,
         }
       }
     }
+  } else if (warp == 6) {
+    // ------------------------------------------------------------------ row pusher
+    if (p.gather && p.world > 1) push_rows(p, ctl, tiles_addr + C::kTileBytes + 2048, wctx, lane);
   } else {
     // ------------------------------------------------------------------ epilogue (warps 0-3)
     // Control flow rule: every named-barrier call below is reached by all 128 threads; a
@@ -394,14 +538,16 @@ fused_lmhead_logp_kernel(const __grid_constant__ CUtensorMap tm_h,
       decode_item(p, i, it);
       const int blk = it.m_tile * G + static_cast<int>(cta_rank);  // 128-row block in the panel
       const int rp = blk * kBM + tid;                              // row inside the panel
-      const int row = p.row_begin + rp;                            // global row
-      const bool row_ok = rp < p.rows;
-      long long id = -1;
-      if (row_ok) id = p.ids[row];
-      const bool id_ok = id >= 0 && id < static_cast<long long>(p.v_global);
-      const long long lid = id - p.vocab_offset;  // column inside this rank's shard
-      const bool t_here = id_ok && lid >= it.col_begin && lid < it.col_end;
-      const int tcol_item = t_here ? static_cast<int>(lid) - it.col_begin : -(1 << 30);
+      const RowRef rr = row_ref(p, blk, tid);
+      const bool row_ok = rr.ok;
+      // A remote row's id arrives with the row: it is read after the first accumulator of the
+      // item is full, which the producer's wait for the block's flag precedes.
+      bool have_id = !p.gather || rr.src == p.rank;
+      long long id = have_id ? load_id(p, rr) : -1;
+      bool id_ok = id >= 0 && id < static_cast<long long>(p.v_global);
+      long long lid = id - p.vocab_offset;  // column inside this rank's shard
+      bool t_here = id_ok && lid >= it.col_begin && lid < it.col_end;
+      int tcol_item = t_here ? static_cast<int>(lid) - it.col_begin : -(1 << 30);
 
       float m = -CUDART_INF_F, l = 0.f, t = 0.f;
       for (int nt = 0; nt < it.n_tiles; ++nt) {
@@ -410,6 +556,14 @@ fused_lmhead_logp_kernel(const __grid_constant__ CUtensorMap tm_h,
         ok = __all_sync(0xffffffffu, mine) != 0;  // warp-uniform: tcgen05.ld needs convergence
         if (!ok) break;
         tc_fence_after_sync();
+        if (!have_id) {
+          have_id = true;
+          id = load_id(p, rr);
+          id_ok = id >= 0 && id < static_cast<long long>(p.v_global);
+          lid = id - p.vocab_offset;
+          t_here = id_ok && lid >= it.col_begin && lid < it.col_end;
+          tcol_item = t_here ? static_cast<int>(lid) - it.col_begin : -(1 << 30);
+        }
         const int valid = min(kBN, it.col_end - (it.col_begin + nt * kBN));
         const int tcol = tcol_item - nt * kBN;
         const uint32_t trow = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) +
@@ -463,6 +617,14 @@ fused_lmhead_logp_kernel(const __grid_constant__ CUtensorMap tm_h,
       const bool is_last = ctl->is_last != 0;
       if (is_last) {
         __threadfence();
+        if (!have_id) {
+          // This item had no tiles. If another sub-slice of the block had some, its producer saw
+          // the block's flag and the arrival counter orders this read after it; if none had,
+          // the shard is empty and has_t is false whatever is read here.
+          id = load_id(p, rr);
+          id_ok = id >= 0 && id < static_cast<long long>(p.v_global);
+          lid = id - p.vocab_offset;
+        }
         const bool has_t = id_ok && lid >= 0 && lid < static_cast<long long>(p.v_local);
         float mm = -CUDART_INF_F, ml = 0.f, mt = 0.f;
         if (row_ok) {
@@ -470,20 +632,27 @@ fused_lmhead_logp_kernel(const __grid_constant__ CUtensorMap tm_h,
           if (has_t) mt = __ldcg(p.tgt + rp);
         }
         if (p.world == 1) {
-          if (row_ok) write_result(p, row, mm, ml, mt, has_t, id_ok);
+          if (row_ok) write_result(p, rr.out_row, mm, ml, mt, has_t, id_ok);
         } else {
+          // Every rank that writes the block's rows gets the triple: all ranks, or only the
+          // rank that holds the rows when each rank keeps its own results.
+          const bool to_all = !p.gather || p.out_all;
           const size_t slot = (static_cast<size_t>(p.epoch & 1u) * p.world + p.rank) * p.ldp + rp;
           const float4 v = make_float4(mm, ml, mt, has_t ? 1.f : 0.f);
           if (row_ok) {
-            for (int d = 0; d < p.world; ++d) st_relaxed_sys_f4(p.xbuf[d] + slot, v);
+            if (to_all) {
+              for (int d = 0; d < p.world; ++d) st_relaxed_sys_f4(p.xbuf[d] + slot, v);
+            } else {
+              st_relaxed_sys_f4(p.xbuf[rr.src] + slot, v);
+            }
           }
           __threadfence_system();
           epi_bar();
-          if (tid < p.world) {
-            st_release_sys_u32(p.xflag[tid] + static_cast<size_t>(p.rank) * p.n_blocks_max + blk,
-                               p.epoch);
+          if (to_all ? (tid < p.world) : (tid == 0)) {
+            const int d = to_all ? tid : rr.src;
+            st_release_sys_u32(p.xflag[d] + static_cast<size_t>(p.rank) * p.n_blocks_max + blk, p.epoch);
           }
-          if (tid == 0) {
+          if (tid == 0 && (to_all || rr.src == p.rank)) {
             const int n = ctl->n_deferred;
             if (n < kMaxDeferred) {
               ctl->deferred[n] = static_cast<uint16_t>(blk);
@@ -502,15 +671,20 @@ fused_lmhead_logp_kernel(const __grid_constant__ CUtensorMap tm_h,
       const int n_def = ctl->n_deferred;
       for (int d = 0; d < n_def; ++d) {
         const int blk = ctl->deferred[d];
+        const RowRef rr = row_ref(p, blk, tid);
         if (tid < p.world) {
           flag_wait_bounded(p.xflag[p.rank] + static_cast<size_t>(tid) * p.n_blocks_max + blk, p.epoch,
                             wctx, kWherePeerFlag, blk);
+        } else if (tid == 32 && p.gather && rr.src != p.rank && (blk - rr.src * p.bps) * kBM < p.rows_local) {
+          // the ids of another rank's rows are read below: make sure its push has landed even if
+          // this rank never loaded the block (an empty vocabulary shard)
+          flag_wait_bounded(p.gflag[p.rank] + static_cast<size_t>(rr.src) * (p.pl / kBM) + (blk - rr.src * p.bps),
+                            p.epoch, wctx, kWhereGatherFlag, blk);
         }
         epi_bar();
         if (ctl->abort_flag) break;  // uniform, as above
         const int rp = blk * kBM + tid;
-        const int row = p.row_begin + rp;
-        if (rp < p.rows) {
+        if (rr.ok) {
           float lm[kSlices], ll[kSlices];
           float t = 0.f;
           bool has_t = false;
@@ -541,9 +715,9 @@ fused_lmhead_logp_kernel(const __grid_constant__ CUtensorMap tm_h,
               }
             }
           }
-          const long long id = p.ids[row];
+          const long long id = load_id(p, rr);
           const bool id_ok = id >= 0 && id < static_cast<long long>(p.v_global);
-          write_result(p, row, lm[0], ll[0], t, has_t, id_ok);
+          write_result(p, rr.out_row, lm[0], ll[0], t, has_t, id_ok);
         }
       }
     }
@@ -570,13 +744,21 @@ fused_lmhead_logp_kernel(const __grid_constant__ CUtensorMap tm_h,
   }
 }
 
+constexpr int kMaxDevices = 64;
+
+// Resident CTAs of the kernel on the current device. The shared-memory opt-in is a per-device
+// attribute, so both it and the occupancy answer are set up and cached per device.
 template <int G>
 int max_ctas(int num_sms) {
-  static int cached[2] = {0, 0};
-  if (cached[G - 1] > 0) return cached[G - 1];
+  static std::mutex mu;
+  static int cached[kMaxDevices] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -1;
+  std::lock_guard<std::mutex> lock(mu);
+  if (cached[dev] > 0) return cached[dev];
   using C = Cfg<G>;
   auto* kern = fused_lmhead_logp_kernel<G>;
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) !=
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytesGather) !=
       cudaSuccess)
     return -1;
   int n = num_sms;
@@ -584,7 +766,7 @@ int max_ctas(int num_sms) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(num_sms / 2 * 2));
     cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = C::kSmemBytes;
+    cfg.dynamicSmemBytes = C::kSmemBytesGather;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
@@ -600,22 +782,23 @@ int max_ctas(int num_sms) {
     n = clusters * 2;
     if (n > num_sms / 2 * 2) n = num_sms / 2 * 2;
   }
-  cached[G - 1] = n;
+  cached[dev] = n;
   return n;
 }
 
 template <int G>
-int launch_panel(const CUtensorMap& tm_h, const CUtensorMap& tm_w, const LogpParams& p, int num_sms,
-                 cudaStream_t stream) {
+int launch_panel(const CUtensorMap& tm_h, const CUtensorMap& tm_w, const CUtensorMap& tm_g, const LogpParams& p,
+                 int num_sms, cudaStream_t stream) {
   using C = Cfg<G>;
   int ctas = max_ctas<G>(num_sms);
   if (ctas <= 0) return -10;
   const int n_items = p.n_mtiles * p.n_chunks;
-  if (n_items * G < ctas) ctas = n_items * G;
+  // with sharded rows every CTA also carries a pusher, so the grid is not shrunk to the items
+  if (!p.gather && n_items * G < ctas) ctas = n_items * G;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(ctas));
   cfg.blockDim = dim3(kThreads);
-  cfg.dynamicSmemBytes = C::kSmemBytes;
+  cfg.dynamicSmemBytes = p.gather ? C::kSmemBytesGather : C::kSmemBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -624,10 +807,200 @@ int launch_panel(const CUtensorMap& tm_h, const CUtensorMap& tm_w, const LogpPar
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, fused_lmhead_logp_kernel<G>, tm_h, tm_w, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, fused_lmhead_logp_kernel<G>, tm_h, tm_w, tm_g, p);
   if (e != cudaSuccess) {
     fprintf(stderr, "[kernel_align_b200] fused_lmhead_logp launch failed: %s\n", cudaGetErrorString(e));
     return -11;
+  }
+  return 0;
+}
+
+size_t ws_status_offset(int v_global, int panel_rows) {
+  const int vs = (v_global + kSlices - 1) / kSlices;
+  const int sub = (vs + kSubCols - 1) / kSubCols;
+  const size_t ldp = static_cast<size_t>(panel_rows);
+  const size_t n_chunks = static_cast<size_t>(kSlices) * sub;  // upper bound (world == 1)
+  const size_t n_blocks = ldp / kBM;
+  size_t bytes = 2 * n_chunks * ldp * sizeof(float);  // part_m, part_l
+  bytes += ldp * sizeof(float);                       // tgt
+  bytes += n_blocks * sizeof(unsigned);               // counters
+  return (bytes + 255) / 256 * 256;
+}
+
+// Layout of the gather arena (see ka_lmhead_logp_gather_bytes).
+struct GatherLayout {
+  size_t ids_off, flag_off, pcount_off, total;
+};
+GatherLayout gather_layout(int world, int panel_rows, int k) {
+  GatherLayout g;
+  const size_t rows2 = 2 * static_cast<size_t>(panel_rows);
+  const size_t blocks_pl = static_cast<size_t>(panel_rows / world) / kBM;
+  g.ids_off = rows2 * static_cast<size_t>(k) * 2;
+  g.flag_off = g.ids_off + rows2 * sizeof(long long);
+  g.pcount_off = g.flag_off + (static_cast<size_t>(world) * blocks_pl * sizeof(unsigned) + 255) / 256 * 256;
+  g.total = g.pcount_off + (blocks_pl * sizeof(unsigned) + 255) / 256 * 256;
+  return g;
+}
+
+struct FwdArgs {
+  const void* hidden;  // all rows, or this rank's rows when `sharded`
+  const void* weight;
+  const long long* ids;
+  float* logp;
+  float* lse;
+  void* workspace;
+  size_t workspace_bytes;
+  void* const* peer_exchange;
+  void* const* peer_gather;
+  int m;  // rows of `hidden`
+  int k, v_global, v_local, vocab_offset, world, rank;
+  unsigned epoch_base;
+  float scale;
+  int panel_rows, sharded, out_all, cta_group, num_sms;
+  unsigned long long timeout_ns;
+  cudaStream_t stream;
+};
+
+int forward_impl(const FwdArgs& a) {
+  if (a.m <= 0) return 0;
+  if (a.k % 8 != 0 || a.k <= 0) return -1;
+  if (!(a.world == 1 || a.world == 2 || a.world == 4 || a.world == 8) || a.rank < 0 || a.rank >= a.world) return -2;
+  if (!(a.scale > 0.f)) return -3;
+  if (a.cta_group != 1 && a.cta_group != 2) return -4;
+  if (a.panel_rows <= 0 || a.panel_rows % 256 != 0) return -5;
+  if (a.workspace_bytes < ka_lmhead_logp_workspace_bytes(a.v_global, a.panel_rows)) return -6;
+  if (a.world > 1 && a.peer_exchange == nullptr) return -7;
+  const bool gather = a.sharded && a.world > 1;
+  if (gather) {
+    if (a.peer_gather == nullptr) return -13;
+    if (a.panel_rows % (256 * a.world) != 0) return -14;
+    if ((reinterpret_cast<uintptr_t>(a.hidden) & 15u) != 0) return -15;
+  }
+
+  const int vs = (a.v_global + kSlices - 1) / kSlices;
+  const int sub = (vs + kSubCols - 1) / kSubCols;
+  const int n_slices_local = kSlices / a.world;
+  if (a.vocab_offset != a.rank * n_slices_local * vs) return -8;
+  {
+    const long long hi = static_cast<long long>(a.rank + 1) * n_slices_local * vs;
+    const long long end = hi < a.v_global ? hi : a.v_global;
+    const long long expect = end - a.vocab_offset > 0 ? end - a.vocab_offset : 0;
+    if (a.v_local != expect) return -9;
+  }
+  const size_t ldp = static_cast<size_t>(a.panel_rows);
+  const size_t n_blocks_max = ldp / kBM;
+  if (n_blocks_max > 65535) return -12;
+
+  LogpParams p = {};
+  uint8_t* ws = static_cast<uint8_t*>(a.workspace);
+  const size_t n_chunks_max = static_cast<size_t>(kSlices) * sub;
+  p.part_m = reinterpret_cast<float*>(ws);
+  p.part_l = p.part_m + n_chunks_max * ldp;
+  p.tgt = p.part_l + n_chunks_max * ldp;
+  p.counters = reinterpret_cast<unsigned*>(p.tgt + ldp);
+  p.status = reinterpret_cast<int*>(ws + ws_status_offset(a.v_global, a.panel_rows));
+  if (a.world > 1) {
+    const size_t xbuf_bytes = 2 * static_cast<size_t>(a.world) * ldp * sizeof(float4);
+    for (int d = 0; d < a.world; ++d) {
+      uint8_t* base = static_cast<uint8_t*>(a.peer_exchange[d]);
+      if (!base) return -7;
+      p.xbuf[d] = reinterpret_cast<float4*>(base);
+      p.xflag[d] = reinterpret_cast<unsigned*>(base + xbuf_bytes);
+    }
+  }
+  p.ids = a.ids;
+  p.logp = a.logp;
+  p.lse = a.lse;
+  p.m = a.m;
+  p.k = a.k;
+  p.v_global = a.v_global;
+  p.v_local = a.v_local;
+  p.vocab_offset = a.vocab_offset;
+  p.vs = vs;
+  p.sub = sub;
+  p.n_slices_local = n_slices_local;
+  p.n_chunks = n_slices_local * sub;
+  p.ldp = static_cast<int>(ldp);
+  p.n_blocks_max = static_cast<int>(n_blocks_max);
+  p.world = a.world;
+  p.rank = a.rank;
+  p.scale = a.scale;
+  p.timeout_ns = a.timeout_ns;
+  // Sub-slices that run side by side (cg) x row tiles that run side by side (mg) ~ CTA pairs.
+  // KA_LOGP_CG overrides the default split for tuning.
+  int cg_pref = 8;
+  if (const char* e = getenv("KA_LOGP_CG")) {
+    const int v = atoi(e);
+    if (v >= 1 && v <= 64) cg_pref = v;
+  }
+  p.cg = p.n_chunks < cg_pref ? p.n_chunks : cg_pref;
+  {
+    const int pairs = a.num_sms / a.cta_group;
+    int mg = pairs / p.cg;
+    if (mg < 1) mg = 1;
+    p.mg = mg;
+  }
+
+  CUtensorMap tm_h, tm_w, tm_g;
+  int rc = make_tmap_2d_16bit_sw128(&tm_h, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, a.hidden, static_cast<uint64_t>(a.m),
+                                    static_cast<uint64_t>(a.k), static_cast<uint64_t>(a.k), kBM, kBK);
+  if (rc != 0) return -20 + rc;
+  rc = make_tmap_2d_16bit_sw128(&tm_w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, a.weight,
+                                static_cast<uint64_t>(a.v_local > 0 ? a.v_local : 1), static_cast<uint64_t>(a.k),
+                                static_cast<uint64_t>(a.k), 128, kBK);
+  if (rc != 0) return -40 + rc;
+  tm_g = tm_h;
+  const int rows_per_mtile = kBM * a.cta_group;
+  unsigned epoch = a.epoch_base;
+
+  if (!gather) {
+    for (int row_begin = 0; row_begin < a.m; row_begin += a.panel_rows) {
+      const int rows = (a.m - row_begin) < a.panel_rows ? (a.m - row_begin) : a.panel_rows;
+      p.row_begin = row_begin;
+      p.rows = rows;
+      p.n_mtiles = (rows + rows_per_mtile - 1) / rows_per_mtile;
+      p.epoch = epoch++;
+      rc = (a.cta_group == 1) ? launch_panel<1>(tm_h, tm_w, tm_g, p, a.num_sms, a.stream)
+                              : launch_panel<2>(tm_h, tm_w, tm_g, p, a.num_sms, a.stream);
+      if (rc != 0) return rc;
+    }
+    return 0;
+  }
+
+  // ---- rows sharded over the ranks
+  const GatherLayout gl = gather_layout(a.world, a.panel_rows, a.k);
+  for (int d = 0; d < a.world; ++d) {
+    uint8_t* base = static_cast<uint8_t*>(a.peer_gather[d]);
+    if (!base) return -13;
+    p.gbuf[d] = base;
+    p.gids[d] = reinterpret_cast<long long*>(base + gl.ids_off);
+    p.gflag[d] = reinterpret_cast<unsigned*>(base + gl.flag_off);
+  }
+  p.pcount = reinterpret_cast<unsigned*>(static_cast<uint8_t*>(a.peer_gather[a.rank]) + gl.pcount_off);
+  p.gather = 1;
+  p.out_all = a.out_all ? 1 : 0;
+  p.m_local = a.m;
+  p.pl = a.panel_rows / a.world;
+  p.h_local = a.hidden;
+  rc = make_tmap_2d_16bit_sw128(&tm_g, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, a.peer_gather[a.rank],
+                                2ull * static_cast<uint64_t>(a.panel_rows), static_cast<uint64_t>(a.k),
+                                static_cast<uint64_t>(a.k), kBM, kBK);
+  if (rc != 0) return -60 + rc;
+  for (int lrb = 0; lrb < a.m; lrb += p.pl) {
+    const int rows_local = (a.m - lrb) < p.pl ? (a.m - lrb) : p.pl;
+    int bps = (rows_local + kBM - 1) / kBM;
+    bps += bps & 1;
+    p.local_row_begin = lrb;
+    p.rows_local = rows_local;
+    p.bps = bps;
+    p.row_begin = 0;
+    p.rows = a.world * bps * kBM;
+    p.n_mtiles = a.world * bps / a.cta_group;
+    p.mt_rot = a.rank * bps / a.cta_group;
+    p.epoch = epoch++;
+    rc = (a.cta_group == 1) ? launch_panel<1>(tm_h, tm_w, tm_g, p, a.num_sms, a.stream)
+                            : launch_panel<2>(tm_h, tm_w, tm_g, p, a.num_sms, a.stream);
+    if (rc != 0) return rc;
   }
   return 0;
 }
@@ -637,21 +1010,8 @@ int launch_panel(const CUtensorMap& tm_h, const CUtensorMap& tm_w, const LogpPar
 
 extern "C" {
 
-// See fused_lmhead_logp.h for the contract.
-static size_t ka_ws_status_offset(int v_global, int panel_rows) {
-  const int vs = (v_global + ka::kSlices - 1) / ka::kSlices;
-  const int sub = (vs + ka::kSubCols - 1) / ka::kSubCols;
-  const size_t ldp = static_cast<size_t>(panel_rows);
-  const size_t n_chunks = static_cast<size_t>(ka::kSlices) * sub;  // upper bound (world == 1)
-  const size_t n_blocks = ldp / ka::kBM;
-  size_t bytes = 2 * n_chunks * ldp * sizeof(float);  // part_m, part_l
-  bytes += ldp * sizeof(float);                       // tgt
-  bytes += n_blocks * sizeof(unsigned);               // counters
-  return (bytes + 255) / 256 * 256;
-}
-
 size_t ka_lmhead_logp_workspace_bytes(int v_global, int panel_rows) {
-  return ka_ws_status_offset(v_global, panel_rows) + 256;
+  return ka::ws_status_offset(v_global, panel_rows) + 256;
 }
 
 size_t ka_lmhead_logp_exchange_bytes(int world, int panel_rows) {
@@ -662,116 +1022,37 @@ size_t ka_lmhead_logp_exchange_bytes(int world, int panel_rows) {
   return xbuf + (xflag + 255) / 256 * 256;
 }
 
-int ka_lmhead_logp_status_offset(int v_global, int panel_rows) {
-  return static_cast<int>(ka_ws_status_offset(v_global, panel_rows));
+size_t ka_lmhead_logp_gather_bytes(int world, int panel_rows, int k) {
+  if (world < 1 || panel_rows <= 0 || panel_rows % (256 * world) != 0 || k <= 0) return 0;
+  return ka::gather_layout(world, panel_rows, k).total;
 }
 
+int ka_lmhead_logp_status_offset(int v_global, int panel_rows) {
+  return static_cast<int>(ka::ws_status_offset(v_global, panel_rows));
+}
+
+// See fused_lmhead_logp.h for the contracts.
 int ka_lmhead_logp_forward(const void* hidden, const void* weight, const long long* ids, float* logp,
                            float* lse, void* workspace, size_t workspace_bytes, void* const* peer_exchange,
                            int m, int k, int v_global, int v_local, int vocab_offset, int world, int rank,
                            unsigned epoch_base, float scale, int panel_rows, int cta_group, int num_sms,
                            unsigned long long timeout_ns, void* stream_ptr) {
-  using namespace ka;
-  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
-  if (m <= 0) return 0;
-  if (k % 8 != 0 || k <= 0) return -1;
-  if (!(world == 1 || world == 2 || world == 4 || world == 8) || rank < 0 || rank >= world) return -2;
-  if (!(scale > 0.f)) return -3;
-  if (cta_group != 1 && cta_group != 2) return -4;
-  if (panel_rows <= 0 || panel_rows % 256 != 0) return -5;
-  if (workspace_bytes < ka_lmhead_logp_workspace_bytes(v_global, panel_rows)) return -6;
-  if (world > 1 && peer_exchange == nullptr) return -7;
+  ka::FwdArgs a = {hidden, weight, ids, logp, lse, workspace, workspace_bytes, peer_exchange, nullptr,
+                   m, k, v_global, v_local, vocab_offset, world, rank, epoch_base, scale, panel_rows,
+                   0, 1, cta_group, num_sms, timeout_ns, static_cast<cudaStream_t>(stream_ptr)};
+  return ka::forward_impl(a);
+}
 
-  const int vs = (v_global + kSlices - 1) / kSlices;
-  const int sub = (vs + kSubCols - 1) / kSubCols;
-  const int n_slices_local = kSlices / world;
-  if (vocab_offset != rank * n_slices_local * vs) return -8;
-  {
-    const long long hi = static_cast<long long>(rank + 1) * n_slices_local * vs;
-    const long long end = hi < v_global ? hi : v_global;
-    const long long expect = end - vocab_offset > 0 ? end - vocab_offset : 0;
-    if (v_local != expect) return -9;
-  }
-  const size_t ldp = static_cast<size_t>(panel_rows);
-  const size_t n_blocks_max = ldp / kBM;
-  if (n_blocks_max > 65535) return -12;
-
-  LogpParams p = {};
-  uint8_t* ws = static_cast<uint8_t*>(workspace);
-  const size_t n_chunks_max = static_cast<size_t>(kSlices) * sub;
-  p.part_m = reinterpret_cast<float*>(ws);
-  p.part_l = p.part_m + n_chunks_max * ldp;
-  p.tgt = p.part_l + n_chunks_max * ldp;
-  p.counters = reinterpret_cast<unsigned*>(p.tgt + ldp);
-  p.status = reinterpret_cast<int*>(ws + ka_lmhead_logp_status_offset(v_global, panel_rows));
-  for (int d = 0; d < 8; ++d) {
-    p.xbuf[d] = nullptr;
-    p.xflag[d] = nullptr;
-  }
-  if (world > 1) {
-    const size_t xbuf_bytes = 2 * static_cast<size_t>(world) * ldp * sizeof(float4);
-    for (int d = 0; d < world; ++d) {
-      uint8_t* base = static_cast<uint8_t*>(peer_exchange[d]);
-      if (!base) return -7;
-      p.xbuf[d] = reinterpret_cast<float4*>(base);
-      p.xflag[d] = reinterpret_cast<unsigned*>(base + xbuf_bytes);
-    }
-  }
-  p.ids = ids;
-  p.logp = logp;
-  p.lse = lse;
-  p.m = m;
-  p.k = k;
-  p.v_global = v_global;
-  p.v_local = v_local;
-  p.vocab_offset = vocab_offset;
-  p.vs = vs;
-  p.sub = sub;
-  p.n_slices_local = n_slices_local;
-  p.n_chunks = n_slices_local * sub;
-  p.ldp = static_cast<int>(ldp);
-  p.n_blocks_max = static_cast<int>(n_blocks_max);
-  p.world = world;
-  p.rank = rank;
-  p.scale = scale;
-  p.timeout_ns = timeout_ns;
-  // Sub-slices that run side by side (cg) x row tiles that run side by side (mg) ~ CTA pairs.
-  // KA_LOGP_CG overrides the default split for tuning.
-  int cg_pref = 8;
-  if (const char* e = getenv("KA_LOGP_CG")) {
-    const int v = atoi(e);
-    if (v >= 1 && v <= 64) cg_pref = v;
-  }
-  p.cg = p.n_chunks < cg_pref ? p.n_chunks : cg_pref;
-  {
-    const int pairs = num_sms / cta_group;
-    int mg = pairs / p.cg;
-    if (mg < 1) mg = 1;
-    p.mg = mg;
-  }
-
-  CUtensorMap tm_h, tm_w;
-  int rc = make_tmap_2d_16bit_sw128(&tm_h, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, hidden, static_cast<uint64_t>(m),
-                                    static_cast<uint64_t>(k), static_cast<uint64_t>(k), kBM, kBK);
-  if (rc != 0) return -20 + rc;
-  rc = make_tmap_2d_16bit_sw128(&tm_w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, weight,
-                                static_cast<uint64_t>(v_local > 0 ? v_local : 1), static_cast<uint64_t>(k),
-                                static_cast<uint64_t>(k), 128, kBK);
-  if (rc != 0) return -40 + rc;
-
-  const int rows_per_mtile = kBM * cta_group;
-  unsigned epoch = epoch_base;
-  for (int row_begin = 0; row_begin < m; row_begin += panel_rows) {
-    const int rows = (m - row_begin) < panel_rows ? (m - row_begin) : panel_rows;
-    p.row_begin = row_begin;
-    p.rows = rows;
-    p.n_mtiles = (rows + rows_per_mtile - 1) / rows_per_mtile;
-    p.epoch = epoch++;
-    rc = (cta_group == 1) ? launch_panel<1>(tm_h, tm_w, p, num_sms, stream)
-                          : launch_panel<2>(tm_h, tm_w, p, num_sms, stream);
-    if (rc != 0) return rc;
-  }
-  return 0;
+int ka_lmhead_logp_forward_sharded(const void* hidden_local, const void* weight, const long long* ids_local,
+                                   float* logp, float* lse, void* workspace, size_t workspace_bytes,
+                                   void* const* peer_exchange, void* const* peer_gather, int m_local, int k,
+                                   int v_global, int v_local, int vocab_offset, int world, int rank,
+                                   unsigned epoch_base, float scale, int panel_rows, int out_all, int cta_group,
+                                   int num_sms, unsigned long long timeout_ns, void* stream_ptr) {
+  ka::FwdArgs a = {hidden_local, weight, ids_local, logp, lse, workspace, workspace_bytes, peer_exchange,
+                   peer_gather, m_local, k, v_global, v_local, vocab_offset, world, rank, epoch_base, scale,
+                   panel_rows, 1, out_all, cta_group, num_sms, timeout_ns, static_cast<cudaStream_t>(stream_ptr)};
+  return ka::forward_impl(a);
 }
 
 }  // extern "C"
@@ -779,8 +1060,6 @@ int ka_lmhead_logp_forward(const void* hidden, const void* weight, const long lo
 // ------------------------------------------------------------------------------------------
 // Allocation-free entry point (see fused_lmhead_logp_noalloc.h for who needs it and the rules).
 // ------------------------------------------------------------------------------------------
-#include <mutex>
-
 #include "fused_lmhead_logp_noalloc.h"
 
 // The kernel's scratch for callers that cannot allocate: partials, target logits, counters
@@ -789,7 +1068,7 @@ int ka_lmhead_logp_forward(const void* hidden, const void* weight, const long lo
 static __device__ __align__(256) unsigned char ka_noalloc_scratch[KA_NOALLOC_SCRATCH_BYTES];
 
 namespace {
-constexpr int kMaxDevices = 64;
+constexpr int kMaxDevices = 64;  // devices with a cached scratch address
 std::mutex g_noalloc_mutex;
 void* g_noalloc_ptr[kMaxDevices] = {};
 

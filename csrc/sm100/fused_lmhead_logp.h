@@ -33,6 +33,23 @@ struct LogpParams {
   unsigned epoch;        // value the flags of this launch carry
   float scale;           // logits are scale * <h, w>; must be > 0
   unsigned long long timeout_ns;
+  int mt_rot;            // rotation of the row-tile order (row-sharded input: own rows first)
+
+  // ---- row-sharded input (gather != 0): rank r holds rows [r * m_local, (r + 1) * m_local) of
+  // the hidden states and the ids; the kernel pushes its rows of the panel into every peer's
+  // gather buffer and reads the other ranks' rows from its own buffer once their flags are up.
+  int gather;
+  int out_all;           // 1: every rank writes all world * m_local results; 0: only its own m_local
+  int m_local;           // rows per rank (the same on every rank)
+  int pl;                // rows per rank and panel = panel_rows / world (multiple of 256)
+  int local_row_begin;   // first local row of this panel
+  int rows_local;        // local rows in this panel (the same on every rank)
+  int bps;               // 128-row blocks per source rank in this panel (even)
+  const void* h_local;   // [m_local, k] bf16
+  uint8_t* gbuf[8];      // per destination rank: [2][world][pl][k] bf16 gathered rows
+  long long* gids[8];    // per destination rank: [2][world][pl] gathered ids
+  unsigned* gflag[8];    // per destination rank: [world][pl / 128] epoch of the last pushed block
+  unsigned* pcount;      // [pl / 128] local: 32-row pieces of a block pushed so far (self-cleaning)
 };
 
 }  // namespace ka
@@ -59,4 +76,25 @@ int ka_lmhead_logp_forward(const void* hidden, const void* weight, const long lo
                            int m, int k, int v_global, int v_local, int vocab_offset, int world, int rank,
                            unsigned epoch_base, float scale, int panel_rows, int cta_group, int num_sms,
                            unsigned long long timeout_ns, void* stream);
+
+// Bytes of the symmetric gather arena each rank maps for its peers when the rows are sharded
+// over the ranks: two generations of panel_rows x k bf16 rows and of panel_rows ids, the block
+// flags and the push counters. Must be zero-initialised once.
+size_t ka_lmhead_logp_gather_bytes(int world, int panel_rows, int k);
+
+// Row-sharded variant: rank r passes only its rows `hidden_local` [m_local, k] and `ids_local`
+// [m_local] of a batch of world * m_local rows (global row = r * m_local + local row). Inside
+// the kernel every rank pushes its rows of a panel to the peers' gather arenas with bulk copies
+// over NVLink and raises a flag per (source rank, 128-row block); the TMA producer waits
+// (bounded) for a block's flag and then loads the block from this GPU's own arena, own rows
+// first. `out_all` = 0: logp / lse are [m_local], this rank's rows. `out_all` = 1: they are
+// [world * m_local] and every rank writes every row. `peer_gather[d]` is rank d's gather arena
+// as mapped into this process. panel_rows must be a multiple of 256 * world. Consumes
+// ceil(m_local / (panel_rows / world)) epochs of the exchange and gather arenas.
+int ka_lmhead_logp_forward_sharded(const void* hidden_local, const void* weight, const long long* ids_local,
+                                   float* logp, float* lse, void* workspace, size_t workspace_bytes,
+                                   void* const* peer_exchange, void* const* peer_gather, int m_local, int k,
+                                   int v_global, int v_local, int vocab_offset, int world, int rank,
+                                   unsigned epoch_base, float scale, int panel_rows, int out_all, int cta_group,
+                                   int num_sms, unsigned long long timeout_ns, void* stream);
 }

@@ -37,8 +37,12 @@ extern "C" {
 
 // hidden [m, k] bf16 row-major, weight [vocab, k] bf16 row-major, ids [m] int64,
 // logp [m] fp32 (output), lse [m] fp32 (output, may be null). scale > 0, k % 8 == 0.
+// `timeout_ns` bounds every wait inside the kernel (on a TMA transfer, an accumulator, a
+// barrier); a wait that runs out is reported through the status block and the kernel returns.
+// Pass about 2e9; with 0 every wait that is not satisfied at once gives up.
 // Returns 0 on success; -30 if vocab exceeds KA_NOALLOC_MAX_VOCAB; -31 if the scratch address
-// could not be resolved; other negative codes as ka_lmhead_logp_forward.
+// could not be resolved; -32 if clearing the counters and the status block could not be
+// enqueued on `stream`; other negative codes as ka_lmhead_logp_forward.
 int ka_lmhead_logp_forward_noalloc(const void* hidden, const void* weight, const long long* ids, float* logp,
                                    float* lse, int m, int k, int vocab, float scale, int cta_group, int num_sms,
                                    unsigned long long timeout_ns, void* stream);

@@ -73,6 +73,17 @@ class GRPOTrainer:
             raise ValueError("zero_stage must be 0 or 1")
         else:
             self.optimizer = FusedAdamW(model.parameters(), lr=lr, weight_decay=weight_decay)
+        self._opt_args = dict(lr=lr, weight_decay=weight_decay)
+        # Ranks drift apart during a rollout (early stops, the user's reward function), and the
+        # device-side waits of the fused collectives are bounded by a couple of seconds. A host
+        # barrier over a CPU group at the start of every update absorbs the skew; what a device
+        # wait still reports afterwards is a real failure (see _check_device_waits).
+        tp = getattr(model, "tp", None)
+        self._multi_rank = dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1 and \
+            (self.dp or (tp is not None and tp.world > 1))
+        self._host_group = None
+        if self._multi_rank and self.on_cuda and dist.get_backend() != "gloo":
+            self._host_group = dist.new_group(backend="gloo")     # collective: every rank builds a trainer
 
     def rebind_data_parallel(self, group) -> None:
         """Continue on another data-parallel group (after ``parallel.health.shrink_group``: the
@@ -81,6 +92,20 @@ class GRPOTrainer:
         self.dp_world = dist.get_world_size(group)
         self.dp_rank = dist.get_rank(group)
         self.dp = self.dp_world > 1
+        # the groups of the old world still contain the ranks that left: meet on the new one
+        self._host_group = None
+        self._rendezvous_group = group
+        from ..parallel.zero import ShardedAdamW
+
+        if isinstance(self.optimizer, ShardedAdamW):
+            # The departed ranks took their slices of the master weights and moments with them.
+            # Re-shard over the new group: master weights restart from the bf16 parameters (which
+            # every rank holds in full); the moments and the step count restart at zero (a fresh
+            # optimizer, consistent bias correction). Load a checkpoint written by the new group
+            # afterwards to continue with exact state.
+            self.optimizer = ShardedAdamW(self.model.parameters(), group=group, **self._opt_args) if self.dp else \
+                FusedAdamW(self.model.parameters(), **self._opt_args)
+            logger.warn_once("ZeRO-1 optimizer state was re-sharded after the group changed: moments reset")
         if self.reducer is not None:
             self.reducer.close()
             self.reducer = None
@@ -117,6 +142,7 @@ class GRPOTrainer:
         tensor parallel (DP x TP: pass its data-parallel group as ``dp_group``); rollouts then come
         from elsewhere, since generation runs on an unsharded model. Returns ``(loss, stats)``."""
         dev = sequences.device
+        self._host_rendezvous()
         if self.reducer is not None:
             self.reducer.zero_grad()
         else:
@@ -161,9 +187,33 @@ class GRPOTrainer:
                         p.grad.div_(self.dp_world)
             if getattr(self.model, "tp", None) is not None and self.model.tp.world > 1:
                 self.model.reduce_replicated_grads()     # norm and embedding weights of a sharded model
+        scale = self._clip_scale()
+        self._check_device_waits(dev)      # raises before the weights move if a reduction is incomplete
         with profile_range("grpo/optimizer", dev):
-            self.optimizer.step(grad_scale=self._clip_scale())
+            self.optimizer.step(grad_scale=scale)
         return loss, stats
+
+    def _host_rendezvous(self) -> None:
+        """Every rank of the job arrives here before the update's first kernel is launched."""
+        if not self._multi_rank:
+            return
+        if getattr(self, "_rendezvous_group", None) is not None:
+            dist.barrier(self._rendezvous_group)
+        elif self._host_group is not None:
+            dist.barrier(self._host_group)
+        elif not self.on_cuda:
+            dist.barrier()
+
+    def _check_device_waits(self, dev) -> None:
+        """One read of all status blocks the step's kernels report into (gradient buckets,
+        scratch all-reduces, the tensor-parallel GEMMs, the fused log-prob). On a timeout the
+        optimizer does not step: the gradients may be partly reduced. The arenas must then be
+        cleared on every rank (``PeerArena.zero``) before the step is repeated."""
+        if not (self._multi_rank and self.on_cuda):
+            return
+        from ..parallel.collectives import check_device_status
+
+        check_device_status(dev)
 
     def _clip_scale(self) -> float:
         if self.max_grad_norm is None:

@@ -35,9 +35,9 @@ class OpBackend(Enum, metaclass=_LookupMeta):
     SM100_SAMPLING = "kernel_align_b200.ops.sampling.sample"
     SM100_ATTENTION = "kernel_align_b200.ops.attention.attention"
     SM100_GEMM = "kernel_align_b200.ops.gemm.gemm_bi"
-    SM100_RMSNORM = "kernel_align_b200.ops.rmsnorm.rmsnorm"
-    SM100_ROPE = "kernel_align_b200.ops.rope.rope"
-    SM100_SWIGLU = "kernel_align_b200.ops.swiglu.swiglu"
+    SM100_RMSNORM = "kernel_align_b200.ops.layer_ops.rmsnorm"
+    SM100_ROPE = "kernel_align_b200.ops.layer_ops.rope_"
+    SM100_SWIGLU = "kernel_align_b200.ops.layer_ops.swiglu"
     SM100_GRPO_LOSS = "kernel_align_b200.ops.grpo_loss.grpo_loss"
     SM100_ALLREDUCE = "kernel_align_b200.parallel.collectives.all_reduce_det"
     SM100_GEMM_RS = "kernel_align_b200.parallel.tp_gemm.gemm_reduce_scatter"

@@ -78,7 +78,8 @@ def workspace_bytes(vocab: int, panel_rows: int = DEFAULT_PANEL_ROWS) -> int:
 
 _WHERE = {1: "producer waiting for a free stage", 2: "MMA waiting for operands",
           3: "MMA waiting for a free accumulator", 4: "epilogue waiting for an accumulator",
-          5: "waiting for a peer rank's flag"}
+          5: "waiting for a peer rank's flag", 6: "waiting for a peer rank's rows (gather flag)",
+          7: "row pusher waiting for its staging copy"}
 
 
 def check_status(ws_status: torch.Tensor) -> None:
@@ -106,6 +107,17 @@ class VocabParallel:
     epoch: int = 1
     panel_rows: int = DEFAULT_PANEL_ROWS
     process_group: object = None   # torch.distributed group (None: the default group); CPU path and backward
+    gather_ptrs: dict = field(default_factory=dict)   # hidden size -> addresses of every rank's gather arena
+
+    def gather_arena_ptrs(self, k: int) -> list[int]:
+        """Addresses of the ranks' gather arenas for hidden size ``k`` (row-sharded input),
+        allocated collectively on first use: every rank must ask in the same order."""
+        ptrs = self.gather_ptrs.get(k)
+        if ptrs is None:
+            from ..parallel.peer import attach_gather_arena
+
+            ptrs = attach_gather_arena(self, k)
+        return ptrs
 
 
 def _lmhead_logp_forward(
@@ -121,13 +133,17 @@ def _lmhead_logp_forward(
     cta_group: int = 2,
     out: Optional[torch.Tensor] = None,
     check: bool = False,
+    row_sharded: bool = False,
+    gather_output: bool = False,
 ):
     """Per-token log-probabilities of ``ids`` under ``softmax(scale * hidden @ weight.T)``.
 
     hidden: ``[..., K]`` bf16; weight: ``[V_local, K]`` bf16 (this rank's vocabulary shard,
     whole canonical slices, see :func:`vocab_shard_range`); ids: ``[...]`` integer, global
     ids. Ids outside ``[0, vocab)`` give 0. Returns fp32 ``[...]`` (and the log-sum-exp if
-    ``return_lse``).
+    ``return_lse``). With ``row_sharded`` the rank passes only its rows of the batch (the same
+    number on every rank) and gets their results, or, with ``gather_output``, the flat
+    ``[world * rows]`` results of the whole batch.
     """
     lead = hidden.shape[:-1]
     k = hidden.shape[-1]
@@ -137,6 +153,9 @@ def _lmhead_logp_forward(
         raise ValueError("ids must have one entry per row of hidden")
     world = 1 if group is None else group.world
     rank = 0 if group is None else group.rank
+    sharded = bool(row_sharded) and world > 1
+    if sharded and gather_output:
+        lead = (world * m,)
     v_global = int(vocab) if vocab is not None else int(weight.shape[0])
     lo, hi = vocab_shard_range(v_global, rank, world)
     if weight.shape[0] != hi - lo or weight.shape[1] != k:
@@ -145,6 +164,24 @@ def _lmhead_logp_forward(
     if hidden.device.type != "cuda":
         from . import cpu_ops
 
+        if sharded:
+            # the rows travel over the CPU backend first; the rest is the replicated-rows path
+            import torch.distributed as dist
+
+            pg = getattr(group, "process_group", None)
+            hs = [torch.empty_like(h2) for _ in range(world)]
+            iv = ids.reshape(-1).to(torch.int64).contiguous()
+            ivs = [torch.empty_like(iv) for _ in range(world)]
+            dist.all_gather(hs, h2.contiguous(), group=pg)
+            dist.all_gather(ivs, iv, group=pg)
+            res = _lmhead_logp_forward(torch.cat(hs), weight, torch.cat(ivs), scale=scale, vocab=vocab, group=group,
+                                       return_lse=return_lse, panel_rows=panel_rows)
+            if gather_output:
+                return res
+            sl = slice(rank * m, (rank + 1) * m)
+            if return_lse:
+                return res[0][sl].reshape(lead), res[1][sl].reshape(lead)
+            return res[sl].reshape(lead)
         if world != 1:
             # vocabulary parallel over the CPU backend of torch.distributed (gloo): every rank
             # computes the states of its canonical slices, all ranks gather the eight of them in
@@ -184,12 +221,17 @@ def _lmhead_logp_forward(
     h2 = h2.contiguous()
     w = weight.contiguous()
     ids64 = ids.reshape(-1).to(torch.int64).contiguous()
-    logp = out.reshape(-1) if out is not None else torch.empty(m, dtype=torch.float32, device=hidden.device)
-    lse = torch.empty(m, dtype=torch.float32, device=hidden.device) if return_lse else None
+    m_out = world * m if (sharded and gather_output) else m
+    logp = out.reshape(-1) if out is not None else torch.empty(m_out, dtype=torch.float32, device=hidden.device)
+    if logp.numel() != m_out:
+        raise ValueError(f"out must have {m_out} elements")
+    lse = torch.empty(m_out, dtype=torch.float32, device=hidden.device) if return_lse else None
     if group is not None:
         panel_rows = group.panel_rows
     ws = _get_workspace(hidden.device, v_global, panel_rows)
-    n_panels = -(-m // panel_rows)
+    if sharded and panel_rows % (256 * world) != 0:
+        raise ValueError("row-sharded input needs panel_rows to be a multiple of 256 * world")
+    n_panels = -(-m // (panel_rows // world)) if sharded else -(-m // panel_rows)
     peer_arr = None
     if world > 1:
         peer_arr = (ctypes.c_void_p * world)(*group.exchange_ptrs)
@@ -200,14 +242,25 @@ def _lmhead_logp_forward(
         ws.epoch += n_panels
     props = torch.cuda.get_device_properties(hidden.device)
     stream = torch.cuda.current_stream(hidden.device).cuda_stream
-    rc = lib.ka_lmhead_logp_forward(
-        h2.data_ptr(), w.data_ptr(), ids64.data_ptr(), logp.data_ptr(),
-        lse.data_ptr() if lse is not None else None,
-        ws.buf.data_ptr(), ws.nbytes, peer_arr,
-        m, k, v_global, hi - lo, lo, world, rank,
-        epoch & 0xFFFFFFFF, float(scale), panel_rows, cta_group, props.multi_processor_count,
-        default_timeout_ns(), stream,
-    )
+    if sharded:
+        gather_arr = (ctypes.c_void_p * world)(*group.gather_arena_ptrs(k))
+        rc = lib.ka_lmhead_logp_forward_sharded(
+            h2.data_ptr(), w.data_ptr(), ids64.data_ptr(), logp.data_ptr(),
+            lse.data_ptr() if lse is not None else None,
+            ws.buf.data_ptr(), ws.nbytes, peer_arr, gather_arr,
+            m, k, v_global, hi - lo, lo, world, rank,
+            epoch & 0xFFFFFFFF, float(scale), panel_rows, 1 if gather_output else 0, cta_group,
+            props.multi_processor_count, default_timeout_ns(), stream,
+        )
+    else:
+        rc = lib.ka_lmhead_logp_forward(
+            h2.data_ptr(), w.data_ptr(), ids64.data_ptr(), logp.data_ptr(),
+            lse.data_ptr() if lse is not None else None,
+            ws.buf.data_ptr(), ws.nbytes, peer_arr,
+            m, k, v_global, hi - lo, lo, world, rank,
+            epoch & 0xFFFFFFFF, float(scale), panel_rows, cta_group, props.multi_processor_count,
+            default_timeout_ns(), stream,
+        )
     if rc != 0:
         raise RuntimeError(f"ka_lmhead_logp_forward rejected its arguments (code {rc})")
     if check:
@@ -226,11 +279,81 @@ def last_status(device: torch.device, vocab: int, panel_rows: int = DEFAULT_PANE
 _GRAD_PANEL_BYTES = 8 << 30
 
 
+def _logp_backward(hidden, weight, ids, lse, g, scale, vocab, group, need_dh, need_dw):
+    """Gradients of the log-probabilities with respect to ``hidden`` (all rows, summed over the
+    vocabulary shards of the group) and to this rank's ``weight`` shard. The logits are
+    recomputed tile by tile inside the GEMM kernel (``kEpiLogitsGrad`` epilogue of
+    ``csrc/sm100/gemm.cu``), which writes ``d_logits = g * scale * (onehot - softmax)`` as bf16
+    for a panel of rows; two GEMMs follow: ``d_hidden = d_logits @ W``, ``d_W = d_logits^T @ hidden``."""
+    from . import gemm as _gemm
+
+    k = hidden.shape[-1]
+    h2 = hidden.reshape(-1, k).contiguous()
+    m = h2.shape[0]
+    v_global = int(vocab) if vocab is not None else int(weight.shape[0])
+    world = 1 if group is None else group.world
+    rank = 0 if group is None else group.rank
+    lo, hi = vocab_shard_range(v_global, rank, world)
+    v_local = hi - lo
+    ids64 = ids.reshape(-1).to(torch.int64).contiguous()
+    valid = (ids64 >= 0) & (ids64 < v_global)
+    g32 = (g.reshape(-1).float() * valid).contiguous()
+    lse32 = lse.reshape(-1).float().contiguous()
+    w = weight.contiguous()
+    if hidden.device.type != "cuda":
+        # the same formula in PyTorch (d_logits rounded to bf16 like the kernel's output)
+        logits = float(scale) * (h2.float() @ w.float().t())
+        d_logits = -(g32 * float(scale))[:, None] * torch.exp(logits - lse32[:, None])
+        mine = valid & (ids64 >= lo) & (ids64 < hi)
+        rows = torch.nonzero(mine).flatten()
+        d_logits[rows, ids64[rows] - lo] += g32[rows] * float(scale)
+        d_logits = d_logits.to(torch.bfloat16).float()
+        d_hidden = (d_logits @ w.float()).to(hidden.dtype) if need_dh else None
+        d_weight = (d_logits.t() @ h2.float()).to(weight.dtype) if need_dw else None
+        if d_hidden is not None and world > 1:
+            from ..parallel.collectives import all_reduce_det
+
+            all_reduce_det(d_hidden, getattr(group, "process_group", None))
+        return d_hidden, d_weight
+    lib = _native.cuda()
+    fn = lib.ka_lmhead_logits_grad
+    fn.restype = ctypes.c_int
+    fn.argtypes = [ctypes.c_void_p] * 6 + [ctypes.c_longlong, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                           ctypes.c_float, ctypes.c_int, ctypes.c_void_p, ctypes.c_int,
+                                           ctypes.c_ulonglong, ctypes.c_void_p]
+    props = torch.cuda.get_device_properties(h2.device)
+    stream = torch.cuda.current_stream(h2.device).cuda_stream
+    rows_per_panel = max(256, min(m, (_GRAD_PANEL_BYTES // max(1, v_local * 2)) // 256 * 256))
+    d_hidden = torch.empty_like(h2) if need_dh else None
+    d_weight = None
+    multi = rows_per_panel < m
+    for r0 in range(0, m, rows_per_panel):
+        r1 = min(m, r0 + rows_per_panel)
+        d_logits = torch.empty(r1 - r0, v_local, dtype=torch.bfloat16, device=h2.device)
+        rc = fn(h2[r0:r1].data_ptr(), w.data_ptr(), ids64[r0:r1].data_ptr(), lse32[r0:r1].data_ptr(),
+                g32[r0:r1].data_ptr(), d_logits.data_ptr(), v_local, r1 - r0, v_local, k, float(scale), lo,
+                _gemm.status_buffer(h2.device).data_ptr(), props.multi_processor_count, default_timeout_ns(),
+                stream)
+        if rc != 0:
+            raise RuntimeError(f"ka_lmhead_logits_grad rejected its arguments (code {rc})")
+        if need_dh:
+            d_hidden[r0:r1] = _gemm.gemm_bi(d_logits, w, trans_b=True)
+        if need_dw:
+            part = _gemm.gemm_bi(d_logits, h2[r0:r1], trans_a=True, trans_b=True,
+                                 out_dtype=torch.float32 if multi else torch.bfloat16)
+            d_weight = part if d_weight is None else d_weight.add_(part)
+        del d_logits
+    if need_dh and world > 1:
+        from ..parallel.collectives import all_reduce_det
+
+        all_reduce_det(d_hidden, getattr(group, "process_group", None))
+    if need_dw and d_weight.dtype != weight.dtype:
+        d_weight = d_weight.to(weight.dtype)
+    return d_hidden, d_weight
+
+
 class _LmheadLogpFn(torch.autograd.Function):
-    """Differentiable fused log-prob. Backward recomputes the logits tile by tile inside the
-    GEMM kernel (``kEpiLogitsGrad`` epilogue of ``csrc/sm100/gemm.cu``), writes
-    ``d_logits = g * scale * (onehot - softmax)`` as bf16 for a panel of rows, and feeds it to
-    the two backward GEMMs: ``d_hidden = d_logits @ W`` and ``d_W = d_logits^T @ hidden``."""
+    """Differentiable fused log-prob; backward in :func:`_logp_backward`."""
 
     @staticmethod
     def forward(ctx, hidden, weight, ids, scale, vocab, group, panel_rows, cta_group):
@@ -238,94 +361,101 @@ class _LmheadLogpFn(torch.autograd.Function):
                                          return_lse=True, panel_rows=panel_rows, cta_group=cta_group)
         ctx.save_for_backward(hidden, weight, ids, lse)
         ctx.scale, ctx.vocab, ctx.group = scale, vocab, group
-        return logp
+        ctx.mark_non_differentiable(lse)
+        return logp, lse
 
     @staticmethod
-    def backward(ctx, g):
-        from . import gemm as _gemm
-
+    def backward(ctx, g, _g_lse):
         hidden, weight, ids, lse = ctx.saved_tensors
+        d_hidden, d_weight = _logp_backward(hidden, weight, ids, lse, g, ctx.scale, ctx.vocab, ctx.group,
+                                            ctx.needs_input_grad[0], ctx.needs_input_grad[1])
+        return (d_hidden.reshape(hidden.shape) if d_hidden is not None else None), d_weight, None, None, None, None, \
+            None, None
+
+
+def _all_gather_flat(x: torch.Tensor, group) -> torch.Tensor:
+    """Concatenation of every rank's ``x`` (same shape on all ranks) along dimension 0."""
+    import torch.distributed as dist
+
+    pg = getattr(group, "process_group", None)
+    x = x.contiguous()
+    if x.device.type == "cuda":
+        out = torch.empty(group.world * x.shape[0], *x.shape[1:], dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(out, x, group=pg)
+        return out
+    pieces = [torch.empty_like(x) for _ in range(group.world)]
+    dist.all_gather(pieces, x, group=pg)
+    return torch.cat(pieces)
+
+
+class _LmheadLogpShardedFn(torch.autograd.Function):
+    """Differentiable fused log-prob on row-sharded hidden states. Forward gathers the rows
+    inside the kernel; backward needs every row on every rank (each rank owns a vocabulary
+    shard of the weight), so it gathers rows, ids and log-sum-exps with a collective, runs
+    :func:`_logp_backward` and keeps this rank's rows of ``d_hidden``. With ``gather_output``
+    the incoming gradient already covers all rows and must be the same on every rank."""
+
+    @staticmethod
+    def forward(ctx, hidden, weight, ids, scale, vocab, group, cta_group, gather_output):
+        logp, lse = _lmhead_logp_forward(hidden, weight, ids, scale=scale, vocab=vocab, group=group, return_lse=True,
+                                         cta_group=cta_group, row_sharded=True, gather_output=gather_output)
+        ctx.save_for_backward(hidden, weight, ids, lse)
+        ctx.scale, ctx.vocab, ctx.group, ctx.gather_output = scale, vocab, group, gather_output
+        ctx.mark_non_differentiable(lse)
+        return logp, lse
+
+    @staticmethod
+    def backward(ctx, g, _g_lse):
+        hidden, weight, ids, lse = ctx.saved_tensors
+        group = ctx.group
         k = hidden.shape[-1]
-        h2 = hidden.reshape(-1, k).contiguous()
+        h2 = hidden.reshape(-1, k)
         m = h2.shape[0]
-        v_global = int(ctx.vocab) if ctx.vocab is not None else int(weight.shape[0])
-        world = 1 if ctx.group is None else ctx.group.world
-        rank = 0 if ctx.group is None else ctx.group.rank
-        lo, hi = vocab_shard_range(v_global, rank, world)
-        v_local = hi - lo
-        ids64 = ids.reshape(-1).to(torch.int64).contiguous()
-        valid = (ids64 >= 0) & (ids64 < v_global)
-        g32 = (g.reshape(-1).float() * valid).contiguous()
-        lse32 = lse.reshape(-1).float().contiguous()
-        w = weight.contiguous()
-        if hidden.device.type != "cuda":
-            # the same formula in PyTorch (d_logits rounded to bf16 like the kernel's output)
-            logits = float(ctx.scale) * (h2.float() @ w.float().t())
-            d_logits = -(g32 * float(ctx.scale))[:, None] * torch.exp(logits - lse32[:, None])
-            mine = valid & (ids64 >= lo) & (ids64 < hi)
-            rows = torch.nonzero(mine).flatten()
-            d_logits[rows, ids64[rows] - lo] += g32[rows] * float(ctx.scale)
-            d_logits = d_logits.to(torch.bfloat16).float()
-            d_hidden = (d_logits @ w.float()).to(hidden.dtype) if ctx.needs_input_grad[0] else None
-            d_weight = (d_logits.t() @ h2.float()).to(weight.dtype) if ctx.needs_input_grad[1] else None
-            if d_hidden is not None and world > 1:
-                from ..parallel.collectives import all_reduce_det
-
-                all_reduce_det(d_hidden, getattr(ctx.group, "process_group", None))
-            return (d_hidden.reshape(hidden.shape) if d_hidden is not None else None), d_weight, None, None, None, None, \
-                None, None
-        lib = _native.cuda()
-        fn = lib.ka_lmhead_logits_grad
-        fn.restype = ctypes.c_int
-        fn.argtypes = [ctypes.c_void_p] * 6 + [ctypes.c_longlong, ctypes.c_int, ctypes.c_int, ctypes.c_int,
-                                               ctypes.c_float, ctypes.c_int, ctypes.c_void_p, ctypes.c_int,
-                                               ctypes.c_ulonglong, ctypes.c_void_p]
-        props = torch.cuda.get_device_properties(h2.device)
-        stream = torch.cuda.current_stream(h2.device).cuda_stream
-        rows_per_panel = max(256, min(m, (_GRAD_PANEL_BYTES // max(1, v_local * 2)) // 256 * 256))
-        need_dh, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
-        d_hidden = torch.empty_like(h2) if need_dh else None
-        d_weight = None
-        multi = rows_per_panel < m
-        for r0 in range(0, m, rows_per_panel):
-            r1 = min(m, r0 + rows_per_panel)
-            d_logits = torch.empty(r1 - r0, v_local, dtype=torch.bfloat16, device=h2.device)
-            rc = fn(h2[r0:r1].data_ptr(), w.data_ptr(), ids64[r0:r1].data_ptr(), lse32[r0:r1].data_ptr(),
-                    g32[r0:r1].data_ptr(), d_logits.data_ptr(), v_local, r1 - r0, v_local, k, float(ctx.scale), lo,
-                    _gemm.status_buffer(h2.device).data_ptr(), props.multi_processor_count, default_timeout_ns(),
-                    stream)
-            if rc != 0:
-                raise RuntimeError(f"ka_lmhead_logits_grad rejected its arguments (code {rc})")
-            if need_dh:
-                d_hidden[r0:r1] = _gemm.gemm_bi(d_logits, w, trans_b=True)
-            if need_dw:
-                part = _gemm.gemm_bi(d_logits, h2[r0:r1], trans_a=True, trans_b=True,
-                                     out_dtype=torch.float32 if multi else torch.bfloat16)
-                d_weight = part if d_weight is None else d_weight.add_(part)
-            del d_logits
-        if need_dh and world > 1:
-            from ..parallel.collectives import all_reduce_det
-
-            all_reduce_det(d_hidden, getattr(ctx.group, "process_group", None))
-        if need_dw and d_weight.dtype != weight.dtype:
-            d_weight = d_weight.to(weight.dtype)
-        return (d_hidden.reshape(hidden.shape) if need_dh else None), d_weight, None, None, None, None, None, None
+        h_all = _all_gather_flat(h2, group)
+        ids_all = _all_gather_flat(ids.reshape(-1).to(torch.int64), group)
+        if ctx.gather_output:
+            lse_all, g_all = lse.reshape(-1), g.reshape(-1)
+        else:
+            lse_all = _all_gather_flat(lse.reshape(-1), group)
+            g_all = _all_gather_flat(g.reshape(-1).float(), group)
+        d_hidden, d_weight = _logp_backward(h_all, weight, ids_all, lse_all, g_all, ctx.scale, ctx.vocab, group,
+                                            ctx.needs_input_grad[0], ctx.needs_input_grad[1])
+        if d_hidden is not None:
+            d_hidden = d_hidden[group.rank * m:(group.rank + 1) * m].reshape(hidden.shape)
+        return d_hidden, d_weight, None, None, None, None, None, None
 
 
 @profiled("lmhead_logp")
 def lmhead_logp(hidden: torch.Tensor, weight: torch.Tensor, ids: torch.Tensor, *, scale: float = 1.0,
                 vocab: Optional[int] = None, group: Optional[VocabParallel] = None, return_lse: bool = False,
                 panel_rows: int = DEFAULT_PANEL_ROWS, cta_group: int = 2, out: Optional[torch.Tensor] = None,
-                check: bool = False):
+                check: bool = False, row_sharded: bool = False, gather_output: bool = False):
     """Per-token log-probabilities of ``ids`` under ``softmax(scale * hidden @ weight.T)``.
 
     hidden: ``[..., K]`` bf16; weight: ``[V_local, K]`` bf16 (this rank's vocabulary shard,
     whole canonical slices, see :func:`vocab_shard_range`); ids: ``[...]`` integer, global
     ids. Ids outside ``[0, vocab)`` give 0. Returns fp32 ``[...]`` (and the log-sum-exp if
-    ``return_lse``). Differentiable with respect to ``hidden`` and ``weight``.
+    ``return_lse``). Differentiable with respect to ``hidden`` and ``weight`` (the log-sum-exp
+    is returned detached).
+
+    ``row_sharded`` (with a vocabulary-parallel ``group``): ``hidden`` and ``ids`` are this
+    rank's rows of a batch of ``world * rows`` (global row = ``rank * rows + local row``); the
+    kernel gathers the other ranks' rows over NVLink while it works on its own. The result
+    covers this rank's rows, or with ``gather_output`` the whole batch, flat ``[world * rows]``,
+    on every rank.
     """
     needs_grad = torch.is_grad_enabled() and (hidden.requires_grad or weight.requires_grad)
-    if needs_grad and not return_lse and out is None:
-        return _LmheadLogpFn.apply(hidden, weight, ids, float(scale), vocab, group, panel_rows, cta_group)
+    sharded = row_sharded and group is not None and group.world > 1
+    if needs_grad:
+        if out is not None:
+            raise ValueError("out= cannot be combined with inputs that require gradients: the result written "
+                             "there would be detached from the graph")
+        if sharded:
+            logp, lse = _LmheadLogpShardedFn.apply(hidden, weight, ids, float(scale), vocab, group, cta_group,
+                                                   bool(gather_output))
+        else:
+            logp, lse = _LmheadLogpFn.apply(hidden, weight, ids, float(scale), vocab, group, panel_rows, cta_group)
+        return (logp, lse) if return_lse else logp
     return _lmhead_logp_forward(hidden, weight, ids, scale=scale, vocab=vocab, group=group, return_lse=return_lse,
-                                panel_rows=panel_rows, cta_group=cta_group, out=out, check=check)
+                                panel_rows=panel_rows, cta_group=cta_group, out=out, check=check,
+                                row_sharded=sharded, gather_output=gather_output)

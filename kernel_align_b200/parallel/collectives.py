@@ -16,6 +16,7 @@ The reference declares ``DistributedStrategy.DATA_PARALLEL``
 """
 from __future__ import annotations
 
+import weakref
 from ctypes import c_int, c_longlong, c_size_t, c_uint, c_ulonglong, c_void_p
 from typing import Iterable, Optional, Sequence
 
@@ -40,6 +41,13 @@ def tree_sum(parts: Sequence[torch.Tensor]) -> torch.Tensor:
             nxt.append(level[-1])
         level = nxt
     return level[0]
+
+
+class CollectiveTimeout(RuntimeError):
+    """A bounded device-side wait of a fused collective ran out (a peer was late or gone)."""
+
+
+_live_vectors: "weakref.WeakSet" = weakref.WeakSet()
 
 
 class SymmetricVector:
@@ -67,9 +75,13 @@ class SymmetricVector:
         self.epoch = 0
         self.sms = props.multi_processor_count
         self.status = torch.zeros(8, dtype=torch.int32, device=dev)
+        _live_vectors.add(self)
 
-    def all_reduce_(self, stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
-        """Sum ``self.tensor`` over the group in place (enqueued on ``stream``)."""
+    def all_reduce_(self, stream: Optional[torch.cuda.Stream] = None, numel: Optional[int] = None) -> torch.Tensor:
+        """Sum ``self.tensor`` (or its first ``numel`` elements, rounded up to ``world * 4``)
+        over the group in place (enqueued on ``stream``). Every rank must pass the same count."""
+        gran = self.world * 4
+        n = self.numel if numel is None else min(self.numel, (int(numel) + gran - 1) // gran * gran)
         lib = _native.cuda()
         fn = lib.ka_allreduce_det
         fn.restype = c_int
@@ -79,7 +91,7 @@ class SymmetricVector:
         bufs = (c_void_p * self.world)(*self.arena.ptrs)
         flags = (c_void_p * self.world)(*[p + self.data_bytes for p in self.arena.ptrs])
         st = stream if stream is not None else torch.cuda.current_stream(self.tensor.device)
-        rc = fn(bufs, flags, self.numel, int(self.dtype == torch.bfloat16), self.world, self.rank,
+        rc = fn(bufs, flags, n, int(self.dtype == torch.bfloat16), self.world, self.rank,
                 self.epoch & 0xFFFFFFFF, self.status.data_ptr(), self.sms, default_timeout_ns(), st.cuda_stream)
         if rc != 0:
             raise RuntimeError(f"ka_allreduce_det rejected its arguments (code {rc})")
@@ -89,10 +101,41 @@ class SymmetricVector:
         st = self.status.cpu().tolist()
         if st[0] != 0:
             self.status.zero_()
-            raise RuntimeError(f"deterministic all-reduce gave up: code {st[0]} at site {st[1]}, aux {st[3:6]}")
+            raise CollectiveTimeout(f"deterministic all-reduce gave up: code {st[0]} at site {st[1]}, aux {st[3:6]}")
+
+
+def check_device_status(device=None) -> None:
+    """Read, with one device-to-host copy, the status blocks of every kernel with bounded waits
+    that ran on ``device`` (all-reduce vectors and gradient buckets, the GEMM family with its
+    fused reduce-scatter / all-gather, the fused log-prob) and raise :class:`CollectiveTimeout`
+    if any wait gave up. A caller that sees the exception must not use the step's results:
+    buffers may be half reduced. Clear the arenas on every rank (``PeerArena.zero``, collective)
+    before the next attempt."""
+    from ..ops import fused_logp, gemm
+
+    dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+    blocks, names = [], []
+    for v in list(_live_vectors):
+        if v.status.device == dev:
+            blocks.append(v.status)
+            names.append(f"all-reduce vector ({v.numel} x {str(v.dtype).replace('torch.', '')})")
+    blocks.append(gemm.status_buffer(dev)[:8])
+    names.append("gemm / fused tensor-parallel gemm")
+    for key, ws in fused_logp._workspaces.items():
+        if key[0] == dev.index:
+            blocks.append(ws.status[:8])
+            names.append(f"fused lm-head log-prob (vocab {key[1]})")
+    host = torch.stack([b.to(torch.int32) for b in blocks]).cpu()
+    bad = [(names[i], host[i].tolist()) for i in range(len(blocks)) if int(host[i, 0]) != 0]
+    if bad:
+        for b in blocks:
+            b.zero_()
+        detail = "; ".join(f"{n}: code {st[0]} at site {st[1]}, block {st[2]}, aux {st[3:6]}" for n, st in bad)
+        raise CollectiveTimeout("a device-side wait gave up: " + detail)
 
 
 _scratch: dict = {}
+_SMALL_SCRATCH = 1 << 20      # elements of the scratch that serves small tensors
 
 
 @profiled("all_reduce_det")
@@ -110,17 +153,24 @@ def all_reduce_det(tensor: torch.Tensor, group: Optional[dist.ProcessGroup] = No
         tensor.copy_(tree_sum(parts).to(tensor.dtype))
         return tensor
     dtype = torch.bfloat16 if tensor.dtype == torch.bfloat16 else torch.float32
-    key = (id(g), dtype, tensor.device.index)
+    # Small tensors (norm weights, scalars, one decode step's activations) and large ones
+    # (an embedding gradient) use separate scratch vectors, and a call only reduces the
+    # elements it holds: a 4096-element sum after a 1 GB one stays a 4096-element sum.
+    small = tensor.numel() <= _SMALL_SCRATCH
+    key = (id(g), dtype, tensor.device.index, small)
     vec = _scratch.get(key)
     if vec is None or vec.numel < tensor.numel():
-        vec = SymmetricVector(max(tensor.numel(), 1 << 20), dtype, g, tensor.device)
-        _scratch[key] = vec
+        vec = SymmetricVector(_SMALL_SCRATCH if small else tensor.numel(), dtype, g, tensor.device)
+        _scratch[key] = vec       # the vector it replaces (a smaller large-tensor scratch) is dropped
     flat = tensor.reshape(-1)
-    vec.tensor[: flat.numel()].copy_(flat.to(dtype))
-    if flat.numel() < vec.numel:
-        vec.tensor[flat.numel():].zero_()
-    vec.all_reduce_()
-    tensor.copy_(vec.tensor[: flat.numel()].view_as(tensor).to(tensor.dtype))
+    n = flat.numel()
+    gran = world * 4
+    n_pad = min(vec.numel, (n + gran - 1) // gran * gran)
+    vec.tensor[:n].copy_(flat.to(dtype))
+    if n_pad > n:
+        vec.tensor[n:n_pad].zero_()
+    vec.all_reduce_(numel=n_pad)
+    tensor.copy_(vec.tensor[:n].view_as(tensor).to(tensor.dtype))
     return tensor
 
 

@@ -100,12 +100,25 @@ class PeerMonitor:
         return agreed
 
 
-def shrink_group(monitor: PeerMonitor, step: int):
+def shrink_group(monitor: PeerMonitor, step: int, power_of_two: Optional[bool] = None):
     """After a :class:`PeerLost`: agree on the surviving ranks and build a process group of
     them without the ones that are gone (``new_group`` with local synchronisation, so the
-    departed ranks need not take part). Returns ``(group, ranks)``. Call it between steps, with
-    no collective in flight. The deterministic all-reduce accepts any number of CPU ranks; its
-    CUDA kernel takes 1, 2, 4 or 8, so a GPU job continues on the largest such prefix."""
+    departed ranks need not take part). Returns ``(group, ranks)``; a surviving rank that is
+    not in ``ranks`` gets ``(None, ranks)`` and has to stand by. Call it between steps, with no
+    collective in flight. The deterministic all-reduce accepts any number of CPU ranks; its
+    CUDA kernel takes 1, 2, 4 or 8, so with ``power_of_two`` (the default when CUDA is in use)
+    the group is the largest such prefix of the survivors."""
     ranks = monitor.agree_on_survivors(step)
+    if power_of_two is None:
+        import torch
+
+        power_of_two = torch.cuda.is_available()
+    if power_of_two:
+        keep = 1
+        while keep * 2 <= len(ranks):
+            keep *= 2
+        ranks = ranks[:keep]
+    if monitor.rank not in ranks:
+        return None, ranks
     group = dist.new_group(ranks, use_local_synchronization=True)
     return group, ranks

@@ -8,10 +8,16 @@ only use plain peer loads/stores on these addresses.
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
 import torch.distributed as dist
+
+# The kernels only use plain peer loads and stores (every cross-GPU sum follows a fixed order,
+# which in-switch reduction does not give), so the arenas are not bound to an NVLink multicast
+# object: a binding nobody uses only widens what a dying rank can disturb on its peers.
+os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
 
 
 class PeerArena:
@@ -63,3 +69,27 @@ def vocab_parallel_group(vocab: int, panel_rows: int = 32768, group: Optional[di
         vp.process_group = g
         _vp_groups[key] = vp
     return vp
+
+
+def attach_gather_arena(vp, k: int) -> list[int]:
+    """Allocate (collectively) the arena the fused log-prob kernel gathers row-sharded hidden
+    states of width ``k`` into: two generations of one panel of rows and ids, with their flags.
+    Its size depends on the panel and on ``k`` only, not on the number of rows."""
+    from .. import _native
+
+    nbytes = _native.cuda().ka_lmhead_logp_gather_bytes(vp.world, vp.panel_rows, k)
+    if nbytes == 0:
+        raise ValueError(f"panel_rows {vp.panel_rows} must be a multiple of 256 * world ({vp.world})")
+    arena = PeerArena(nbytes, getattr(vp, "process_group", None))
+    if not hasattr(vp, "gather_arenas"):
+        vp.gather_arenas = {}
+    vp.gather_arenas[k] = arena   # keep the mapping alive
+    vp.gather_ptrs[k] = arena.ptrs
+    return arena.ptrs
+
+
+def gather_arena_bytes(vp, k: int) -> int:
+    """Bytes of symmetric memory :func:`attach_gather_arena` holds per rank."""
+    from .. import _native
+
+    return int(_native.cuda().ka_lmhead_logp_gather_bytes(vp.world, vp.panel_rows, k))

@@ -510,7 +510,7 @@ def test_cpu_strategy_layouts_build_the_right_groups(tmp_path):
     assert not torch.equal(o[0]["logp"], o[2]["logp"])
 
 
-def _elastic_dp_worker(rank, world, port, out_dir):
+def _elastic_dp_worker(rank, world, port, out_dir, zero_stage=0):
     sys.path.insert(0, ROOT)
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -526,7 +526,7 @@ def _elastic_dp_worker(rank, world, port, out_dir):
     solo.group, solo.rank, solo.world, solo.device, solo._arenas = None, 0, 1, CPU, {}
     model = LlamaModel(cfg, tp=solo, seed=4, device=CPU)
     trainer = GRPOTrainer(model, lambda p, t: (t % 5 == 0).float().mean(1), group_size=2, max_new_tokens=3, lr=1e-3,
-                          seed=3, top_k=50, data_parallel=True)
+                          seed=3, top_k=50, data_parallel=True, zero_stage=zero_stage)
     prompts = torch.randint(0, cfg.vocab_size, (2, 8), generator=torch.Generator().manual_seed(20 + rank))
     mon = PeerMonitor(timeout_s=2.0)
     mon.check(0)
@@ -546,8 +546,12 @@ def _elastic_dp_worker(rank, world, port, out_dir):
     time.sleep(1)
 
 
-def test_cpu_data_parallel_training_continues_after_a_rank_leaves(tmp_path):
-    mp.spawn(_elastic_dp_worker, args=(3, 29821, str(tmp_path)), nprocs=3, join=True)
+@pytest.mark.parametrize("zero_stage", [0, 1])
+def test_cpu_data_parallel_training_continues_after_a_rank_leaves(tmp_path, zero_stage):
+    """With ``zero_stage=1`` the optimizer state is sharded over the ranks: after the shrink it
+    must be re-sharded over the two that are left, or the step's all-gather would wait for the
+    rank that is gone."""
+    mp.spawn(_elastic_dp_worker, args=(3, 29821 + zero_stage, str(tmp_path), zero_stage), nprocs=3, join=True)
     a, b = torch.load(tmp_path / "r0.pt"), torch.load(tmp_path / "r1.pt")
     assert a["dp_world"] == 2 and b["dp_world"] == 2
     assert torch.equal(a["w"], b["w"]) and torch.isfinite(a["loss"]) and torch.isfinite(b["loss"])

@@ -59,6 +59,15 @@ def test_noalloc_entry_matches_regular_entry_twice(cuda_device):
         torch.cuda.synchronize()
         assert rc == 0, f"call {call}: rc {rc}"
         assert torch.cuda.memory_allocated() == before
+        # torch's counter cannot see a raw cudaMalloc, the driver's free-memory figure can. The
+        # first call on a device may still load the kernel image, so the figure is compared
+        # around one more call on the same inputs.
+        free_before, _ = torch.cuda.mem_get_info()
+        rc = _call(fn, h, w, ids, logp, lse, scale=1.3)
+        torch.cuda.synchronize()
+        assert rc == 0, f"call {call} (repeat): rc {rc}"
+        free_after, _ = torch.cuda.mem_get_info()
+        assert free_after >= free_before, (free_before, free_after)
         host = (ctypes.c_int * 8)()
         assert status(v, host) == 0 and list(host)[0] == 0, list(host)
         assert (logp - want).abs().max().item() < 2e-3

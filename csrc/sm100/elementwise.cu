@@ -171,68 +171,135 @@ swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* _
   }
 }
 
-// Backward of y = bf16(bf16(x * inv) * w): one CTA per chunk of kRmsChunk rows (fixed, so the
-// order in which rows enter d_w does not depend on the grid), threads own columns.
+// Backward of y = bf16(bf16(x * inv) * w).
 //   dx = inv * (dy*w - n * mean(dy*w*n)),  n = x * inv;   dw_partial[chunk] = sum_rows dy * n
+// One CTA per chunk of kRmsChunk rows (fixed, so the order in which rows enter d_w does not
+// depend on the grid); threads own columns. kRows rows are in flight at once: their x and dy
+// vectors are loaded once into registers and serve all three steps (sum of squares, the dot
+// product, dx / dw), and the block reductions of the kRows rows share their two barriers.
 constexpr int kRmsChunk = 128;
 
-__global__ void __launch_bounds__(256)
+// Fixed-order sums of R values per thread over the CTA (8 warps): lanes by xor-shuffle, then the
+// eight warp sums left to right, the same in every thread.
+template <int R>
+__device__ __forceinline__ void block_sum_fixed_multi(float (&v)[R], float (*s_warp)[8]) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v[r] = __fadd_rn(v[r], __shfl_xor_sync(0xffffffffu, v[r], o));
+    if (lane == 0) s_warp[r][warp] = v[r];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t = __fadd_rn(t, s_warp[r][w]);
+    v[r] = t;
+  }
+  __syncthreads();
+}
+
+// VPT: 16-byte vectors per thread and row (d <= 2048 * VPT); kRows: rows in flight.
+template <int VPT, int kRows>
+__global__ void __launch_bounds__(256, 2)
 rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                    const __nv_bfloat16* __restrict__ dy, __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_part,
                    int rows, int d, float eps) {
-  __shared__ float s_warp[8];
+  __shared__ float s_warp[kRows][8];
   const int chunk = blockIdx.x;
   const int r0 = chunk * kRmsChunk, r1 = min(rows, r0 + kRmsChunk);
   const int nvec = d / 8;
-  // each thread owns the vectors threadIdx.x, threadIdx.x + 256, ... (at most 4 for d <= 8192)
-  float dw_acc[4][8];
+  float dw_acc[VPT][8];
 #pragma unroll
-  for (int a = 0; a < 4; ++a)
+  for (int a = 0; a < VPT; ++a)
 #pragma unroll
     for (int j = 0; j < 8; ++j) dw_acc[a][j] = 0.f;
-  for (int row = r0; row < r1; ++row) {
-    const Bf16x8* xp = reinterpret_cast<const Bf16x8*>(x + static_cast<size_t>(row) * d);
-    const Bf16x8* gp = reinterpret_cast<const Bf16x8*>(dy + static_cast<size_t>(row) * d);
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < nvec; i += 256) {
-      const Bf16x8 a = xp[i];
+  const Bf16x8* wp = reinterpret_cast<const Bf16x8*>(w);  // re-read per use: it stays in L1
+  for (int row0 = r0; row0 < r1; row0 += kRows) {
+    Bf16x8 xv[kRows][VPT], gv[kRows][VPT];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float f = __bfloat162float(a.v[j]);
-        ss = __fmaf_rn(f, f, ss);
+    for (int r = 0; r < kRows; ++r) {
+      const int row = row0 + r;
+#pragma unroll
+      for (int a = 0; a < VPT; ++a) {
+        const int i = threadIdx.x + a * 256;
+        if (row < r1 && i < nvec) {
+          xv[r][a] = reinterpret_cast<const Bf16x8*>(x + static_cast<size_t>(row) * d)[i];
+          gv[r][a] = reinterpret_cast<const Bf16x8*>(dy + static_cast<size_t>(row) * d)[i];
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            xv[r][a].v[j] = __float2bfloat16_rn(0.f);
+            gv[r][a].v[j] = __float2bfloat16_rn(0.f);
+          }
+        }
       }
     }
-    const float total = block_sum_fixed(ss, s_warp, 8);
-    const float inv = __fdiv_rn(1.f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, static_cast<float>(d)), eps)));
-    float dot = 0.f;
-    for (int i = threadIdx.x; i < nvec; i += 256) {
-      const Bf16x8 a = xp[i], g = gp[i], ww = reinterpret_cast<const Bf16x8*>(w)[i];
+    float red[kRows];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float n = __fmul_rn(__bfloat162float(a.v[j]), inv);
-        dot = __fmaf_rn(__fmul_rn(__bfloat162float(g.v[j]), __bfloat162float(ww.v[j])), n, dot);
-      }
+    for (int r = 0; r < kRows; ++r) {
+      float ss = 0.f;
+#pragma unroll
+      for (int a = 0; a < VPT; ++a)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float f = __bfloat162float(xv[r][a].v[j]);
+          ss = __fmaf_rn(f, f, ss);
+        }
+      red[r] = ss;
     }
-    const float mean_dot = __fdiv_rn(block_sum_fixed(dot, s_warp, 8), static_cast<float>(d));
-    int slot = 0;
-    for (int i = threadIdx.x; i < nvec; i += 256, ++slot) {
-      const Bf16x8 a = xp[i], g = gp[i], ww = reinterpret_cast<const Bf16x8*>(w)[i];
-      Bf16x8 o;
+    block_sum_fixed_multi<kRows>(red, s_warp);
+    float inv[kRows];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float n = __fmul_rn(__bfloat162float(a.v[j]), inv);
-        const float gw = __fmul_rn(__bfloat162float(g.v[j]), __bfloat162float(ww.v[j]));
-        o.v[j] = __float2bfloat16_rn(__fmul_rn(inv, __fsub_rn(gw, __fmul_rn(n, mean_dot))));
-        if (slot < 4) dw_acc[slot][j] = __fmaf_rn(__bfloat162float(g.v[j]), n, dw_acc[slot][j]);
+    for (int r = 0; r < kRows; ++r) {
+      inv[r] = __fdiv_rn(1.f, __fsqrt_rn(__fadd_rn(__fdiv_rn(red[r], static_cast<float>(d)), eps)));
+      float dot = 0.f;
+#pragma unroll
+      for (int a = 0; a < VPT; ++a) {
+        const int i = threadIdx.x + a * 256;
+        if (i >= nvec) continue;
+        const Bf16x8 wv = wp[i];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float n = __fmul_rn(__bfloat162float(xv[r][a].v[j]), inv[r]);
+          dot = __fmaf_rn(__fmul_rn(__bfloat162float(gv[r][a].v[j]), __bfloat162float(wv.v[j])), n, dot);
+        }
       }
-      reinterpret_cast<Bf16x8*>(dx + static_cast<size_t>(row) * d)[i] = o;
+      red[r] = dot;
+    }
+    block_sum_fixed_multi<kRows>(red, s_warp);
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) {
+      const int row = row0 + r;
+      if (row >= r1) break;  // uniform over the CTA
+      const float mean_dot = __fdiv_rn(red[r], static_cast<float>(d));
+#pragma unroll
+      for (int a = 0; a < VPT; ++a) {
+        const int i = threadIdx.x + a * 256;
+        if (i >= nvec) continue;
+        const Bf16x8 wv = wp[i];
+        Bf16x8 o;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float n = __fmul_rn(__bfloat162float(xv[r][a].v[j]), inv[r]);
+          const float g = __bfloat162float(gv[r][a].v[j]);
+          const float gw = __fmul_rn(g, __bfloat162float(wv.v[j]));
+          o.v[j] = __float2bfloat16_rn(__fmul_rn(inv[r], __fsub_rn(gw, __fmul_rn(n, mean_dot))));
+          dw_acc[a][j] = __fmaf_rn(g, n, dw_acc[a][j]);  // rows enter in increasing order
+        }
+        reinterpret_cast<Bf16x8*>(dx + static_cast<size_t>(row) * d)[i] = o;
+      }
     }
   }
-  int slot = 0;
-  for (int i = threadIdx.x; i < nvec && slot < 4; i += 256, ++slot) {
-    float* dst = dw_part + static_cast<size_t>(chunk) * d + i * 8;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) dst[j] = dw_acc[slot][j];
+  for (int a = 0; a < VPT; ++a) {
+    const int i = threadIdx.x + a * 256;
+    if (i >= nvec) continue;
+    float4* dst = reinterpret_cast<float4*>(dw_part + static_cast<size_t>(chunk) * d + i * 8);
+    dst[0] = make_float4(dw_acc[a][0], dw_acc[a][1], dw_acc[a][2], dw_acc[a][3]);
+    dst[1] = make_float4(dw_acc[a][4], dw_acc[a][5], dw_acc[a][6], dw_acc[a][7]);
   }
 }
 
@@ -315,9 +382,17 @@ int ka_rmsnorm_bwd(const void* x, const void* w, const void* dy, void* dx, void*
   if (d % 8 != 0 || d > 8192) return -1;
   const int chunks = (rows + kRmsChunk - 1) / kRmsChunk;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  rmsnorm_bwd_kernel<<<chunks, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
-                                             static_cast<const __nv_bfloat16*>(dy), static_cast<__nv_bfloat16*>(dx),
-                                             dw_part, rows, d, eps);
+  const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(x);
+  const __nv_bfloat16* wb = static_cast<const __nv_bfloat16*>(w);
+  const __nv_bfloat16* gb = static_cast<const __nv_bfloat16*>(dy);
+  __nv_bfloat16* ob = static_cast<__nv_bfloat16*>(dx);
+  const int vpt = (d / 8 + 255) / 256;
+  if (vpt <= 1)
+    rmsnorm_bwd_kernel<1, 4><<<chunks, 256, 0, st>>>(xb, wb, gb, ob, dw_part, rows, d, eps);
+  else if (vpt == 2)
+    rmsnorm_bwd_kernel<2, 2><<<chunks, 256, 0, st>>>(xb, wb, gb, ob, dw_part, rows, d, eps);
+  else
+    rmsnorm_bwd_kernel<4, 1><<<chunks, 256, 0, st>>>(xb, wb, gb, ob, dw_part, rows, d, eps);
   rmsnorm_dw_kernel<<<(d + 255) / 256, 256, 0, st>>>(dw_part, static_cast<__nv_bfloat16*>(dw), chunks, d);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }

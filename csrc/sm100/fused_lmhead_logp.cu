@@ -856,7 +856,7 @@ struct FwdArgs {
   int k, v_global, v_local, vocab_offset, world, rank;
   unsigned epoch_base;
   float scale;
-  int panel_rows, sharded, out_all, cta_group, num_sms;
+  int panel_rows, sharded, out_all, cta_group, cg_pref, num_sms;
   unsigned long long timeout_ns;
   cudaStream_t stream;
 };
@@ -927,8 +927,8 @@ int forward_impl(const FwdArgs& a) {
   p.scale = a.scale;
   p.timeout_ns = a.timeout_ns;
   // Sub-slices that run side by side (cg) x row tiles that run side by side (mg) ~ CTA pairs.
-  // KA_LOGP_CG overrides the default split for tuning.
-  int cg_pref = 8;
+  // The caller's preference (0: the default of 8), which KA_LOGP_CG overrides for tuning.
+  int cg_pref = a.cg_pref >= 1 && a.cg_pref <= 64 ? a.cg_pref : 8;
   if (const char* e = getenv("KA_LOGP_CG")) {
     const int v = atoi(e);
     if (v >= 1 && v <= 64) cg_pref = v;
@@ -1039,7 +1039,18 @@ int ka_lmhead_logp_forward(const void* hidden, const void* weight, const long lo
                            unsigned long long timeout_ns, void* stream_ptr) {
   ka::FwdArgs a = {hidden, weight, ids, logp, lse, workspace, workspace_bytes, peer_exchange, nullptr,
                    m, k, v_global, v_local, vocab_offset, world, rank, epoch_base, scale, panel_rows,
-                   0, 1, cta_group, num_sms, timeout_ns, static_cast<cudaStream_t>(stream_ptr)};
+                   0, 1, cta_group, 0, num_sms, timeout_ns, static_cast<cudaStream_t>(stream_ptr)};
+  return ka::forward_impl(a);
+}
+
+int ka_lmhead_logp_forward_sched(const void* hidden, const void* weight, const long long* ids, float* logp,
+                                 float* lse, void* workspace, size_t workspace_bytes, void* const* peer_exchange,
+                                 int m, int k, int v_global, int v_local, int vocab_offset, int world, int rank,
+                                 unsigned epoch_base, float scale, int panel_rows, int cta_group, int cg_pref,
+                                 int num_sms, unsigned long long timeout_ns, void* stream_ptr) {
+  ka::FwdArgs a = {hidden, weight, ids, logp, lse, workspace, workspace_bytes, peer_exchange, nullptr,
+                   m, k, v_global, v_local, vocab_offset, world, rank, epoch_base, scale, panel_rows,
+                   0, 1, cta_group, cg_pref, num_sms, timeout_ns, static_cast<cudaStream_t>(stream_ptr)};
   return ka::forward_impl(a);
 }
 
@@ -1048,10 +1059,11 @@ int ka_lmhead_logp_forward_sharded(const void* hidden_local, const void* weight,
                                    void* const* peer_exchange, void* const* peer_gather, int m_local, int k,
                                    int v_global, int v_local, int vocab_offset, int world, int rank,
                                    unsigned epoch_base, float scale, int panel_rows, int out_all, int cta_group,
-                                   int num_sms, unsigned long long timeout_ns, void* stream_ptr) {
+                                   int cg_pref, int num_sms, unsigned long long timeout_ns, void* stream_ptr) {
   ka::FwdArgs a = {hidden_local, weight, ids_local, logp, lse, workspace, workspace_bytes, peer_exchange,
                    peer_gather, m_local, k, v_global, v_local, vocab_offset, world, rank, epoch_base, scale,
-                   panel_rows, 1, out_all, cta_group, num_sms, timeout_ns, static_cast<cudaStream_t>(stream_ptr)};
+                   panel_rows, 1, out_all, cta_group, cg_pref, num_sms, timeout_ns,
+                   static_cast<cudaStream_t>(stream_ptr)};
   return ka::forward_impl(a);
 }
 

@@ -77,6 +77,16 @@ int ka_lmhead_logp_forward(const void* hidden, const void* weight, const long lo
                            unsigned epoch_base, float scale, int panel_rows, int cta_group, int num_sms,
                            unsigned long long timeout_ns, void* stream);
 
+// The same with an explicit schedule: `cg_pref` sub-slices of the vocabulary run side by side
+// (0: the default, 8), the CTAs that are left over them work on different row tiles. The
+// schedule changes which tiles share the L2 at a time, hence memory traffic and power, never a
+// result: every (cta_group, cg_pref) gives the same bits.
+int ka_lmhead_logp_forward_sched(const void* hidden, const void* weight, const long long* ids, float* logp,
+                                 float* lse, void* workspace, size_t workspace_bytes, void* const* peer_exchange,
+                                 int m, int k, int v_global, int v_local, int vocab_offset, int world, int rank,
+                                 unsigned epoch_base, float scale, int panel_rows, int cta_group, int cg_pref,
+                                 int num_sms, unsigned long long timeout_ns, void* stream);
+
 // Bytes of the symmetric gather arena each rank maps for its peers when the rows are sharded
 // over the ranks: two generations of panel_rows x k bf16 rows and of panel_rows ids, the block
 // flags and the push counters. Must be zero-initialised once.
@@ -96,5 +106,5 @@ int ka_lmhead_logp_forward_sharded(const void* hidden_local, const void* weight,
                                    void* const* peer_exchange, void* const* peer_gather, int m_local, int k,
                                    int v_global, int v_local, int vocab_offset, int world, int rank,
                                    unsigned epoch_base, float scale, int panel_rows, int out_all, int cta_group,
-                                   int num_sms, unsigned long long timeout_ns, void* stream);
+                                   int cg_pref, int num_sms, unsigned long long timeout_ns, void* stream);
 }

@@ -199,29 +199,14 @@ class LlamaModel(nn.Module):
 
     def token_logp(self, input_ids: torch.Tensor, targets: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
         """Log-probability of ``targets [B, L]`` given ``input_ids [B, L]`` (fp32 ``[B, L]``, with
-        autograd), on every rank of the tensor-parallel group: the hidden states are gathered
-        over the sequence shards and the LM head runs vocabulary parallel, its (max, sum-exp,
-        target) exchange inside the kernel on CUDA and over the CPU backend otherwise."""
-        from ..ops.fused_logp import VocabParallel, lmhead_logp
+        autograd), on every rank of the tensor-parallel group. The layers leave every rank with
+        its token rows of the hidden states; the LM head runs vocabulary parallel on them, the
+        fused kernel gathering the other ranks' rows over NVLink while it works on its own and
+        exchanging the (max, sum-exp, target) triples (over the CPU backend for CPU tensors)."""
+        from ..ops.fused_logp import lmhead_logp, sharded_token_logp
 
         tokens = input_ids.numel()
         h = self.hidden_states(input_ids)
         if self.tp.world == 1:
             return lmhead_logp(h[:tokens], self.lm_head, targets.reshape(-1), scale=scale).view(targets.shape)
-        full = self.gather_rows(h, tokens)
-        if full.device.type == "cuda":
-            from ..parallel.peer import vocab_parallel_group
-
-            vp = vocab_parallel_group(self.cfg.vocab_size, group=self.tp.group)
-        else:
-            vp = VocabParallel(rank=self.tp.rank, world=self.tp.world, process_group=self.tp.group)
-        return lmhead_logp(full, self.lm_head, targets.reshape(-1), vocab=self.cfg.vocab_size, group=vp,
-                           scale=scale).view(targets.shape)
-
-    def gather_rows(self, x_local: torch.Tensor, tokens: int) -> torch.Tensor:
-        """All ranks' rows ``[tokens, hidden]`` (differentiable)."""
-        if self.tp.world == 1:
-            return x_local[:tokens]
-        from .dist_autograd import all_gather_rows
-
-        return all_gather_rows(x_local, self.tp)[:tokens]
+        return sharded_token_logp(h, self.lm_head, targets, self.cfg.vocab_size, self.tp, scale)

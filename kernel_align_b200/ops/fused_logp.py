@@ -93,6 +93,64 @@ def check_status(ws_status: torch.Tensor) -> None:
         )
 
 
+# ---- schedule selection -------------------------------------------------------------------
+# The kernel has two tile variants (a CTA pair per 256-row tile, or one CTA per 128-row tile) and
+# a free parameter of its work order (how many vocabulary sub-slices run side by side). All of
+# them give the same bits; they differ in cycles and in power. The pair variant needs about 15 %
+# fewer cycles, the single-CTA variant draws less power per cycle. A B200 that runs this kernel
+# back to back sits at its power cap and clocks down, so there the second one is often faster,
+# by an amount that depends on the GPU; in a short burst at full clock the first one wins. So
+# the first large call of a shape times the candidates on the actual inputs, twice round, and
+# keeps the fastest of the second round (as cuDNN's benchmark mode does for convolutions).
+# KA_LOGP_SCHEDULE="<cta_group>,<cg>" pins a schedule; KA_LOGP_AUTOTUNE=0 keeps the default.
+_SCHEDULES = [(2, 8), (1, 4), (1, 2), (1, 3)]
+_DEFAULT_SCHEDULE = (2, 0)
+_AUTOTUNE_MIN_MACS = 2.0e12      # smaller calls take a few milliseconds at most: default schedule
+_tuned: dict = {}
+
+
+def _pinned_schedule():
+    env = os.environ.get("KA_LOGP_SCHEDULE")
+    if not env:
+        return None
+    try:
+        g, cg = (int(x) for x in env.split(","))
+    except ValueError:
+        raise ValueError('KA_LOGP_SCHEDULE must look like "2,8" or "1,4"') from None
+    if g not in (1, 2) or not 0 <= cg <= 64:
+        raise ValueError("KA_LOGP_SCHEDULE: cta_group is 1 or 2, cg between 0 and 64")
+    return g, cg
+
+
+def _choose_schedule(key, macs: float, device, launch):
+    """The schedule for this call: pinned, tuned earlier, tuned now, or the default."""
+    pinned = _pinned_schedule()
+    if pinned is not None:
+        return pinned
+    if key in _tuned:
+        return _tuned[key]
+    if macs < _AUTOTUNE_MIN_MACS or os.environ.get("KA_LOGP_AUTOTUNE", "1") == "0" or \
+            torch.cuda.is_current_stream_capturing():
+        return _DEFAULT_SCHEDULE
+    timings = {}
+    for _round in range(2):
+        for sched in _SCHEDULES:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            launch(*sched)
+            e1.record()
+            timings[sched] = (e0, e1)
+        torch.cuda.synchronize(device)
+        timings = {k: v[0].elapsed_time(v[1]) for k, v in timings.items()}
+    best = min(timings, key=timings.get)
+    _tuned[key] = best
+    from ..utils.logger import logger
+
+    logger.info_once(f"fused_lmhead_logp schedule for {key[1:]}: cta_group {best[0]}, cg {best[1]} "
+                     f"({', '.join(f'{g}/{c}: {t:.2f} ms' for (g, c), t in timings.items())})")
+    return best
+
+
 @dataclass
 class VocabParallel:
     """Description of a vocabulary-parallel group for :func:`lmhead_logp`.
@@ -130,7 +188,7 @@ def _lmhead_logp_forward(
     group: Optional[VocabParallel] = None,
     return_lse: bool = False,
     panel_rows: int = DEFAULT_PANEL_ROWS,
-    cta_group: int = 2,
+    cta_group: Optional[int] = None,
     out: Optional[torch.Tensor] = None,
     check: bool = False,
     row_sharded: bool = False,
@@ -232,37 +290,49 @@ def _lmhead_logp_forward(
     if sharded and panel_rows % (256 * world) != 0:
         raise ValueError("row-sharded input needs panel_rows to be a multiple of 256 * world")
     n_panels = -(-m // (panel_rows // world)) if sharded else -(-m // panel_rows)
-    peer_arr = None
-    if world > 1:
-        peer_arr = (ctypes.c_void_p * world)(*group.exchange_ptrs)
-        epoch = group.epoch
-        group.epoch += n_panels
-    else:
-        epoch = ws.epoch
-        ws.epoch += n_panels
+    peer_arr = (ctypes.c_void_p * world)(*group.exchange_ptrs) if world > 1 else None
+    gather_arr = (ctypes.c_void_p * world)(*group.gather_arena_ptrs(k)) if sharded else None
     props = torch.cuda.get_device_properties(hidden.device)
     stream = torch.cuda.current_stream(hidden.device).cuda_stream
-    if sharded:
-        gather_arr = (ctypes.c_void_p * world)(*group.gather_arena_ptrs(k))
-        rc = lib.ka_lmhead_logp_forward_sharded(
-            h2.data_ptr(), w.data_ptr(), ids64.data_ptr(), logp.data_ptr(),
-            lse.data_ptr() if lse is not None else None,
-            ws.buf.data_ptr(), ws.nbytes, peer_arr, gather_arr,
-            m, k, v_global, hi - lo, lo, world, rank,
-            epoch & 0xFFFFFFFF, float(scale), panel_rows, 1 if gather_output else 0, cta_group,
-            props.multi_processor_count, default_timeout_ns(), stream,
-        )
+
+    def launch(g: int, cg: int) -> None:
+        """Enqueue one forward with the given schedule (consumes the epochs of its panels)."""
+        if world > 1:
+            epoch = group.epoch
+            group.epoch += n_panels
+        else:
+            epoch = ws.epoch
+            ws.epoch += n_panels
+        if sharded:
+            rc = lib.ka_lmhead_logp_forward_sharded(
+                h2.data_ptr(), w.data_ptr(), ids64.data_ptr(), logp.data_ptr(),
+                lse.data_ptr() if lse is not None else None,
+                ws.buf.data_ptr(), ws.nbytes, peer_arr, gather_arr,
+                m, k, v_global, hi - lo, lo, world, rank,
+                epoch & 0xFFFFFFFF, float(scale), panel_rows, 1 if gather_output else 0, g, cg,
+                props.multi_processor_count, default_timeout_ns(), stream,
+            )
+        else:
+            rc = lib.ka_lmhead_logp_forward_sched(
+                h2.data_ptr(), w.data_ptr(), ids64.data_ptr(), logp.data_ptr(),
+                lse.data_ptr() if lse is not None else None,
+                ws.buf.data_ptr(), ws.nbytes, peer_arr,
+                m, k, v_global, hi - lo, lo, world, rank,
+                epoch & 0xFFFFFFFF, float(scale), panel_rows, g, cg, props.multi_processor_count,
+                default_timeout_ns(), stream,
+            )
+        if rc != 0:
+            raise RuntimeError(f"ka_lmhead_logp_forward rejected its arguments (code {rc})")
+
+    if cta_group is None:
+        # keyed and sized by quantities that are the same on every rank of a group, so that all
+        # ranks tune (a collective sequence of calls when the vocabulary is sharded) or none does
+        rows_total = m * world if sharded else m
+        key = (hidden.device.index, rows_total, k, v_global, world, sharded)
+        sched = _choose_schedule(key, float(rows_total) * k * (v_global / world), hidden.device, launch)
     else:
-        rc = lib.ka_lmhead_logp_forward(
-            h2.data_ptr(), w.data_ptr(), ids64.data_ptr(), logp.data_ptr(),
-            lse.data_ptr() if lse is not None else None,
-            ws.buf.data_ptr(), ws.nbytes, peer_arr,
-            m, k, v_global, hi - lo, lo, world, rank,
-            epoch & 0xFFFFFFFF, float(scale), panel_rows, cta_group, props.multi_processor_count,
-            default_timeout_ns(), stream,
-        )
-    if rc != 0:
-        raise RuntimeError(f"ka_lmhead_logp_forward rejected its arguments (code {rc})")
+        sched = (int(cta_group), 0)
+    launch(*sched)
     if check:
         check_status(ws.status)
     logp = logp.reshape(lead)
@@ -428,15 +498,17 @@ class _LmheadLogpShardedFn(torch.autograd.Function):
 @profiled("lmhead_logp")
 def lmhead_logp(hidden: torch.Tensor, weight: torch.Tensor, ids: torch.Tensor, *, scale: float = 1.0,
                 vocab: Optional[int] = None, group: Optional[VocabParallel] = None, return_lse: bool = False,
-                panel_rows: int = DEFAULT_PANEL_ROWS, cta_group: int = 2, out: Optional[torch.Tensor] = None,
-                check: bool = False, row_sharded: bool = False, gather_output: bool = False):
+                panel_rows: int = DEFAULT_PANEL_ROWS, cta_group: Optional[int] = None,
+                out: Optional[torch.Tensor] = None, check: bool = False, row_sharded: bool = False,
+                gather_output: bool = False):
     """Per-token log-probabilities of ``ids`` under ``softmax(scale * hidden @ weight.T)``.
 
     hidden: ``[..., K]`` bf16; weight: ``[V_local, K]`` bf16 (this rank's vocabulary shard,
     whole canonical slices, see :func:`vocab_shard_range`); ids: ``[...]`` integer, global
     ids. Ids outside ``[0, vocab)`` give 0. Returns fp32 ``[...]`` (and the log-sum-exp if
     ``return_lse``). Differentiable with respect to ``hidden`` and ``weight`` (the log-sum-exp
-    is returned detached).
+    is returned detached). ``cta_group`` (1 or 2) picks the tile variant; by default the first
+    large call of a shape times the schedules and keeps the fastest (same bits either way).
 
     ``row_sharded`` (with a vocabulary-parallel ``group``): ``hidden`` and ``ids`` are this
     rank's rows of a batch of ``world * rows`` (global row = ``rank * rows + local row``); the
@@ -459,3 +531,28 @@ def lmhead_logp(hidden: torch.Tensor, weight: torch.Tensor, ids: torch.Tensor, *
     return _lmhead_logp_forward(hidden, weight, ids, scale=scale, vocab=vocab, group=group, return_lse=return_lse,
                                 panel_rows=panel_rows, cta_group=cta_group, out=out, check=check,
                                 row_sharded=sharded, gather_output=gather_output)
+
+
+def sharded_token_logp(h_local: torch.Tensor, lm_head: torch.Tensor, targets: torch.Tensor, vocab: int, tp,
+                       scale: float = 1.0) -> torch.Tensor:
+    """Log-probabilities of ``targets`` (any shape, ``tokens`` entries, the same on every rank)
+    from the sequence-sharded final hidden states of a tensor-parallel model: rank ``r`` holds
+    rows ``[r * rows, (r + 1) * rows)`` of the flattened tokens (trailing rows are padding) and a
+    vocabulary shard of the LM head. The rows are gathered inside the fused kernel; every rank
+    gets the full result, shaped like ``targets``. Differentiable."""
+    tokens = targets.numel()
+    rows = h_local.shape[0]
+    flat = targets.reshape(-1)
+    lo, hi = min(tokens, tp.rank * rows), min(tokens, (tp.rank + 1) * rows)
+    ids_local = flat[lo:hi]
+    if hi - lo < rows:
+        ids_local = torch.cat([ids_local, ids_local.new_full((rows - (hi - lo),), -100)])
+    if h_local.device.type == "cuda":
+        from ..parallel.peer import vocab_parallel_group
+
+        vp = vocab_parallel_group(vocab, group=tp.group)
+    else:
+        vp = VocabParallel(rank=tp.rank, world=tp.world, process_group=tp.group)
+    full = lmhead_logp(h_local, lm_head, ids_local, vocab=vocab, group=vp, scale=scale, row_sharded=True,
+                       gather_output=True)
+    return full[:tokens].view(targets.shape)

@@ -134,6 +134,16 @@ def check_device_status(device=None) -> None:
         raise CollectiveTimeout("a device-side wait gave up: " + detail)
 
 
+def reset_after_timeout() -> None:
+    """After :class:`CollectiveTimeout`: clear all peer arenas and status blocks so that the
+    step can be repeated. Collective over the default group (see ``peer.reset_all_arenas``)."""
+    from .peer import reset_all_arenas
+
+    reset_all_arenas()
+    for v in list(_live_vectors):
+        v.status.zero_()
+
+
 _scratch: dict = {}
 _SMALL_SCRATCH = 1 << 20      # elements of the scratch that serves small tensors
 

@@ -9,6 +9,7 @@ only use plain peer loads/stores on these addresses.
 from __future__ import annotations
 
 import os
+import weakref
 from typing import Optional
 
 import torch
@@ -18,6 +19,21 @@ import torch.distributed as dist
 # which in-switch reduction does not give), so the arenas are not bound to an NVLink multicast
 # object: a binding nobody uses only widens what a dying rank can disturb on its peers.
 os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+
+
+_live_arenas: "weakref.WeakSet" = weakref.WeakSet()
+
+
+def reset_all_arenas() -> None:
+    """Clear every peer arena of this process (flags, exchange and gather buffers) after a
+    device-side wait gave up and left them half written. Collective over the default group:
+    every rank of the job calls it, with no kernel in flight."""
+    torch.cuda.synchronize()
+    dist.barrier()
+    for arena in list(_live_arenas):
+        arena.buf.zero_()
+    torch.cuda.synchronize()
+    dist.barrier()
 
 
 class PeerArena:
@@ -37,6 +53,7 @@ class PeerArena:
         torch.cuda.synchronize(self.device)
         dist.barrier(self.group)
         self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        _live_arenas.add(self)
 
     def zero(self) -> None:
         """Collectively clear the arena (after an aborted launch left flags half-written)."""

@@ -93,23 +93,13 @@ class PipelineStage(nn.Module):
     def token_logp(self, x_local: torch.Tensor, targets: torch.Tensor, scale: float) -> torch.Tensor:
         """Last stage: final norm and the LM head (vocabulary parallel over the tensor-parallel
         group) on this stage's output rows."""
-        from ..ops.fused_logp import VocabParallel
+        from ..ops.fused_logp import sharded_token_logp
 
         tokens = targets.numel()
         h = rmsnorm_fn(x_local, self.norm, self.cfg.rms_eps)
         if self.tp.world == 1:
             return lmhead_logp(h[:tokens], self.lm_head, targets.reshape(-1), scale=scale).view(targets.shape)
-        from ..models.dist_autograd import all_gather_rows
-
-        full = all_gather_rows(h, self.tp)[:tokens]
-        if full.device.type == "cuda":
-            from .peer import vocab_parallel_group
-
-            vp = vocab_parallel_group(self.cfg.vocab_size, group=self.tp.group)
-        else:
-            vp = VocabParallel(rank=self.tp.rank, world=self.tp.world, process_group=self.tp.group)
-        return lmhead_logp(full, self.lm_head, targets.reshape(-1), vocab=self.cfg.vocab_size, group=vp,
-                           scale=scale).view(targets.shape)
+        return sharded_token_logp(h, self.lm_head, targets, self.cfg.vocab_size, self.tp, scale)
 
     def replicated_parameters(self) -> list:
         out = [self.embed] if self.first else []

@@ -58,6 +58,26 @@ def test_fused_logp_bitwise_batch_invariant_and_repeatable(cuda_device):
     assert torch.equal(fused_logp.lmhead_logp(h, w, ids, cta_group=1, check=True), full)
 
 
+def test_fused_logp_every_schedule_gives_the_same_bits_and_autotune_picks_one(cuda_device, monkeypatch):
+    """The tile variant and the work order change cycles and power, never a result. The first
+    large call of a shape times the candidates; here the size limit is lowered so that a small
+    case goes through the same code."""
+    h, w, ids = _inputs(cuda_device, 3000, 512, 30000, seed=4)
+    want, want_lse = fused_logp.lmhead_logp(h, w, ids, cta_group=2, return_lse=True, check=True)
+    for sched in ("2,8", "2,3", "1,4", "1,2", "1,3", "1,1"):
+        monkeypatch.setenv("KA_LOGP_SCHEDULE", sched)
+        out, lse = fused_logp.lmhead_logp(h, w, ids, return_lse=True, check=True)
+        assert torch.equal(out, want) and torch.equal(lse, want_lse), sched
+    monkeypatch.delenv("KA_LOGP_SCHEDULE")
+    monkeypatch.setattr(fused_logp, "_AUTOTUNE_MIN_MACS", 0.0)
+    fused_logp._tuned.clear()
+    out = fused_logp.lmhead_logp(h, w, ids, check=True)
+    assert torch.equal(out, want)
+    assert len(fused_logp._tuned) == 1 and next(iter(fused_logp._tuned.values())) in fused_logp._SCHEDULES
+    assert torch.equal(fused_logp.lmhead_logp(h, w, ids, check=True), want)      # the tuned schedule, reused
+    fused_logp._tuned.clear()
+
+
 def test_fused_logp_ignored_ids_and_3d(cuda_device):
     h, w, ids = _inputs(cuda_device, 4 * 64, 256, 1024, seed=2)
     ids = ids.clone()

@@ -62,3 +62,14 @@ def test_tp_decoder_layer_bitwise_equals_single_gpu(world):
         pytest.skip(f"needs {world} GPUs")
     res = _run_worker("tp_layer_worker.py", world)
     assert res["all_ranks_ok"], res
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_model_parallel_layouts_on_gpus(world):
+    """Tensor-parallel token_logp / generation, pipeline, ZeRO-1 and the late-peer path on two
+    GPUs; DP x TP policy update on four (tests/workers/model_parallel_worker.py)."""
+    if world not in _world_sizes():
+        pytest.skip(f"needs {world} GPUs")
+    # no in-switch reduction anywhere in these runs: one of them makes a rank late on purpose
+    res = _run_worker("model_parallel_worker.py", world, timeout=900, extra_env={"NCCL_NVLS_ENABLE": "0"})
+    assert res["all_ranks_ok"], res

@@ -32,16 +32,19 @@ def main():
     res = {}
     tiny = LlamaConfig(vocab_size=2048, hidden=1024, n_layers=2, n_heads=16, n_kv_heads=8, head_dim=128, ffn=4096,
                        max_pos=1024)
-    cases = {"tiny": (tiny, [(1, 256), (8, 256)]), "llama8b": (LlamaConfig.llama3_8b(), [(1, 512), (8, 512)])}
+    cases = {"tiny": (tiny, [(1, 256), (8, 256)]), "llama8b": (LlamaConfig.llama3_8b(), [(1, 512), (8, 512), (64, 512)])}
     for name, (cfg, shapes) in cases.items():
         layer_tp = DecoderLayer(cfg, tp, seed=5, device=dev)
         layer_1 = DecoderLayer(cfg, solo, seed=5, device=dev)
         cos, sin = rope_tables(cfg.max_pos, cfg.head_dim, cfg.rope_theta, device=dev)
+        first_seq = None      # the single-GPU output rows of sequence 0 at the first batch size
+        g = torch.Generator(device=dev).manual_seed(11)
+        max_tokens = max(b * l for b, l in shapes)
+        x_all = torch.randn(max_tokens, cfg.hidden, device=dev, generator=g).to(torch.bfloat16)
+        dy_all = torch.randn(max_tokens, cfg.hidden, device=dev, generator=g).to(torch.bfloat16)
         for batch, seq_len in shapes:
             tokens = batch * seq_len
-            g = torch.Generator(device=dev).manual_seed(11)
-            x = torch.randn(tokens, cfg.hidden, device=dev, generator=g).to(torch.bfloat16)
-            dy = torch.randn(tokens, cfg.hidden, device=dev, generator=g).to(torch.bfloat16)
+            x, dy = x_all[:tokens].clone(), dy_all[:tokens].clone()     # every batch starts with the same rows
             pos = torch.arange(seq_len, device=dev).repeat(batch)
             # TP = 1
             x1 = x.clone().requires_grad_()
@@ -63,6 +66,13 @@ def main():
             yl.backward(dyl)
             key = f"{name}_b{batch}"
             res[key + "_fwd"] = bool(torch.equal(yl[: hi - lo], y1.detach()[lo:hi]))
+            # per-row equality across batch sizes: sequence 0 is the same input in every batch and
+            # must give the same output rows
+            # (with the line above: for every tensor-parallel degree as well)
+            if first_seq is None:
+                first_seq = y1.detach()[:seq_len].clone()
+            else:
+                res[key + "_rows_equal_across_batch"] = bool(torch.equal(y1.detach()[:seq_len], first_seq))
 
             def close(a, b):
                 if a.numel() == 0:

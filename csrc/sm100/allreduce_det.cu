@@ -28,6 +28,7 @@ struct ArParams {
   int world, rank;
   int is_bf16;
   unsigned epoch;
+  unsigned* epoch_dev;   // or null: [0] epoch of the last call on this vector, [1] CTAs that are done
   int* status;
   unsigned long long timeout_ns;
 };
@@ -45,6 +46,20 @@ __device__ __forceinline__ float4 tree8(const float4 (&s)[8], int world) {
   return add4(add4(add4(s[0], s[1]), add4(s[2], s[3])), add4(add4(s[4], s[5]), add4(s[6], s[7])));
 }
 
+// Device-side epoch: the last CTA of the grid to get here stores the epoch this call used.
+__device__ __forceinline__ void finish_epoch(const ArParams& p, unsigned epoch) {
+  if (p.epoch_dev == nullptr) return;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned prev = atomicAdd(p.epoch_dev + 1, 1u);
+    if (prev + 1u == gridDim.x) {
+      p.epoch_dev[1] = 0u;
+      __threadfence();
+      p.epoch_dev[0] = epoch;
+    }
+  }
+}
+
 __global__ void __launch_bounds__(kThreads)
 allreduce_det_kernel(const __grid_constant__ ArParams p) {
   __shared__ int abort_flag;
@@ -53,14 +68,21 @@ allreduce_det_kernel(const __grid_constant__ ArParams p) {
   __syncthreads();
   WaitCtx wctx{&abort_flag, p.status, p.timeout_ns};
   const int grid = gridDim.x, cta = blockIdx.x;
+  // The epoch is a launch argument, or (so that a captured graph can replay the launch) one more
+  // than the word the previous call left in device memory. Every CTA reads that word before it
+  // counts itself done, and only the last CTA to be done advances it.
+  const unsigned epoch = p.epoch_dev ? __ldcg(p.epoch_dev) + 1u : p.epoch;
 
   // ---- start handshake: every rank's kernel has begun, so every input is final
   if (tid < p.world) {
-    st_release_sys_u32(p.flags[tid] + (0 * p.world + p.rank) * grid + cta, p.epoch);
-    flag_wait_bounded(p.flags[p.rank] + (0 * p.world + tid) * grid + cta, p.epoch, wctx, 21, tid);
+    st_release_sys_u32(p.flags[tid] + (0 * p.world + p.rank) * grid + cta, epoch);
+    flag_wait_bounded(p.flags[p.rank] + (0 * p.world + tid) * grid + cta, epoch, wctx, 21, tid);
   }
   __syncthreads();
-  if (abort_flag) return;
+  if (abort_flag) {
+    finish_epoch(p, epoch);
+    return;
+  }
 
   const long long slice = p.n / p.world;
   const long long begin = slice * p.rank;
@@ -105,9 +127,10 @@ allreduce_det_kernel(const __grid_constant__ ArParams p) {
   __threadfence_system();
   __syncthreads();
   if (tid < p.world) {
-    st_release_sys_u32(p.flags[tid] + (1 * p.world + p.rank) * grid + cta, p.epoch);
-    flag_wait_bounded(p.flags[p.rank] + (1 * p.world + tid) * grid + cta, p.epoch, wctx, 22, tid);
+    st_release_sys_u32(p.flags[tid] + (1 * p.world + p.rank) * grid + cta, epoch);
+    flag_wait_bounded(p.flags[p.rank] + (1 * p.world + tid) * grid + cta, epoch, wctx, 22, tid);
   }
+  finish_epoch(p, epoch);
 }
 
 }  // namespace
@@ -124,8 +147,22 @@ size_t ka_allreduce_flag_bytes(int world, int num_sms) {
 
 // bufs[r] / flags[r]: rank r's vector and flag block as mapped in this process. n elements,
 // a multiple of world * 4. epoch must grow by one per call on these buffers.
+int ka_allreduce_det_ex(void* const* bufs, void* const* flags, long long n, int is_bf16, int world, int rank,
+                        unsigned epoch, unsigned* epoch_dev, int* status, int num_sms, unsigned long long timeout_ns,
+                        void* stream);
+
 int ka_allreduce_det(void* const* bufs, void* const* flags, long long n, int is_bf16, int world, int rank,
                      unsigned epoch, int* status, int num_sms, unsigned long long timeout_ns, void* stream) {
+  return ka_allreduce_det_ex(bufs, flags, n, is_bf16, world, rank, epoch, nullptr, status, num_sms, timeout_ns, stream);
+}
+
+// The same with an optional device-side epoch: `epoch_dev` points to two zero-initialised words
+// of this rank's memory that belong to the vector; the kernel then uses *epoch_dev + 1 and stores
+// it back when it is done, so the launch can be captured in a CUDA graph and replayed. `epoch`
+// is ignored in that case. All ranks must use the same mode for a vector.
+int ka_allreduce_det_ex(void* const* bufs, void* const* flags, long long n, int is_bf16, int world, int rank,
+                        unsigned epoch, unsigned* epoch_dev, int* status, int num_sms, unsigned long long timeout_ns,
+                        void* stream) {
   using namespace ka;
   if (!(world == 1 || world == 2 || world == 4 || world == 8) || rank < 0 || rank >= world) return -50;
   if (n % (static_cast<long long>(world) * 4) != 0) return -51;
@@ -140,9 +177,16 @@ int ka_allreduce_det(void* const* bufs, void* const* flags, long long n, int is_
   p.rank = rank;
   p.is_bf16 = is_bf16;
   p.epoch = epoch;
+  p.epoch_dev = epoch_dev;
   p.status = status;
   p.timeout_ns = timeout_ns;
-  allreduce_det_kernel<<<ka_allreduce_grid(num_sms), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  // a short vector does not need the whole grid: fewer CTAs, fewer handshakes (the flag index
+  // depends on the grid size, which every rank derives from the same n)
+  int grid = ka_allreduce_grid(num_sms);
+  const long long vec_per_rank = n / world / 4;
+  const long long want = (vec_per_rank + kThreads - 1) / kThreads;
+  if (want < grid) grid = want < 1 ? 1 : static_cast<int>(want);
+  allreduce_det_kernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

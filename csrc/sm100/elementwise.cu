@@ -108,6 +108,38 @@ rope_kernel(__nv_bfloat16* __restrict__ x, long long token_stride, const long lo
   }
 }
 
+// The same rotation with 16-byte accesses: a thread takes eight consecutive pairs (j .. j + 7 and
+// their partners in the second half). hd / 2 must be a multiple of 8, rows 16-byte aligned.
+__global__ void __launch_bounds__(256)
+rope_vec8_kernel(__nv_bfloat16* __restrict__ x, long long token_stride, const long long* __restrict__ positions,
+                 const float* __restrict__ cos_t, const float* __restrict__ sin_t, int tokens, int heads, int hd) {
+  const int half = hd / 2, groups = half / 8;
+  const long long total = static_cast<long long>(tokens) * heads * groups;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int j = static_cast<int>(i % groups) * 8;
+    const long long th = i / groups;
+    const int h = static_cast<int>(th % heads);
+    const long long t = th / heads;
+    const long long pos = positions[t];
+    const float4* cp = reinterpret_cast<const float4*>(cos_t + pos * half + j);
+    const float4* sp = reinterpret_cast<const float4*>(sin_t + pos * half + j);
+    const float4 c0 = cp[0], c1 = cp[1], s0 = sp[0], s1 = sp[1];
+    const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+    __nv_bfloat16* p = x + t * token_stride + static_cast<long long>(h) * hd;
+    Bf16x8 lo = *reinterpret_cast<const Bf16x8*>(p + j), hi = *reinterpret_cast<const Bf16x8*>(p + j + half);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float a = __bfloat162float(lo.v[e]), b = __bfloat162float(hi.v[e]);
+      lo.v[e] = __float2bfloat16_rn(__fsub_rn(__fmul_rn(a, c[e]), __fmul_rn(b, sn[e])));
+      hi.v[e] = __float2bfloat16_rn(__fadd_rn(__fmul_rn(b, c[e]), __fmul_rn(a, sn[e])));
+    }
+    *reinterpret_cast<Bf16x8*>(p + j) = lo;
+    *reinterpret_cast<Bf16x8*>(p + j + half) = hi;
+  }
+}
+
 __device__ __forceinline__ float tanh_approx(float x) {
   float y;
   asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -342,6 +374,12 @@ int ka_rope(void* x, long long token_stride, const long long* positions, const f
   using namespace ka;
   if (tokens <= 0) return 0;
   if (hd % 2 != 0) return -1;
+  if ((hd / 2) % 8 == 0 && token_stride % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0) {
+    const long long groups = static_cast<long long>(tokens) * heads * (hd / 16);
+    rope_vec8_kernel<<<grid_for(groups, 256, num_sms), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<__nv_bfloat16*>(x), token_stride, positions, cos_t, sin_t, tokens, heads, hd);
+    return cudaGetLastError() == cudaSuccess ? 0 : -11;
+  }
   const long long total = static_cast<long long>(tokens) * heads * (hd / 2);
   rope_kernel<<<grid_for(total, 256, num_sms), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<__nv_bfloat16*>(x), token_stride, positions, cos_t, sin_t, tokens, heads, hd);

@@ -23,7 +23,7 @@ import torch
 
 from ..kernels.sampling import SamplerBackend
 from ..ops.attention import attention
-from ..ops.decode import attention_decode
+from ..ops.decode import attention_decode, decode_qkv_rope_cache
 from ..ops.gemm import gemm_bi
 from ..ops.layer_ops import rmsnorm, rope_, swiglu
 from ..ops.logits_logp import logits_logp
@@ -88,25 +88,25 @@ def _full_logits(model, h: torch.Tensor) -> torch.Tensor:
 
 
 @torch.no_grad()
-def _layer_decode(layer, x, batch, pos_t, cos, sin, cache_k, cache_v, lens_t, slot_t):
+def _layer_decode(layer, x, delta, batch, pos_t, cos, sin, cache_k, cache_v, lens_t, slot_t):
     """One decoder layer on one new token per sequence, with every step-dependent quantity in
     a device tensor (``pos_t [B]`` int64 position, ``lens_t [B]`` int32 keys to attend to,
-    ``slot_t [1]`` int64 cache slot), so the same launches can be replayed from a graph."""
+    ``slot_t [1]`` int64 cache slot), so the same launches can be replayed from a graph.
+
+    ``x`` is the residual stream and ``delta`` the previous block's output that has not been
+    added to it yet (``None`` for the first layer): each residual add runs inside the RMSNorm
+    kernel that follows it. Nine launches: norm, qkv GEMM, split + RoPE + cache write, attention,
+    output GEMM, add + norm, gate / up GEMM, SwiGLU, down GEMM. Returns ``(x, delta)``."""
     cfg = layer.cfg
-    hd, hq, hkv = cfg.head_dim, layer.hq, layer.hkv
-    h = rmsnorm(x, layer.norm1, cfg.rms_eps)
+    if delta is None:
+        h = rmsnorm(x, layer.norm1, cfg.rms_eps)
+    else:
+        h, x = rmsnorm(delta, layer.norm1, cfg.rms_eps, residual=x)
     qkv = gemm_bi(h, layer.wqkv)
-    q = qkv[:, : hq * hd].reshape(batch, hq, hd).contiguous()
-    k = qkv[:, hq * hd:(hq + hkv) * hd].reshape(batch, hkv, hd).contiguous()
-    v = qkv[:, (hq + hkv) * hd:].reshape(batch, 1, hkv, hd)
-    rope_(q, pos_t, cos, sin)
-    rope_(k, pos_t, cos, sin)
-    cache_k.index_copy_(1, slot_t, k.view(batch, 1, hkv, hd))
-    cache_v.index_copy_(1, slot_t, v)
-    a = attention_decode(q, cache_k, cache_v, lens_t).reshape(batch, hq * hd)
-    x = x + gemm_bi(a, layer.wo)
-    h = rmsnorm(x, layer.norm2, cfg.rms_eps)
-    return x + gemm_bi(swiglu(gemm_bi(h, layer.wgu)), layer.wdown)
+    q = decode_qkv_rope_cache(qkv, pos_t, slot_t, cos, sin, cache_k, cache_v, layer.hq, layer.hkv)
+    a = attention_decode(q, cache_k, cache_v, lens_t).reshape(batch, layer.hq * cfg.head_dim)
+    h, x = rmsnorm(gemm_bi(a, layer.wo), layer.norm2, cfg.rms_eps, residual=x)
+    return x, gemm_bi(swiglu(gemm_bi(h, layer.wgu)), layer.wdown)
 
 
 class _DecodeGraph:
@@ -126,9 +126,12 @@ class _DecodeGraph:
     def _body(self):
         m = self.model
         x = torch.nn.functional.embedding(self.tok, m.embed)
+        delta = None
         for layer, (ck, cv) in zip(m.layers, self.caches):
-            x = _layer_decode(layer, x, self.batch, self.pos, m.rope_cos, m.rope_sin, ck, cv, self.lens, self.slot)
-        logits = gemm_bi(rmsnorm(x, m.norm, m.cfg.rms_eps), m.lm_head)
+            x, delta = _layer_decode(layer, x, delta, self.batch, self.pos, m.rope_cos, m.rope_sin, ck, cv, self.lens,
+                                     self.slot)
+        h = rmsnorm(x, m.norm, m.cfg.rms_eps) if delta is None else rmsnorm(delta, m.norm, m.cfg.rms_eps, residual=x)[0]
+        logits = gemm_bi(h, m.lm_head)
         self.pos += 1
         self.lens += 1
         self.slot += 1
@@ -145,9 +148,13 @@ class _DecodeGraph:
         try:
             with torch.cuda.graph(g):
                 self.logits = self._body()
-        except RuntimeError:
+        except RuntimeError as e:
             # something on this path cannot be captured: stay eager (state tensors untouched,
-            # a capture records launches without running them)
+            # a capture records launches without running them), and say so: an eager decode
+            # step is two to three times slower
+            from ..utils.logger import logger
+
+            logger.warn_once(f"decode step could not be captured in a CUDA graph, running eagerly: {str(e)[:200]}")
             self.graph = None
             return self._body()
         self.graph = g

@@ -41,6 +41,43 @@ def attention_decode(q: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.Tens
     return out
 
 
+@profiled("decode_qkv_rope_cache")
+def decode_qkv_rope_cache(qkv: torch.Tensor, pos: torch.Tensor, slot: torch.Tensor, cos: torch.Tensor,
+                          sin: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.Tensor, hq: int,
+                          hkv: int) -> torch.Tensor:
+    """The step between the fused qkv projection and attention of a decode step, in one launch:
+    ``qkv [B, (hq + 2 hkv) * D]`` is split, q and k are rotated at ``pos [B]`` (int64), k and v
+    are written into cache row ``slot [1]`` (int64) of ``cache_k / cache_v [B, T, hkv, D]``.
+    Returns the rotated ``q [B, hq, D]``. Position and slot are device tensors, so a CUDA graph
+    can replay the launch. The same bits as ``rope_`` followed by ``index_copy_``."""
+    b = qkv.shape[0]
+    d = cache_k.shape[-1]
+    if qkv.device.type != "cuda" or d != 128:
+        from .layer_ops import rope_
+
+        q = qkv[:, : hq * d].reshape(b, hq, d).contiguous()
+        k = qkv[:, hq * d:(hq + hkv) * d].reshape(b, hkv, d).contiguous()
+        v = qkv[:, (hq + hkv) * d:].reshape(b, 1, hkv, d)
+        rope_(q, pos, cos, sin)
+        rope_(k, pos, cos, sin)
+        cache_k.index_copy_(1, slot, k.view(b, 1, hkv, d))
+        cache_v.index_copy_(1, slot, v)
+        return q
+    if qkv.stride(1) != 1 or not cache_k.is_contiguous() or not cache_v.is_contiguous():
+        raise ValueError("decode_qkv_rope_cache takes a row-major qkv and contiguous caches")
+    q = torch.empty(b, hq, d, dtype=qkv.dtype, device=qkv.device)
+    fn = _native.cuda().ka_decode_qkv_rope_cache
+    fn.restype = c_int
+    fn.argtypes = [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                   c_int, c_int, c_int, c_void_p]
+    rc = fn(qkv.data_ptr(), qkv.stride(0), pos.data_ptr(), slot.data_ptr(), cos.data_ptr(), sin.data_ptr(),
+            q.data_ptr(), cache_k.data_ptr(), cache_v.data_ptr(), b, hq, hkv, cache_k.shape[1],
+            torch.cuda.current_stream(qkv.device).cuda_stream)
+    if rc != 0:
+        raise RuntimeError(f"ka_decode_qkv_rope_cache failed ({rc})")
+    return q
+
+
 class FusedAdamW:
     """AdamW over bf16 parameters with fp32 master weights and moments, one fused kernel per
     parameter tensor. Gradients may be fp32 (the deterministic all-reduce buckets) or bf16."""

@@ -385,6 +385,16 @@ def _logp_backward(hidden, weight, ids, lse, g, scale, vocab, group, need_dh, ne
 
             all_reduce_det(d_hidden, getattr(group, "process_group", None))
         return d_hidden, d_weight
+    m_real = m
+    if m % 8:
+        # the weight-gradient GEMM contracts over the rows, whose count must be a multiple of 8:
+        # pad with rows whose upstream gradient is zero (their d_logits are exactly zero)
+        pad = 8 - m % 8
+        h2 = torch.cat([h2, h2.new_zeros(pad, k)])
+        ids64 = torch.cat([ids64, ids64.new_full((pad,), -1)])
+        g32 = torch.cat([g32, g32.new_zeros(pad)])
+        lse32 = torch.cat([lse32, lse32.new_zeros(pad)])
+        m += pad
     lib = _native.cuda()
     fn = lib.ka_lmhead_logits_grad
     fn.restype = ctypes.c_int
@@ -413,6 +423,8 @@ def _logp_backward(hidden, weight, ids, lse, g, scale, vocab, group, need_dh, ne
                                  out_dtype=torch.float32 if multi else torch.bfloat16)
             d_weight = part if d_weight is None else d_weight.add_(part)
         del d_logits
+    if need_dh and m_real != m:
+        d_hidden = d_hidden[:m_real].contiguous()
     if need_dh and world > 1:
         from ..parallel.collectives import all_reduce_det
 

@@ -29,6 +29,44 @@ def test_decode_attention_matches_math(cuda_device):
     assert torch.equal(attention_decode(q[1:2], ck[1:2], cv[1:2], lens[1:2]), out[1:2])
 
 
+def test_decode_qkv_rope_cache_equals_the_separate_steps_bitwise(cuda_device):
+    from kernel_align_b200.ops.decode import decode_qkv_rope_cache
+    from kernel_align_b200.ops.layer_ops import rope_, rope_tables
+
+    b, hq, hkv, d, t = 5, 8, 2, 128, 40
+    g = torch.Generator(device=cuda_device).manual_seed(1)
+    qkv = torch.randn(b, (hq + 2 * hkv) * d, device=cuda_device, generator=g).to(torch.bfloat16)
+    pos = torch.tensor([3, 17, 0, 39, 8], device=cuda_device)
+    slot = torch.tensor([21], device=cuda_device)
+    cos, sin = rope_tables(64, d, 500000.0, device=cuda_device)
+    ck = torch.randn(b, t, hkv, d, device=cuda_device, generator=g).to(torch.bfloat16)
+    cv = torch.randn(b, t, hkv, d, device=cuda_device, generator=g).to(torch.bfloat16)
+    ck2, cv2 = ck.clone(), cv.clone()
+    q = decode_qkv_rope_cache(qkv, pos, slot, cos, sin, ck, cv, hq, hkv)
+    q_ref = qkv[:, : hq * d].reshape(b, hq, d).contiguous()
+    k_ref = qkv[:, hq * d:(hq + hkv) * d].reshape(b, hkv, d).contiguous()
+    rope_(q_ref, pos, cos, sin)
+    rope_(k_ref, pos, cos, sin)
+    ck2.index_copy_(1, slot, k_ref.view(b, 1, hkv, d))
+    cv2.index_copy_(1, slot, qkv[:, (hq + hkv) * d:].reshape(b, 1, hkv, d))
+    assert torch.equal(q, q_ref) and torch.equal(ck, ck2) and torch.equal(cv, cv2)
+
+
+def test_fused_logp_backward_with_a_row_count_that_is_not_a_multiple_of_eight(cuda_device):
+    from kernel_align_b200.ops.fused_logp import lmhead_logp
+
+    g = torch.Generator(device=cuda_device).manual_seed(2)
+    h = torch.randn(380, 256, device=cuda_device, generator=g).to(torch.bfloat16).requires_grad_()
+    w = (torch.randn(1000, 256, device=cuda_device, generator=g) * 0.05).to(torch.bfloat16).requires_grad_()
+    ids = torch.randint(0, 1000, (380,), device=cuda_device, generator=g)
+    lmhead_logp(h, w, ids).sum().backward()
+    hr, wr = h.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    torch.log_softmax(hr @ wr.t(), -1).gather(-1, ids[:, None]).sum().backward()
+    assert h.grad.shape == h.shape
+    assert (h.grad.float() - hr.grad).abs().max().item() < 0.03 * hr.grad.abs().max().item() + 1e-3
+    assert (w.grad.float() - wr.grad).abs().max().item() < 0.03 * wr.grad.abs().max().item() + 1e-3
+
+
 def test_generation_is_seeded_batch_invariant_and_consistent_with_prefill(cuda_device):
     model = _model(cuda_device)
     prompts = torch.randint(0, model.cfg.vocab_size, (3, 16), device=cuda_device,

@@ -78,6 +78,29 @@ def small_op_cases(dev, g, rows=32768, hidden=4096, groups=256, seq=512, batch=6
     opt = FusedAdamW([w], lr=1e-5)
     cases.append((f"fused AdamW {params} params", opt.step, None, params * (2 + 2 + 12 + 12 + 2)))
 
+    from kernel_align_b200.ops.layer_ops import rmsnorm_fn
+
+    xn = torch.randn(rows, hidden, device=dev, generator=g).to(torch.bfloat16).requires_grad_()
+    wn = torch.ones(hidden, device=dev, dtype=torch.bfloat16).requires_grad_()
+    dyn = torch.randn(rows, hidden, device=dev, generator=g).to(torch.bfloat16)
+    yn = rmsnorm_fn(xn, wn, 1e-5)
+
+    def norm_bwd():
+        xn.grad = None
+        wn.grad = None
+        yn.backward(dyn, retain_graph=True)
+
+    xr = xn.detach().float().requires_grad_()
+    wr = wn.detach().float().requires_grad_()
+    yr = F.rms_norm(xr, (hidden,), wr, 1e-5)
+
+    def norm_bwd_torch():
+        xr.grad = None
+        wr.grad = None
+        yr.backward(dyn.float(), retain_graph=True)
+
+    cases.append((f"rmsnorm backward {rows}x{hidden}", norm_bwd, norm_bwd_torch, rows * hidden * 2 * 3))
+
     vocab = 128256 if rows >= 4096 else 512
     m = min(rows, 8192)
     hs = torch.randn(m, hidden, device=dev, generator=g).to(torch.bfloat16).requires_grad_()

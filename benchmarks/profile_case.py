@@ -21,7 +21,8 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--op", required=True,
                     choices=["fused_logp", "logits_logp", "sampling", "rmsnorm", "swiglu", "gemm", "attention", "attention_bwd",
-                             "grpo_loss"])
+                             "grpo_loss", "rope", "adamw", "decode_attention", "gemm_skinny", "rmsnorm_bwd", "logp_bwd",
+                             "decode_qkv"])
     ap.add_argument("--rows", type=int, default=4736)
     ap.add_argument("--vocab", type=int, default=128256)
     ap.add_argument("--hidden", type=int, default=4096)
@@ -85,6 +86,91 @@ def main():
         a = torch.randn(8192, args.hidden, device=dev, generator=g).to(torch.bfloat16)
         b = (torch.randn(28672, args.hidden, device=dev, generator=g) * 0.02).to(torch.bfloat16)
         fn = lambda: gemm_bi(a, b)  # noqa: E731
+    elif args.op == "grpo_loss":
+        from kernel_align_b200.ops.grpo_loss import grpo_loss
+
+        groups, seq = max(256, args.rows // 512 * 4), 512      # [G, L] log-probs; bytes are tiny, the launch is the cost
+        new = (torch.randn(groups, seq, device=dev, generator=g) * 0.1 - 2).requires_grad_()
+        old = torch.randn(groups, seq, device=dev, generator=g) * 0.1 - 2
+        adv = torch.randn(groups, device=dev, generator=g)
+
+        def fn():
+            new.grad = None
+            loss = grpo_loss(new, old, adv)
+            loss.backward()
+            return loss
+    elif args.op == "rope":
+        from kernel_align_b200.ops.layer_ops import rope_, rope_tables
+
+        rows = max(args.rows, 32768)
+        x = torch.randn(rows, 32, 128, device=dev, generator=g).to(torch.bfloat16)     # 268 MB at 32768 rows
+        pos = torch.arange(512, device=dev).repeat(rows // 512 + 1)[:rows]
+        cos, sin = rope_tables(512, 128, 500000.0, device=dev)
+        fn = lambda: rope_(x, pos, cos, sin)  # noqa: E731
+    elif args.op == "adamw":
+        from kernel_align_b200.ops.decode import FusedAdamW
+
+        n = 1 << 27                                                                     # 2.7 GB of state and gradients
+        w = torch.nn.Parameter((torch.randn(n, device=dev, generator=g) * 0.02).to(torch.bfloat16))
+        w.grad = torch.randn(n, device=dev, generator=g).to(torch.bfloat16)
+        opt = FusedAdamW([w], lr=1e-5)
+
+        def fn():
+            opt.step()
+            return w
+    elif args.op == "decode_attention":
+        from kernel_align_b200.ops.decode import attention_decode
+
+        b_, ctx = 256, 1024                                                             # 1.07 GB of K and V
+        q = torch.randn(b_, 32, 128, device=dev, generator=g).to(torch.bfloat16)
+        ck = torch.randn(b_, ctx, 8, 128, device=dev, generator=g).to(torch.bfloat16)
+        cv = torch.randn(b_, ctx, 8, 128, device=dev, generator=g).to(torch.bfloat16)
+        lens = torch.full((b_,), ctx, dtype=torch.int32, device=dev)
+        fn = lambda: attention_decode(q, ck, cv, lens)  # noqa: E731
+    elif args.op == "decode_qkv":
+        from kernel_align_b200.ops.decode import decode_qkv_rope_cache
+        from kernel_align_b200.ops.layer_ops import rope_tables
+
+        b_, t = 64, 512
+        qkv = torch.randn(b_, 48 * 128, device=dev, generator=g).to(torch.bfloat16)
+        pos = torch.full((b_,), 100, device=dev)
+        slot = torch.tensor([100], device=dev)
+        cos, sin = rope_tables(t, 128, 500000.0, device=dev)
+        ck = torch.zeros(b_, t, 8, 128, device=dev, dtype=torch.bfloat16)
+        cv = torch.zeros_like(ck)
+        fn = lambda: decode_qkv_rope_cache(qkv, pos, slot, cos, sin, ck, cv, 32, 8)  # noqa: E731
+    elif args.op == "gemm_skinny":
+        from kernel_align_b200.ops.gemm import gemm_bi
+
+        a = torch.randn(8, args.hidden, device=dev, generator=g).to(torch.bfloat16)
+        b = (torch.randn(28672, args.hidden, device=dev, generator=g) * 0.02).to(torch.bfloat16)   # 235 MB of weights
+        fn = lambda: gemm_bi(a, b)  # noqa: E731
+    elif args.op == "rmsnorm_bwd":
+        from kernel_align_b200.ops.layer_ops import rmsnorm_fn
+
+        rows = max(args.rows, 32768)
+        x = torch.randn(rows, args.hidden, device=dev, generator=g).to(torch.bfloat16).requires_grad_()
+        w = torch.ones(args.hidden, device=dev, dtype=torch.bfloat16).requires_grad_()
+        dy = torch.randn(rows, args.hidden, device=dev, generator=g).to(torch.bfloat16)
+
+        def fn():
+            x.grad = None
+            w.grad = None
+            rmsnorm_fn(x, w, 1e-5).backward(dy)
+            return x.grad
+    elif args.op == "logp_bwd":
+        from kernel_align_b200.ops.fused_logp import lmhead_logp
+
+        rows = min(args.rows, 4096)
+        h = torch.randn(rows, args.hidden, device=dev, generator=g).to(torch.bfloat16).requires_grad_()
+        w = torch.nn.Parameter((torch.randn(args.vocab, args.hidden, device=dev, generator=g) * 0.02).to(torch.bfloat16))
+        ids = torch.randint(0, args.vocab, (rows,), device=dev, generator=g)
+
+        def fn():
+            h.grad = None
+            w.grad = None
+            lmhead_logp(h, w, ids).sum().backward()
+            return h.grad
     else:
         raise SystemExit(f"--op {args.op}: no profile case defined yet")
     for _ in range(args.launches):

@@ -209,7 +209,7 @@ swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* _
 // depend on the grid); threads own columns. kRows rows are in flight at once: their x and dy
 // vectors are loaded once into registers and serve all three steps (sum of squares, the dot
 // product, dx / dw), and the block reductions of the kRows rows share their two barriers.
-constexpr int kRmsChunk = 128;
+constexpr int kRmsChunk = 64;
 
 // Fixed-order sums of R values per thread over the CTA (8 warps): lanes by xor-shuffle, then the
 // eight warp sums left to right, the same in every thread.
@@ -411,8 +411,11 @@ int ka_swiglu_bwd(const void* gate, const void* up, long long in_stride, const v
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
+// Rows per partial sum of the weight gradient (the size of dw_part follows from it).
+int ka_rmsnorm_bwd_chunk() { return ka::kRmsChunk; }
+
 // x, dy: [rows, d] bf16; dx: [rows, d] bf16; dw: [d] bf16; dw_part: scratch of
-// ceil(rows / 128) * d floats. d % 8 == 0 and d <= 8192.
+// ceil(rows / ka_rmsnorm_bwd_chunk()) * d floats. d % 8 == 0 and d <= 8192.
 int ka_rmsnorm_bwd(const void* x, const void* w, const void* dy, void* dx, void* dw, float* dw_part, int rows, int d,
                    float eps, void* stream) {
   using namespace ka;

@@ -5,9 +5,10 @@ Each data-parallel rank generates for its own prompts. All heavy steps are the n
 GEMMs (``gemm_bi``), prefill attention, decode attention, RMSNorm, RoPE, SwiGLU, the sampler
 and the logits log-prob kernel. With a tensor-parallel model the activations stay replicated
 over the group (no sequence sharding for one token per sequence): every rank runs its heads
-and its slice of the FFN, the two row-parallel products are summed with the deterministic
-all-reduce, the LM-head shards are gathered into full logits, and every rank draws the same
-token from the same seeded stream.
+and its slice of the FFN, the two row-parallel products are written into peer-mapped memory
+and summed there by the deterministic all-reduce, the LM-head shards become full logits the
+same way (each rank fills its columns of a zeroed buffer), and every rank draws the same token
+from the same seeded stream.
 
 On CUDA the decode step (embedding -> every layer -> final norm -> LM-head logits: a few
 hundred small launches) is captured once in a CUDA graph and replayed per token; position,
@@ -87,8 +88,45 @@ def _full_logits(model, h: torch.Tensor) -> torch.Tensor:
     return torch.cat(cols, 1).contiguous()
 
 
+class _TPDecodeBuffers:
+    """Peer-mapped buffers of a tensor-parallel decode step. The two row-parallel products of a
+    layer are written straight into ``act`` and summed there in place by the deterministic
+    all-reduce; the LM-head shards are written into their columns of ``logits`` (zero elsewhere)
+    and the same all-reduce turns that into the full logits on every rank (adding zeros is exact).
+    Both vectors keep their handshake epoch on the device, so the whole step, collectives
+    included, can be captured in a CUDA graph."""
+
+    def __init__(self, model, batch: int):
+        from ..parallel.collectives import SymmetricVector
+
+        cfg, tp = model.cfg, model.tp
+        dev = model.embed.device
+        self.batch = batch
+        self.n_act, self.n_logits = batch * cfg.hidden, batch * cfg.vocab_size
+        self.act = SymmetricVector(self.n_act, torch.bfloat16, tp.group, dev, device_epoch=True)
+        self.logits = SymmetricVector(self.n_logits, torch.bfloat16, tp.group, dev, device_epoch=True)
+        self.act_view = self.act.tensor[: self.n_act].view(batch, cfg.hidden)
+        self.logits_view = self.logits.tensor[: self.n_logits].view(batch, cfg.vocab_size)
+        lo, hi = model.vocab_range
+        self.my_cols = self.logits_view[:, lo:hi]
+        self.cols_aligned = self.my_cols.data_ptr() % 16 == 0 and cfg.vocab_size % 8 == 0
+
+    def reduce_act(self) -> torch.Tensor:
+        self.act.all_reduce_(numel=self.n_act)
+        return self.act_view
+
+    def full_logits(self, h: torch.Tensor, lm_head: torch.Tensor) -> torch.Tensor:
+        self.logits.tensor.zero_()
+        if self.cols_aligned:
+            gemm_bi(h, lm_head, out=self.my_cols)
+        else:
+            self.my_cols.copy_(gemm_bi(h, lm_head))
+        self.logits.all_reduce_(numel=self.n_logits)
+        return self.logits_view
+
+
 @torch.no_grad()
-def _layer_decode(layer, x, delta, batch, pos_t, cos, sin, cache_k, cache_v, lens_t, slot_t):
+def _layer_decode(layer, x, delta, batch, pos_t, cos, sin, cache_k, cache_v, lens_t, slot_t, tpbuf=None):
     """One decoder layer on one new token per sequence, with every step-dependent quantity in
     a device tensor (``pos_t [B]`` int64 position, ``lens_t [B]`` int32 keys to attend to,
     ``slot_t [1]`` int64 cache slot), so the same launches can be replayed from a graph.
@@ -96,7 +134,9 @@ def _layer_decode(layer, x, delta, batch, pos_t, cos, sin, cache_k, cache_v, len
     ``x`` is the residual stream and ``delta`` the previous block's output that has not been
     added to it yet (``None`` for the first layer): each residual add runs inside the RMSNorm
     kernel that follows it. Nine launches: norm, qkv GEMM, split + RoPE + cache write, attention,
-    output GEMM, add + norm, gate / up GEMM, SwiGLU, down GEMM. Returns ``(x, delta)``."""
+    output GEMM, add + norm, gate / up GEMM, SwiGLU, down GEMM; with a tensor-parallel model
+    (``tpbuf``) the two row-parallel products are followed by an in-place all-reduce.
+    Returns ``(x, delta)``."""
     cfg = layer.cfg
     if delta is None:
         h = rmsnorm(x, layer.norm1, cfg.rms_eps)
@@ -105,8 +145,13 @@ def _layer_decode(layer, x, delta, batch, pos_t, cos, sin, cache_k, cache_v, len
     qkv = gemm_bi(h, layer.wqkv)
     q = decode_qkv_rope_cache(qkv, pos_t, slot_t, cos, sin, cache_k, cache_v, layer.hq, layer.hkv)
     a = attention_decode(q, cache_k, cache_v, lens_t).reshape(batch, layer.hq * cfg.head_dim)
-    h, x = rmsnorm(gemm_bi(a, layer.wo), layer.norm2, cfg.rms_eps, residual=x)
-    return x, gemm_bi(swiglu(gemm_bi(h, layer.wgu)), layer.wdown)
+    if tpbuf is None:
+        h, x = rmsnorm(gemm_bi(a, layer.wo), layer.norm2, cfg.rms_eps, residual=x)
+        return x, gemm_bi(swiglu(gemm_bi(h, layer.wgu)), layer.wdown)
+    gemm_bi(a, layer.wo, out=tpbuf.act_view)
+    h, x = rmsnorm(tpbuf.reduce_act(), layer.norm2, cfg.rms_eps, residual=x)
+    gemm_bi(swiglu(gemm_bi(h, layer.wgu)), layer.wdown, out=tpbuf.act_view)
+    return x, tpbuf.reduce_act()     # consumed by the next RMSNorm before the buffer is written again
 
 
 class _DecodeGraph:
@@ -122,6 +167,13 @@ class _DecodeGraph:
         self.slot = torch.full((1,), first_pos, dtype=torch.int64, device=dev)
         self.graph = None
         self.logits = None
+        self.tpbuf = None
+        if model.tp.world > 1:
+            # peer-mapped memory is allocated collectively: keep it with the model, per batch size
+            cache = model.__dict__.setdefault("_tp_decode_buffers", {})
+            if batch not in cache:
+                cache[batch] = _TPDecodeBuffers(model, batch)
+            self.tpbuf = cache[batch]
 
     def _body(self):
         m = self.model
@@ -129,9 +181,9 @@ class _DecodeGraph:
         delta = None
         for layer, (ck, cv) in zip(m.layers, self.caches):
             x, delta = _layer_decode(layer, x, delta, self.batch, self.pos, m.rope_cos, m.rope_sin, ck, cv, self.lens,
-                                     self.slot)
+                                     self.slot, self.tpbuf)
         h = rmsnorm(x, m.norm, m.cfg.rms_eps) if delta is None else rmsnorm(delta, m.norm, m.cfg.rms_eps, residual=x)[0]
-        logits = gemm_bi(h, m.lm_head)
+        logits = gemm_bi(h, m.lm_head) if self.tpbuf is None else self.tpbuf.full_logits(h, m.lm_head)
         self.pos += 1
         self.lens += 1
         self.slot += 1
@@ -195,10 +247,9 @@ def generate(model, prompts: torch.Tensor, sampler: Optional[SamplerBackend] = N
         x = _layer_step(layer, x, batch, lp, pos, model.rope_cos, model.rope_sin, ck, cv, 0)
     last = x.view(batch, lp, -1)[:, -1].contiguous()
     logits = _full_logits(model, rmsnorm(last, model.norm, cfg.rms_eps))           # [batch, vocab] bf16
-    # the graph path is for the unsharded model: the deterministic all-reduce of a tensor-parallel
-    # step carries a host-side epoch per call, which a replayed graph could not advance
+    # (a tensor-parallel step is captured as well: its all-reduces keep their epoch on the device)
     use_graph = cuda_graph and dev.type == "cuda" and max_new_tokens > 3
-    dec = _DecodeGraph(model, caches, batch, lp) if dev.type == "cuda" and model.tp.world == 1 else None
+    dec = _DecodeGraph(model, caches, batch, lp) if dev.type == "cuda" else None
     finished = torch.zeros(batch, dtype=torch.bool, device=dev) if eos_token_id is not None else None
     mask = torch.zeros(batch, max_new_tokens, dtype=torch.float32, device=dev) if eos_token_id is not None else None
     if eos_token_id is not None:

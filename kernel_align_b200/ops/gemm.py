@@ -20,6 +20,8 @@ from __future__ import annotations
 import os
 from ctypes import c_int, c_longlong, c_ulonglong, c_void_p
 
+from typing import Optional
+
 import torch
 
 from .. import _native
@@ -65,15 +67,26 @@ def _skinny_fn():
 
 
 @profiled("gemm_skinny")
-def gemm_skinny(a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-    """``a [M <= 64, K] @ w[N, K].T`` on the weight-streaming kernel (bf16 in, bf16 out)."""
+def _check_out(out: torch.Tensor, m: int, n: int, dtype: torch.dtype) -> None:
+    if out.shape != (m, n) or out.dtype != dtype or out.stride(1) != 1 or out.stride(0) % 8 != 0 or \
+            out.data_ptr() % 16 != 0:
+        raise ValueError(f"out must be a [{m}, {n}] {dtype} view with unit column stride, a row stride that is a "
+                         "multiple of 8 and a 16-byte aligned start")
+
+
+def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``a [M <= 64, K] @ w[N, K].T`` on the weight-streaming kernel (bf16 in, bf16 out).
+    ``out``: write into this ``[M, N]`` view (rows may be strided, e.g. a column block)."""
     m, k = a.shape
     n = w.shape[0]
     if m > SKINNY_MAX_ROWS or w.shape[1] != k:
         raise ValueError("gemm_skinny takes at most 64 rows and matching inner dimensions")
     a = a if a.stride(-1) == 1 else a.contiguous()
     w = w if w.stride(-1) == 1 else w.contiguous()
-    out = torch.empty(m, n, dtype=torch.bfloat16, device=a.device)
+    if out is None:
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=a.device)
+    else:
+        _check_out(out, m, n, torch.bfloat16)
     rc = _skinny_fn()(a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), m, n, k,
                       status_buffer(a.device).data_ptr(), default_timeout_ns(),
                       torch.cuda.current_stream(a.device).cuda_stream)
@@ -84,9 +97,10 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
 
 @profiled("gemm_bi")
 def gemm_bi(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bool = False,
-            out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+            out_dtype: torch.dtype = torch.bfloat16, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``op(a) @ op(b).T`` with ``op(a) = a.T if trans_a`` (a stored ``[K, M]``) and
-    ``op(b) = b.T if trans_b`` (b stored ``[K, N]``). 2-D bf16 inputs, row-major."""
+    ``op(b) = b.T if trans_b`` (b stored ``[K, N]``). 2-D bf16 inputs, row-major. ``out`` (CUDA):
+    write the result into this view instead of a new tensor (rows may be strided)."""
     if a.device.type != "cuda":
         # the C++ library's GEMM: every dot product in one fixed order, so a row's result does not
         # depend on the batch here either (a BLAS call may block differently for different M)
@@ -94,7 +108,11 @@ def gemm_bi(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b:
 
         af = a.float().t() if trans_a else a.float()
         bf = b.float().t() if trans_b else b.float()
-        return cpu_ops.gemm_cpu(af.contiguous(), bf.contiguous()).to(out_dtype)
+        res = cpu_ops.gemm_cpu(af.contiguous(), bf.contiguous()).to(out_dtype)
+        if out is not None:
+            out.copy_(res)
+            return out
+        return res
     if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
         raise TypeError("gemm_bi takes bf16 operands")
     a = a if a.stride(-1) == 1 else a.contiguous()
@@ -105,8 +123,11 @@ def gemm_bi(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b:
         raise ValueError(f"inner dimensions differ: {k} vs {kb}")
     if (0 < m <= SKINNY_MAX_ROWS and not trans_a and not trans_b and out_dtype == torch.bfloat16
             and os.environ.get("KA_GEMM_SKINNY", "1") != "0"):
-        return gemm_skinny(a, b)
-    out = torch.empty(m, n, dtype=out_dtype, device=a.device)
+        return gemm_skinny(a, b, out=out)
+    if out is None:
+        out = torch.empty(m, n, dtype=out_dtype, device=a.device)
+    else:
+        _check_out(out, m, n, out_dtype)
     props = torch.cuda.get_device_properties(a.device)
     rc = _fn()(a.data_ptr(), a.stride(0), int(trans_a), b.data_ptr(), b.stride(0), int(trans_b), out.data_ptr(),
                out.stride(0), int(out_dtype == torch.float32), m, n, k, status_buffer(a.device).data_ptr(),

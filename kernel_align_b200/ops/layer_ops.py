@@ -163,7 +163,8 @@ class _RMSNormFn(torch.autograd.Function):
             return dx.to(x.dtype).reshape(x.shape), dw.to(weight.dtype), None
         dx = torch.empty_like(x2)
         dw = torch.empty_like(weight)
-        part = torch.empty((rows + 127) // 128, d, dtype=torch.float32, device=x.device)
+        chunk = int(_native.cuda().ka_rmsnorm_bwd_chunk())
+        part = torch.empty((rows + chunk - 1) // chunk, d, dtype=torch.float32, device=x.device)
         fn = _native.cuda().ka_rmsnorm_bwd
         fn.restype = c_int
         fn.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p]

@@ -53,7 +53,11 @@ _live_vectors: "weakref.WeakSet" = weakref.WeakSet()
 class SymmetricVector:
     """A flat fp32 / bf16 vector in peer-mapped memory plus the flag block of the all-reduce."""
 
-    def __init__(self, numel: int, dtype: torch.dtype, group: Optional[dist.ProcessGroup] = None, device=None):
+    def __init__(self, numel: int, dtype: torch.dtype, group: Optional[dist.ProcessGroup] = None, device=None,
+                 device_epoch: bool = False):
+        """``device_epoch``: keep the call counter that the handshake flags carry in device memory
+        (the kernel advances it itself), so that ``all_reduce_`` can be captured in a CUDA graph
+        and replayed. Every rank must choose the same mode for a vector."""
         from .peer import PeerArena
 
         self.group = group if group is not None else dist.group.WORLD
@@ -75,6 +79,7 @@ class SymmetricVector:
         self.epoch = 0
         self.sms = props.multi_processor_count
         self.status = torch.zeros(8, dtype=torch.int32, device=dev)
+        self.epoch_dev = torch.zeros(2, dtype=torch.int32, device=dev) if device_epoch else None
         _live_vectors.add(self)
 
     def all_reduce_(self, stream: Optional[torch.cuda.Stream] = None, numel: Optional[int] = None) -> torch.Tensor:
@@ -83,16 +88,17 @@ class SymmetricVector:
         gran = self.world * 4
         n = self.numel if numel is None else min(self.numel, (int(numel) + gran - 1) // gran * gran)
         lib = _native.cuda()
-        fn = lib.ka_allreduce_det
+        fn = lib.ka_allreduce_det_ex
         fn.restype = c_int
-        fn.argtypes = [c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_uint, c_void_p, c_int, c_ulonglong,
-                       c_void_p]
+        fn.argtypes = [c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_uint, c_void_p, c_void_p, c_int,
+                       c_ulonglong, c_void_p]
         self.epoch += 1
         bufs = (c_void_p * self.world)(*self.arena.ptrs)
         flags = (c_void_p * self.world)(*[p + self.data_bytes for p in self.arena.ptrs])
         st = stream if stream is not None else torch.cuda.current_stream(self.tensor.device)
         rc = fn(bufs, flags, n, int(self.dtype == torch.bfloat16), self.world, self.rank,
-                self.epoch & 0xFFFFFFFF, self.status.data_ptr(), self.sms, default_timeout_ns(), st.cuda_stream)
+                self.epoch & 0xFFFFFFFF, self.epoch_dev.data_ptr() if self.epoch_dev is not None else None,
+                self.status.data_ptr(), self.sms, default_timeout_ns(), st.cuda_stream)
         if rc != 0:
             raise RuntimeError(f"ka_allreduce_det rejected its arguments (code {rc})")
         return self.tensor
@@ -142,6 +148,9 @@ def reset_after_timeout() -> None:
     reset_all_arenas()
     for v in list(_live_vectors):
         v.status.zero_()
+        if v.epoch_dev is not None:
+            v.epoch_dev.zero_()
+        v.epoch = 0
 
 
 _scratch: dict = {}

@@ -1,6 +1,7 @@
 """Multi-GPU tier: child processes under torchrun, one rank per GPU (skipped with < 2 GPUs)."""
 import json
 import os
+import signal
 import subprocess
 import sys
 
@@ -11,17 +12,25 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def _run_worker(script, nproc, timeout=600, extra_env=None):
+def _run_worker(script, nproc, timeout=300, extra_env=None):
     env = dict(os.environ)
     env.setdefault("MASTER_ADDR", "127.0.0.1")
     env.update(extra_env or {})
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", str(29500 + nproc), os.path.join(HERE, "workers", script)]
-    proc = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
-    lines = [l for l in proc.stdout.splitlines() if l.startswith("RESULT ")]
+    # a session of its own, so that a launcher that runs out of time is ended together with its ranks
+    proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, env=env,
+                            start_new_session=True)
+    try:
+        stdout, _ = proc.communicate(timeout=timeout)
+    except subprocess.TimeoutExpired:
+        os.killpg(proc.pid, signal.SIGKILL)
+        stdout, _ = proc.communicate()
+        raise AssertionError(f"worker {script} ran out of time ({timeout} s): " + stdout[-1500:]) from None
+    lines = [l for l in stdout.splitlines() if l.startswith("RESULT ")]
     if proc.returncode != 0 or not lines:
-        i = proc.stdout.find("WORKER_ERROR")
-        raise AssertionError("worker failed: " + (proc.stdout[i:i + 2500] if i >= 0 else proc.stdout[-1500:]))
+        i = stdout.find("WORKER_ERROR")
+        raise AssertionError("worker failed: " + (stdout[i:i + 2500] if i >= 0 else stdout[-1500:]))
     return json.loads(lines[-1][len("RESULT "):])
 
 
@@ -71,5 +80,5 @@ def test_model_parallel_layouts_on_gpus(world):
     if world not in _world_sizes():
         pytest.skip(f"needs {world} GPUs")
     # no in-switch reduction anywhere in these runs: one of them makes a rank late on purpose
-    res = _run_worker("model_parallel_worker.py", world, timeout=900, extra_env={"NCCL_NVLS_ENABLE": "0"})
+    res = _run_worker("model_parallel_worker.py", world, timeout=420, extra_env={"NCCL_NVLS_ENABLE": "0"})
     assert res["all_ranks_ok"], res

@@ -114,8 +114,16 @@ __device__ __forceinline__ void decode_item(const LogpParams& p, int i, Item& it
   const int h = r / (mg_sz * p.cg);
   const int cg_sz = min(p.cg, p.n_chunks - h * p.cg);
   const int r2 = r - h * mg_sz * p.cg;
-  const int m_local = r2 / cg_sz;
-  const int c_local = r2 - m_local * cg_sz;
+  // Which of the two indices runs fastest over consecutive CTAs decides which CTAs are
+  // neighbours: the sub-slices of one row tile (m_fast = 0), or the row tiles of one sub-slice.
+  int m_local, c_local;
+  if (p.m_fast) {
+    c_local = r2 / mg_sz;
+    m_local = r2 - c_local * mg_sz;
+  } else {
+    m_local = r2 / cg_sz;
+    c_local = r2 - m_local * cg_sz;
+  }
   it.m_tile = g * p.mg + m_local + p.mt_rot;
   if (it.m_tile >= p.n_mtiles) it.m_tile -= p.n_mtiles;
   // Schedule position -> (slice, sub-slice): sub-slice major, so that the sub-slices that run
@@ -420,6 +428,12 @@ fused_lmhead_logp_kernel(const __grid_constant__ CUtensorMap tm_h,
   if (warp == 4) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
+      // L2 eviction hints. The rows of H that a wave works on are read again for every tile of
+      // every sub-slice, the W tiles are streamed: 1 keeps H and lets W go first, 2 keeps H
+      // only, 3 keeps W only, 0 gives no preference.
+      const uint64_t pol_h = (p.l2_hint == 1 || p.l2_hint == 2) ? l2_policy_evict_last() : l2_policy_evict_normal();
+      const uint64_t pol_w = p.l2_hint == 1 ? l2_policy_evict_first()
+                                            : (p.l2_hint == 3 ? l2_policy_evict_last() : l2_policy_evict_normal());
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -457,15 +471,15 @@ fused_lmhead_logp_kernel(const __grid_constant__ CUtensorMap tm_h,
             const uint32_t full = smem_u32(&ctl->full[stage]);
             if constexpr (G == 1) {
               mbar_arrive_expect_tx(full, C::kTxBytes);
-              tma_load_2d(a_dst, tm_a, kb * kBK, row0, full);
-              tma_load_2d(b_dst, &tm_w, kb * kBK, n0, full);
-              tma_load_2d(b_dst + 128 * kBK * 2, &tm_w, kb * kBK, n0 + 128, full);
+              tma_load_2d_hint(a_dst, tm_a, kb * kBK, row0, full, pol_h);
+              tma_load_2d_hint(b_dst, &tm_w, kb * kBK, n0, full, pol_w);
+              tma_load_2d_hint(b_dst + 128 * kBK * 2, &tm_w, kb * kBK, n0 + 128, full, pol_w);
             } else {
               if (leader) mbar_arrive_expect_tx(full, C::kTxBytes);
               const uint32_t full_leader = mapa_u32(full, 0);
-              tma_load_2d_pair(a_dst, tm_a, kb * kBK, row0, full_leader);
-              tma_load_2d_pair(b_dst, &tm_w, kb * kBK, n0 + static_cast<int>(cta_rank) * C::kBRows,
-                               full_leader);
+              tma_load_2d_pair_hint(a_dst, tm_a, kb * kBK, row0, full_leader, pol_h);
+              tma_load_2d_pair_hint(b_dst, &tm_w, kb * kBK, n0 + static_cast<int>(cta_rank) * C::kBRows,
+                                    full_leader, pol_w);
             }
             if (++stage == C::kStages) {
               stage = 0;
@@ -856,7 +870,7 @@ struct FwdArgs {
   int k, v_global, v_local, vocab_offset, world, rank;
   unsigned epoch_base;
   float scale;
-  int panel_rows, sharded, out_all, cta_group, cg_pref, num_sms;
+  int panel_rows, sharded, out_all, cta_group, cg_pref, m_fast, l2_hint, num_sms;
   unsigned long long timeout_ns;
   cudaStream_t stream;
 };
@@ -933,6 +947,12 @@ int forward_impl(const FwdArgs& a) {
     const int v = atoi(e);
     if (v >= 1 && v <= 64) cg_pref = v;
   }
+  p.l2_hint = a.l2_hint >= 0 && a.l2_hint <= 3 ? a.l2_hint : 0;
+  if (const char* e = getenv("KA_LOGP_L2HINT")) {
+    const int v = atoi(e);
+    if (v >= 0 && v <= 3) p.l2_hint = v;
+  }
+  p.m_fast = a.m_fast ? 1 : 0;
   p.cg = p.n_chunks < cg_pref ? p.n_chunks : cg_pref;
   {
     const int pairs = a.num_sms / a.cta_group;
@@ -1039,7 +1059,7 @@ int ka_lmhead_logp_forward(const void* hidden, const void* weight, const long lo
                            unsigned long long timeout_ns, void* stream_ptr) {
   ka::FwdArgs a = {hidden, weight, ids, logp, lse, workspace, workspace_bytes, peer_exchange, nullptr,
                    m, k, v_global, v_local, vocab_offset, world, rank, epoch_base, scale, panel_rows,
-                   0, 1, cta_group, 0, num_sms, timeout_ns, static_cast<cudaStream_t>(stream_ptr)};
+                   0, 1, cta_group, 0, 0, 0, num_sms, timeout_ns, static_cast<cudaStream_t>(stream_ptr)};
   return ka::forward_impl(a);
 }
 
@@ -1047,10 +1067,12 @@ int ka_lmhead_logp_forward_sched(const void* hidden, const void* weight, const l
                                  float* lse, void* workspace, size_t workspace_bytes, void* const* peer_exchange,
                                  int m, int k, int v_global, int v_local, int vocab_offset, int world, int rank,
                                  unsigned epoch_base, float scale, int panel_rows, int cta_group, int cg_pref,
-                                 int num_sms, unsigned long long timeout_ns, void* stream_ptr) {
+                                 int m_fast, int l2_hint, int num_sms, unsigned long long timeout_ns,
+                                 void* stream_ptr) {
   ka::FwdArgs a = {hidden, weight, ids, logp, lse, workspace, workspace_bytes, peer_exchange, nullptr,
                    m, k, v_global, v_local, vocab_offset, world, rank, epoch_base, scale, panel_rows,
-                   0, 1, cta_group, cg_pref, num_sms, timeout_ns, static_cast<cudaStream_t>(stream_ptr)};
+                   0, 1, cta_group, cg_pref, m_fast, l2_hint, num_sms, timeout_ns,
+                   static_cast<cudaStream_t>(stream_ptr)};
   return ka::forward_impl(a);
 }
 
@@ -1059,10 +1081,11 @@ int ka_lmhead_logp_forward_sharded(const void* hidden_local, const void* weight,
                                    void* const* peer_exchange, void* const* peer_gather, int m_local, int k,
                                    int v_global, int v_local, int vocab_offset, int world, int rank,
                                    unsigned epoch_base, float scale, int panel_rows, int out_all, int cta_group,
-                                   int cg_pref, int num_sms, unsigned long long timeout_ns, void* stream_ptr) {
+                                   int cg_pref, int m_fast, int l2_hint, int num_sms, unsigned long long timeout_ns,
+                                   void* stream_ptr) {
   ka::FwdArgs a = {hidden_local, weight, ids_local, logp, lse, workspace, workspace_bytes, peer_exchange,
                    peer_gather, m_local, k, v_global, v_local, vocab_offset, world, rank, epoch_base, scale,
-                   panel_rows, 1, out_all, cta_group, cg_pref, num_sms, timeout_ns,
+                   panel_rows, 1, out_all, cta_group, cg_pref, m_fast, l2_hint, num_sms, timeout_ns,
                    static_cast<cudaStream_t>(stream_ptr)};
   return ka::forward_impl(a);
 }

@@ -34,6 +34,8 @@ struct LogpParams {
   float scale;           // logits are scale * <h, w>; must be > 0
   unsigned long long timeout_ns;
   int mt_rot;            // rotation of the row-tile order (row-sharded input: own rows first)
+  int l2_hint;           // L2 eviction hints of the operand loads, see the producer
+  int m_fast;            // work order inside a wave: 1 = consecutive CTAs take consecutive row tiles
 
   // ---- row-sharded input (gather != 0): rank r holds rows [r * m_local, (r + 1) * m_local) of
   // the hidden states and the ids; the kernel pushes its rows of the panel into every peer's
@@ -78,14 +80,17 @@ int ka_lmhead_logp_forward(const void* hidden, const void* weight, const long lo
                            unsigned long long timeout_ns, void* stream);
 
 // The same with an explicit schedule: `cg_pref` sub-slices of the vocabulary run side by side
-// (0: the default, 8), the CTAs that are left over them work on different row tiles. The
-// schedule changes which tiles share the L2 at a time, hence memory traffic and power, never a
-// result: every (cta_group, cg_pref) gives the same bits.
+// (0: the default, 8), the CTAs that are left over them work on different row tiles; `m_fast`
+// says whether consecutive CTAs take consecutive row tiles of one sub-slice (1) or the
+// sub-slices of one row tile (0); `l2_hint` gives the operand loads an L2 eviction priority
+// (0 none, 1 keep the hidden rows and let the weight tiles go first, 2 keep the hidden rows,
+// 3 keep the weight tiles). The schedule changes which tiles share the L2 at a time, hence
+// memory traffic and power, never a result: every combination gives the same bits.
 int ka_lmhead_logp_forward_sched(const void* hidden, const void* weight, const long long* ids, float* logp,
                                  float* lse, void* workspace, size_t workspace_bytes, void* const* peer_exchange,
                                  int m, int k, int v_global, int v_local, int vocab_offset, int world, int rank,
                                  unsigned epoch_base, float scale, int panel_rows, int cta_group, int cg_pref,
-                                 int num_sms, unsigned long long timeout_ns, void* stream);
+                                 int m_fast, int l2_hint, int num_sms, unsigned long long timeout_ns, void* stream);
 
 // Bytes of the symmetric gather arena each rank maps for its peers when the rows are sharded
 // over the ranks: two generations of panel_rows x k bf16 rows and of panel_rows ids, the block
@@ -106,5 +111,6 @@ int ka_lmhead_logp_forward_sharded(const void* hidden_local, const void* weight,
                                    void* const* peer_exchange, void* const* peer_gather, int m_local, int k,
                                    int v_global, int v_local, int vocab_offset, int world, int rank,
                                    unsigned epoch_base, float scale, int panel_rows, int out_all, int cta_group,
-                                   int cg_pref, int num_sms, unsigned long long timeout_ns, void* stream);
+                                   int cg_pref, int m_fast, int l2_hint, int num_sms, unsigned long long timeout_ns,
+                                   void* stream);
 }

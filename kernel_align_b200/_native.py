@@ -50,7 +50,7 @@ def cuda() -> ctypes.CDLL:
         c_int,
         [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p,
          c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-         c_uint, c_float, c_int, c_int, c_int, c_int, c_ulonglong, c_void_p],
+         c_uint, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_ulonglong, c_void_p],
     )
     _bind(lib, "ka_lmhead_logp_gather_bytes", c_size_t, [c_int, c_int, c_int])
     _bind(
@@ -59,7 +59,7 @@ def cuda() -> ctypes.CDLL:
         c_int,
         [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p,
          c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-         c_uint, c_float, c_int, c_int, c_int, c_int, c_int, c_ulonglong, c_void_p],
+         c_uint, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_ulonglong, c_void_p],
     )
     _bind(
         lib,

@@ -100,11 +100,13 @@ def check_status(ws_status: torch.Tensor) -> None:
 # fewer cycles, the single-CTA variant draws less power per cycle. A B200 that runs this kernel
 # back to back sits at its power cap and clocks down, so there the second one is often faster,
 # by an amount that depends on the GPU; in a short burst at full clock the first one wins. So
-# the first large call of a shape times the candidates on the actual inputs, twice round, and
-# keeps the fastest of the second round (as cuDNN's benchmark mode does for convolutions).
-# KA_LOGP_SCHEDULE="<cta_group>,<cg>" pins a schedule; KA_LOGP_AUTOTUNE=0 keeps the default.
-_SCHEDULES = [(2, 8), (1, 4), (1, 2), (1, 3)]
-_DEFAULT_SCHEDULE = (2, 0)
+# the first large call of a shape times the candidates on the actual inputs, three calls each,
+# and keeps the fastest (as cuDNN's benchmark mode does for convolutions).
+# KA_LOGP_SCHEDULE="<cta_group>,<cg>[,<m_fast>[,<l2_hint>]]" pins a schedule; KA_LOGP_AUTOTUNE=0 keeps the default.
+# (cta_group, sub-slices side by side, 1 = consecutive CTAs take consecutive row tiles,
+#  L2 eviction hint of the operand loads: 0 none, 1 keep H / stream W, 2 keep H, 3 keep W)
+_SCHEDULES = [(2, 8, 0, 0), (2, 8, 0, 2), (2, 4, 1, 0), (1, 4, 0, 1), (1, 4, 0, 0), (1, 2, 0, 3), (1, 2, 0, 0)]
+_DEFAULT_SCHEDULE = (2, 0, 0, 0)
 _AUTOTUNE_MIN_MACS = 2.0e12      # smaller calls take a few milliseconds at most: default schedule
 _tuned: dict = {}
 
@@ -114,12 +116,15 @@ def _pinned_schedule():
     if not env:
         return None
     try:
-        g, cg = (int(x) for x in env.split(","))
-    except ValueError:
-        raise ValueError('KA_LOGP_SCHEDULE must look like "2,8" or "1,4"') from None
-    if g not in (1, 2) or not 0 <= cg <= 64:
-        raise ValueError("KA_LOGP_SCHEDULE: cta_group is 1 or 2, cg between 0 and 64")
-    return g, cg
+        parts = [int(x) for x in env.split(",")]
+        g, cg = parts[0], parts[1]
+        m_fast = parts[2] if len(parts) > 2 else 0
+        hint = parts[3] if len(parts) > 3 else 0
+    except (ValueError, IndexError):
+        raise ValueError('KA_LOGP_SCHEDULE must look like "2,8", "1,4", "1,2,1" or "1,2,0,3"') from None
+    if g not in (1, 2) or not 0 <= cg <= 64 or m_fast not in (0, 1) or hint not in (0, 1, 2, 3):
+        raise ValueError("KA_LOGP_SCHEDULE: cta_group is 1 or 2, cg between 0 and 64, m_fast 0 or 1, l2_hint 0..3")
+    return g, cg, m_fast, hint
 
 
 def _choose_schedule(key, macs: float, device, launch):
@@ -132,22 +137,26 @@ def _choose_schedule(key, macs: float, device, launch):
     if macs < _AUTOTUNE_MIN_MACS or os.environ.get("KA_LOGP_AUTOTUNE", "1") == "0" or \
             torch.cuda.is_current_stream_capturing():
         return _DEFAULT_SCHEDULE
-    timings = {}
-    for _round in range(2):
-        for sched in _SCHEDULES:
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            launch(*sched)
-            e1.record()
-            timings[sched] = (e0, e1)
-        torch.cuda.synchronize(device)
-        timings = {k: v[0].elapsed_time(v[1]) for k, v in timings.items()}
+    # Each candidate runs three times back to back and the last two are timed: what decides
+    # under the power cap is the rate a schedule sustains, and the first call after a change
+    # of schedule still runs at the clock the previous one left behind.
+    events = {}
+    for sched in _SCHEDULES:
+        launch(*sched)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        launch(*sched)
+        launch(*sched)
+        e1.record()
+        events[sched] = (e0, e1)
+    torch.cuda.synchronize(device)
+    timings = {k: v[0].elapsed_time(v[1]) / 2 for k, v in events.items()}
     best = min(timings, key=timings.get)
     _tuned[key] = best
     from ..utils.logger import logger
 
-    logger.info_once(f"fused_lmhead_logp schedule for {key[1:]}: cta_group {best[0]}, cg {best[1]} "
-                     f"({', '.join(f'{g}/{c}: {t:.2f} ms' for (g, c), t in timings.items())})")
+    logger.info_once(f"fused_lmhead_logp schedule for {key[1:]}: cta_group {best[0]}, cg {best[1]}, m_fast {best[2]}, "
+                     f"l2_hint {best[3]} ({', '.join(f'{g}/{c}/{o}/{h}: {t:.2f} ms' for (g, c, o, h), t in timings.items())})")
     return best
 
 
@@ -295,7 +304,7 @@ def _lmhead_logp_forward(
     props = torch.cuda.get_device_properties(hidden.device)
     stream = torch.cuda.current_stream(hidden.device).cuda_stream
 
-    def launch(g: int, cg: int) -> None:
+    def launch(g: int, cg: int, m_fast: int = 0, hint: int = 0) -> None:
         """Enqueue one forward with the given schedule (consumes the epochs of its panels)."""
         if world > 1:
             epoch = group.epoch
@@ -309,7 +318,7 @@ def _lmhead_logp_forward(
                 lse.data_ptr() if lse is not None else None,
                 ws.buf.data_ptr(), ws.nbytes, peer_arr, gather_arr,
                 m, k, v_global, hi - lo, lo, world, rank,
-                epoch & 0xFFFFFFFF, float(scale), panel_rows, 1 if gather_output else 0, g, cg,
+                epoch & 0xFFFFFFFF, float(scale), panel_rows, 1 if gather_output else 0, g, cg, m_fast, hint,
                 props.multi_processor_count, default_timeout_ns(), stream,
             )
         else:
@@ -318,7 +327,7 @@ def _lmhead_logp_forward(
                 lse.data_ptr() if lse is not None else None,
                 ws.buf.data_ptr(), ws.nbytes, peer_arr,
                 m, k, v_global, hi - lo, lo, world, rank,
-                epoch & 0xFFFFFFFF, float(scale), panel_rows, g, cg, props.multi_processor_count,
+                epoch & 0xFFFFFFFF, float(scale), panel_rows, g, cg, m_fast, hint, props.multi_processor_count,
                 default_timeout_ns(), stream,
             )
         if rc != 0:
@@ -331,7 +340,7 @@ def _lmhead_logp_forward(
         key = (hidden.device.index, rows_total, k, v_global, world, sharded)
         sched = _choose_schedule(key, float(rows_total) * k * (v_global / world), hidden.device, launch)
     else:
-        sched = (int(cta_group), 0)
+        sched = (int(cta_group), 0, 0, 0)
     launch(*sched)
     if check:
         check_status(ws.status)

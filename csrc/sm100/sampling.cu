@@ -13,11 +13,14 @@
 // the batch size, the launch shape or the schedule, and the C++ CPU path reproduces it bit
 // for bit.
 //
-// Two kernels:
+// Three kernels:
 //   sample_topk_kernel     top_k in [1, 1024] (greedy = top_k 1), optional top_p
+//   sample_topk_cluster_kernel  the same for 16-bit logits and few rows: a cluster of 2 or 4
+//                          CTAs per row, candidates exchanged through distributed shared memory
 //   sample_general_kernel  no top_k (or k > 1024), optional top_p: threshold search by radix
 //                          descent on (count, mass) histograms
 #include <cstdint>
+#include <cstdlib>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -207,6 +210,98 @@ __device__ __forceinline__ T from_bits16(uint32_t h) {
   return *reinterpret_cast<const T*>(&us);
 }
 
+// Second half of the top-k path, shared by the one-CTA and the cluster kernel: n_cand candidates
+// sit in s.cand_key / s.cand_idx (in any order; if there are more than the buffer holds the row
+// is searched exactly), the kk largest by (key desc, id asc) are the survivors; masses, top-p
+// and the draw follow. Run by all threads of one CTA.
+template <typename T>
+__device__ __forceinline__ void topk_finish(TopkSmem& s, int n_cand, const T* __restrict__ rp, int v, bool vec_ok,
+                                            int kk, float inv_temp, float top_p, unsigned long long seed,
+                                            unsigned long long step, const long long* __restrict__ row_ids, int row,
+                                            int* __restrict__ out) {
+  const int tid = threadIdx.x;
+  const int nt = blockDim.x;
+  if (n_cand > kCandCap) {
+    // ---- rare: more ties / near-ties than the candidate buffer holds. Exact radix select by
+    // counting passes, then an index-ordered pick among the ties at the threshold.
+    uint32_t tau = 0;
+    for (int bit = 31; bit >= 0; --bit) {
+      const uint32_t cand = tau | (1u << bit);
+      int local = 0;
+      for_each_key<T>(rp, v, vec_ok, [&](uint32_t key, int) { local += (key >= cand) ? 1 : 0; });
+      if (block_sum_int(local, s.red) >= kk) tau = cand;
+    }
+    int local_gt = 0;
+    for_each_key<T>(rp, v, vec_ok, [&](uint32_t key, int) { local_gt += (key > tau) ? 1 : 0; });
+    const int n_gt = block_sum_int(local_gt, s.red);
+    const int quota = kk - n_gt;
+    if (tid == 0) s.count = 0;
+    __syncthreads();
+    for_each_key<T>(rp, v, vec_ok, [&](uint32_t key, int i) {
+      if (key > tau) {
+        const int slot = atomicAdd(&s.count, 1);
+        s.cand_key[slot] = key;
+        s.cand_idx[slot] = static_cast<uint32_t>(i);
+      }
+    });
+    __syncthreads();
+    unsigned long long tie_base = 0;
+    constexpr int kPer = 8;
+    for (int base = 0; base < v && tie_base < static_cast<unsigned long long>(quota); base += nt * kPer) {
+      const int i0 = base + tid * kPer;
+      int mine = 0;
+      for (int j = 0; j < kPer; ++j) {
+        const int i = i0 + j;
+        if (i < v && float_to_key(Elem<T>::to_float(rp[i])) == tau) ++mine;
+      }
+      unsigned long long total;
+      unsigned long long off = tie_base + block_exscan_u64(static_cast<unsigned long long>(mine), s.scan, total);
+      for (int j = 0; j < kPer; ++j) {
+        const int i = i0 + j;
+        if (i < v && float_to_key(Elem<T>::to_float(rp[i])) == tau) {
+          if (off < static_cast<unsigned long long>(quota)) {
+            s.cand_key[n_gt + off] = tau;
+            s.cand_idx[n_gt + off] = static_cast<uint32_t>(i);
+          }
+          ++off;
+        }
+      }
+      tie_base += total;
+    }
+    __syncthreads();
+    n_cand = kk;
+  }
+
+  // ---- rank sort of the candidates by (key desc, id asc); the first kk are the survivors
+  for (int i = tid; i < n_cand; i += nt) {
+    const uint32_t ki = s.cand_key[i], ii = s.cand_idx[i];
+    int rank = 0;
+    for (int j = 0; j < n_cand; ++j) {
+      const uint32_t kj = s.cand_key[j], ij = s.cand_idx[j];
+      rank += (kj > ki || (kj == ki && ij < ii)) ? 1 : 0;
+    }
+    if (rank < kk) {
+      s.sorted_key[rank] = ki;
+      s.sorted_idx[rank] = ii;
+    }
+  }
+  __syncthreads();
+
+  // ---- masses, top-p, draw
+  const float y0 = mul_rn(key_to_float(s.sorted_key[0]), inv_temp);
+  for (int i = tid; i < kk; i += nt) {
+    const float y = mul_rn(key_to_float(s.sorted_key[i]), inv_temp);
+    s.mass[i] = mass_fixed(exp_det(sub_rn(y, y0)));
+  }
+  __syncthreads();
+  if (tid < 32) {
+    const unsigned long long rid = row_ids ? static_cast<unsigned long long>(row_ids[row])
+                                           : static_cast<unsigned long long>(row);
+    const int pos = pick_sorted_warp(s.mass, kk, top_p, uniform_u24(seed, rid, step));
+    if (tid == 0) out[row] = static_cast<int>(s.sorted_idx[pos]);
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kTopkThreads, 2)
 sample_topk_kernel(const T* __restrict__ logits, long long row_stride, int v, const long long* __restrict__ row_ids,
@@ -312,85 +407,157 @@ sample_topk_kernel(const T* __restrict__ logits, long long row_stride, int v, co
   int n_cand = s.count;
   __syncthreads();
 
-  if (n_cand > kCandCap) {
-    // ---- rare: more ties / near-ties than the candidate buffer holds. Exact radix select by
-    // counting passes, then an index-ordered pick among the ties at the threshold.
-    uint32_t tau = 0;
-    for (int bit = 31; bit >= 0; --bit) {
-      const uint32_t cand = tau | (1u << bit);
-      int local = 0;
-      for_each_key<T>(rp, v, vec_ok, [&](uint32_t key, int) { local += (key >= cand) ? 1 : 0; });
-      if (block_sum_int(local, s.red) >= kk) tau = cand;
-    }
-    int local_gt = 0;
-    for_each_key<T>(rp, v, vec_ok, [&](uint32_t key, int) { local_gt += (key > tau) ? 1 : 0; });
-    const int n_gt = block_sum_int(local_gt, s.red);
-    const int quota = kk - n_gt;
-    if (tid == 0) s.count = 0;
-    __syncthreads();
-    for_each_key<T>(rp, v, vec_ok, [&](uint32_t key, int i) {
-      if (key > tau) {
-        const int slot = atomicAdd(&s.count, 1);
-        s.cand_key[slot] = key;
-        s.cand_idx[slot] = static_cast<uint32_t>(i);
-      }
-    });
-    __syncthreads();
-    unsigned long long tie_base = 0;
-    constexpr int kPer = 8;
-    for (int base = 0; base < v && tie_base < static_cast<unsigned long long>(quota); base += nt * kPer) {
-      const int i0 = base + tid * kPer;
-      int mine = 0;
-      for (int j = 0; j < kPer; ++j) {
-        const int i = i0 + j;
-        if (i < v && float_to_key(Elem<T>::to_float(rp[i])) == tau) ++mine;
-      }
-      unsigned long long total;
-      unsigned long long off = tie_base + block_exscan_u64(static_cast<unsigned long long>(mine), s.scan, total);
-      for (int j = 0; j < kPer; ++j) {
-        const int i = i0 + j;
-        if (i < v && float_to_key(Elem<T>::to_float(rp[i])) == tau) {
-          if (off < static_cast<unsigned long long>(quota)) {
-            s.cand_key[n_gt + off] = tau;
-            s.cand_idx[n_gt + off] = static_cast<uint32_t>(i);
-          }
-          ++off;
-        }
-      }
-      tie_base += total;
-    }
-    __syncthreads();
-    n_cand = kk;
-  }
+  topk_finish<T>(s, n_cand, rp, v, vec_ok, kk, inv_temp, top_p, seed, step, row_ids, row, out);
+}
 
-  // ---- rank sort of the candidates by (key desc, id asc); the first kk are the survivors
-  for (int i = tid; i < n_cand; i += nt) {
-    const uint32_t ki = s.cand_key[i], ii = s.cand_idx[i];
-    int rank = 0;
-    for (int j = 0; j < n_cand; ++j) {
-      const uint32_t kj = s.cand_key[j], ij = s.cand_idx[j];
-      rank += (kj > ki || (kj == ki && ij < ii)) ? 1 : 0;
-    }
-    if (rank < kk) {
-      s.sorted_key[rank] = ki;
-      s.sorted_idx[rank] = ii;
-    }
-  }
-  __syncthreads();
+// ------------------------------------------------------------------------------------------
+// Cluster variant of the top-k kernel for 16-bit logits and few rows: C CTAs of a thread-block
+// cluster share one row, so that C SMs pull it instead of one (a single CTA is bound by the
+// latency of its own loads; with 64 rows only 64 of the 148 SMs would work at all).
+//   1. CTA r scans its 1/C of the row and finds, as above, a bound that at least kk of its own
+//      elements reach. The largest of the C bounds is valid for the whole row: the part that
+//      produced it alone holds kk elements at or above it.
+//   2. The bounds travel through distributed shared memory (one store per peer, one cluster
+//      barrier); every CTA collects the elements of its part that reach the common bound.
+//   3. Counts are exchanged the same way, every CTA copies its candidates into CTA 0's list at
+//      its offset (remote shared-memory stores), and CTA 0 finishes as the one-CTA kernel does.
+// The survivors are the kk largest by (key desc, id asc) of a candidate set that contains them
+// all, so the token is the one the one-CTA kernel and the CPU library return. No multicast.
+// ------------------------------------------------------------------------------------------
+constexpr int kMaxCluster = 4;
 
-  // ---- masses, top-p, draw
-  const float y0 = mul_rn(key_to_float(s.sorted_key[0]), inv_temp);
-  for (int i = tid; i < kk; i += nt) {
-    const float y = mul_rn(key_to_float(s.sorted_key[i]), inv_temp);
-    s.mass[i] = mass_fixed(exp_det(sub_rn(y, y0)));
+struct ClusterXchg {
+  uint32_t low[kMaxCluster];   // bound found by each CTA of the cluster
+  int cnt[kMaxCluster];        // candidates collected by each CTA
+};
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(const void* p, uint32_t rank) {
+  uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(p)), r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_remote_u32(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+}
+
+template <typename T, int C>
+__global__ void __launch_bounds__(kTopkThreads, 2)
+sample_topk_cluster_kernel(const T* __restrict__ logits, long long row_stride, int v,
+                           const long long* __restrict__ row_ids, float inv_temp, int top_k, float top_p,
+                           unsigned long long seed, unsigned long long step, int* __restrict__ out) {
+  static_assert(Elem<T>::kPacked, "the cluster kernel takes 16-bit logits");
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  TopkSmem& s = *reinterpret_cast<TopkSmem*>(smem_raw);
+  ClusterXchg& x = *reinterpret_cast<ClusterXchg*>(smem_raw + sizeof(TopkSmem));
+  const int tid = threadIdx.x;
+  const int nt = blockDim.x;
+  const int row = blockIdx.x / C;
+  const int cr = static_cast<int>(cluster_rank());
+  const T* rp = logits + static_cast<long long>(row) * row_stride;  // 16-byte aligned (checked by the host)
+  const int kk = min(min(top_k, kMaxTopK), v);
+  if (tid == 0) s.count = 0;
+
+  // ---- this CTA's part: vectors [v0, v1) of the row, the scalar tail goes to the last CTA
+  const int nvec = v / 8;
+  const int v0 = static_cast<int>(static_cast<long long>(nvec) * cr / C);
+  const int v1 = static_cast<int>(static_cast<long long>(nvec) * (cr + 1) / C);
+  const uint4* vp = reinterpret_cast<const uint4*>(rp);
+  const unsigned short* hp = reinterpret_cast<const unsigned short*>(rp);
+  const bool has_tail = cr == C - 1;
+  constexpr int kU = 8;
+  uint32_t tm2 = 0;
+  int i = v0 + tid;
+  for (; i + (kU - 1) * nt < v1; i += kU * nt) {
+    uint4 raw[kU];
+#pragma unroll
+    for (int u = 0; u < kU; ++u) raw[u] = __ldg(vp + i + u * nt);
+#pragma unroll
+    for (int u = 0; u < kU; ++u)
+      tm2 = __vmaxu2(tm2, __vmaxu2(__vmaxu2(key16x2<T>(raw[u].x), key16x2<T>(raw[u].y)),
+                                   __vmaxu2(key16x2<T>(raw[u].z), key16x2<T>(raw[u].w))));
   }
+  for (; i < v1; i += nt) {
+    const uint4 raw = __ldg(vp + i);
+    tm2 = __vmaxu2(tm2, __vmaxu2(__vmaxu2(key16x2<T>(raw.x), key16x2<T>(raw.y)),
+                                 __vmaxu2(key16x2<T>(raw.z), key16x2<T>(raw.w))));
+  }
+  if (has_tail)
+    for (int t = nvec * 8 + tid; t < v; t += nt) tm2 = __vmaxu2(tm2, key16x2<T>(hp[t]) & 0xFFFFu);
+  const uint32_t m_lo = tm2 & 0xFFFFu, m_hi = tm2 >> 16;
+  uint32_t low16 = 0;
+  for (int bit = 15; bit >= 0; --bit) {
+    const uint32_t cand = low16 | (1u << bit);
+    const int cnt = __syncthreads_count(m_lo >= cand) + __syncthreads_count(m_hi >= cand);
+    if (cnt >= kk) low16 = cand;
+  }
+  // ---- the largest of the C bounds serves the whole row
+  if (tid < C) st_remote_u32(map_to_cta(&x.low[cr], static_cast<uint32_t>(tid)), low16);
+  cluster_sync_all();
+#pragma unroll
+  for (int r = 0; r < C; ++r) low16 = max(low16, x.low[r]);
+
+  // ---- collect this part's elements at or above the bound (second pass: L2)
+  const uint32_t low2 = low16 * 0x00010001u;
+  auto push = [&](uint32_t bits16, int idx) {
+    const int slot = atomicAdd(&s.count, 1);
+    if (slot < kCandCap) {
+      s.cand_key[slot] = float_to_key(Elem<T>::to_float(from_bits16<T>(bits16)));
+      s.cand_idx[slot] = static_cast<uint32_t>(idx);
+    }
+  };
+  auto scan_vec = [&](const uint4& raw, int vi) {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    const uint32_t h0 = __vcmpgeu2(key16x2<T>(w[0]), low2), h1 = __vcmpgeu2(key16x2<T>(w[1]), low2);
+    const uint32_t h2 = __vcmpgeu2(key16x2<T>(w[2]), low2), h3 = __vcmpgeu2(key16x2<T>(w[3]), low2);
+    if ((h0 | h1 | h2 | h3) == 0u) return;
+    const uint32_t hit[4] = {h0, h1, h2, h3};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (hit[j] & 0xFFFFu) push(w[j] & 0xFFFFu, vi * 8 + 2 * j);
+      if (hit[j] >> 16) push(w[j] >> 16, vi * 8 + 2 * j + 1);
+    }
+  };
+  i = v0 + tid;
+  for (; i + (kU - 1) * nt < v1; i += kU * nt) {
+    uint4 raw[kU];
+#pragma unroll
+    for (int u = 0; u < kU; ++u) raw[u] = __ldg(vp + i + u * nt);
+#pragma unroll
+    for (int u = 0; u < kU; ++u) scan_vec(raw[u], i + u * nt);
+  }
+  for (; i < v1; i += nt) scan_vec(__ldg(vp + i), i);
+  if (has_tail)
+    for (int t = nvec * 8 + tid; t < v; t += nt)
+      if ((key16x2<T>(hp[t]) & 0xFFFFu) >= low16) push(hp[t], t);
   __syncthreads();
-  if (tid < 32) {
-    const unsigned long long rid = row_ids ? static_cast<unsigned long long>(row_ids[row])
-                                           : static_cast<unsigned long long>(row);
-    const int pos = pick_sorted_warp(s.mass, kk, top_p, uniform_u24(seed, rid, step));
-    if (tid == 0) out[row] = static_cast<int>(s.sorted_idx[pos]);
+  const int mine = s.count;  // may exceed the buffer: then the total does too and CTA 0 searches the row exactly
+  if (tid < C) st_remote_u32(map_to_cta(&x.cnt[cr], static_cast<uint32_t>(tid)), static_cast<uint32_t>(mine));
+  cluster_sync_all();
+  int total = 0, offset = 0;
+#pragma unroll
+  for (int r = 0; r < C; ++r) {
+    if (r < cr) offset += x.cnt[r];
+    total += x.cnt[r];
   }
+  // ---- candidates of the other CTAs move into CTA 0's list
+  if (cr != 0 && total <= kCandCap) {
+    const uint32_t dst_key = map_to_cta(&s.cand_key[0], 0u), dst_idx = map_to_cta(&s.cand_idx[0], 0u);
+    for (int j = tid; j < mine; j += nt) {
+      st_remote_u32(dst_key + 4u * static_cast<uint32_t>(offset + j), s.cand_key[j]);
+      st_remote_u32(dst_idx + 4u * static_cast<uint32_t>(offset + j), s.cand_idx[j]);
+    }
+  }
+  cluster_sync_all();  // after this barrier nobody touches another CTA's shared memory
+  if (cr != 0) return;
+  topk_finish<T>(s, total, rp, v, true, kk, inv_temp, top_p, seed, step, row_ids, row, out);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -662,6 +829,49 @@ int launch_sampling(const void* logits, long long row_stride, int rows, int v, c
                                static_cast<int>(sizeof(TopkSmem)));
       if (e != cudaSuccess) return -10;
       configured = true;
+    }
+    // few rows of 16-bit logits: several CTAs per row (a cluster), so that every SM has work
+    int cluster = 1;
+    if constexpr (Elem<T>::kPacked) {
+      int dev = 0, sms = 0;
+      cudaGetDevice(&dev);
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+      const bool aligned = (reinterpret_cast<uintptr_t>(lp) & 15u) == 0 && (row_stride * sizeof(T)) % 16 == 0 && v >= 8192;
+      if (aligned && rows * 4 <= sms * 2) cluster = 4;
+      else if (aligned && rows * 2 <= sms * 2) cluster = 2;
+      if (const char* e = getenv("KA_SAMPLE_CLUSTER")) {      // 1 / 2 / 4: pin the variant (tuning, tests)
+        const int c = atoi(e);
+        if (c == 1 || ((c == 2 || c == 4) && aligned)) cluster = c;
+      }
+    }
+    if (cluster > 1) {
+      if constexpr (Elem<T>::kPacked) {
+        const int smem = static_cast<int>(sizeof(TopkSmem) + sizeof(ClusterXchg));
+        auto* k2 = sample_topk_cluster_kernel<T, 2>;
+        auto* k4 = sample_topk_cluster_kernel<T, 4>;
+        static bool cluster_configured = false;
+        if (!cluster_configured) {
+          if (cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
+              cudaFuncSetAttribute(k4, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+            return -10;
+          cluster_configured = true;
+        }
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(static_cast<unsigned>(rows * cluster));
+        cfg.blockDim = dim3(kTopkThreads);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = static_cast<unsigned>(cluster);
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        e = cudaLaunchKernelEx(&cfg, cluster == 2 ? k2 : k4, lp, row_stride, v, row_ids, inv_temp, top_k, top_p, seed,
+                               step, out);
+        return e == cudaSuccess ? 0 : -11;
+      }
     }
     sample_topk_kernel<T><<<rows, kTopkThreads, sizeof(TopkSmem), stream>>>(lp, row_stride, v, row_ids, inv_temp, top_k,
                                                                          top_p, seed, step, out);

@@ -39,6 +39,28 @@ def test_sampler_llama_vocab_headline_config(cuda_device):
     assert torch.equal(tok, sample(logits, top_k=50, top_p=0.9, temperature=0.7, seed=1, step=3))
 
 
+@pytest.mark.parametrize("cluster", ["1", "2", "4"])
+def test_sampler_cluster_variants_equal_cpu_definition(cuda_device, cluster, monkeypatch):
+    """Few rows of 16-bit logits are sampled by a cluster of CTAs per row; every variant must
+    return the tokens of the CPU definition: a vocabulary with a scalar tail, heavy ties that
+    overflow the candidate list, k from 1 to 1024."""
+    monkeypatch.setenv("KA_SAMPLE_CLUSTER", cluster)
+    g = torch.Generator(device=cuda_device).manual_seed(7)
+    wide = (torch.randn(12, 50016, device=cuda_device, generator=g) * 2).to(torch.bfloat16)[:, :50011]
+    for top_k, top_p in ((50, 0.9), (1, None), (1024, 0.95)):
+        tok = sample(wide, top_k=top_k, top_p=top_p, temperature=0.7, seed=3, step=2)
+        assert torch.equal(tok.cpu(), _cpu(wide, top_k, top_p, 0.7, 3, 2)), (cluster, top_k, top_p)
+    ties = torch.zeros(4, 20000, device=cuda_device, dtype=torch.float16)
+    ties[2, 19999] = 1.0
+    tok = sample(ties, top_k=50, top_p=0.5, seed=2, step=0)
+    assert torch.equal(tok.cpu(), _cpu(ties, 50, 0.5, 1.0, 2, 0))
+    llama = (torch.randn(64, 128256, device=cuda_device, generator=g) * 2).to(torch.bfloat16)
+    tok = sample(llama, top_k=50, top_p=0.9, temperature=0.7, seed=1, step=5)
+    assert torch.equal(tok[:16].cpu(), _cpu(llama[:16], 50, 0.9, 0.7, 1, 5))
+    monkeypatch.setenv("KA_SAMPLE_CLUSTER", "1")
+    assert torch.equal(tok, sample(llama, top_k=50, top_p=0.9, temperature=0.7, seed=1, step=5))
+
+
 def test_sampler_heavy_ties(cuda_device):
     # constant rows overflow the candidate list: the exact-select path cuts ties by token id
     logits = torch.zeros(4, 20000, device=cuda_device, dtype=torch.bfloat16)

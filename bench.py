@@ -57,7 +57,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._pump, daemon=True)
             self.thread.start()
         except OSError:
@@ -65,9 +65,13 @@ class ClockSampler:
 
     def _pump(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.time(), line.strip()))
 
-    def stop(self) -> dict:
+    def stop(self, t0: float = 0.0, t1: float = float("inf")) -> dict:
+        """Summary of the samples taken between wall-clock times ``t0`` and ``t1`` (the timed
+        region). The sampler is started before the warm-up, because nvidia-smi needs a few
+        hundred milliseconds to produce its first line; if the timed region is shorter than the
+        sampling period, the samples closest to it are used and ``window`` says so."""
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -77,7 +81,13 @@ class ClockSampler:
             self.proc.kill()
         sm, smax, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
+        inside = [l for t, l in self.lines if t0 <= t <= t1 + 0.05]
+        window = "timed region"
+        if not inside and self.lines:
+            nearest = sorted(self.lines, key=lambda tl: min(abs(tl[0] - t0), abs(tl[0] - t1)))[:3]
+            inside = [l for _, l in nearest]
+            window = "nearest samples (timed region shorter than the sampling period)"
+        for line in inside:
             parts = [x.strip() for x in line.split(",")]
             if len(parts) < 7:
                 continue
@@ -90,7 +100,7 @@ class ClockSampler:
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "reasons": sorted(reasons), "window": window}
 
 
 def init_dist(n_gpus: int):
@@ -135,20 +145,22 @@ def make_inputs(rows: int, v_rows: int, seed: int):
 def time_device(step, args, world, local):
     """W warm-up calls, then K calls between two CUDA events; max over ranks, with the clocks
     sampled while the timed calls run."""
+    clocks = ClockSampler(local)
+    clocks.start()
     for _ in range(args.warmup):
         step()
     barrier_sync(world)
-    clocks = ClockSampler(local)
-    clocks.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier_sync(world)
+    t0 = time.time()
     e0.record()
     for _ in range(args.steps):
         step()
     e1.record()
     barrier_sync(world)
+    t1 = time.time()
     ms = max_over_ranks(e0.elapsed_time(e1), world) / args.steps
-    return ms, clocks.stop()
+    return ms, clocks.stop(t0, t1)
 
 
 def time_end_to_end(step, h_host, ids_host, out_host, args, world):

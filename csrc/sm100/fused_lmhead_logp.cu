@@ -107,13 +107,29 @@ struct Item {
 };
 
 __device__ __forceinline__ void decode_item(const LogpParams& p, int i, Item& it) {
-  const int per_group = p.mg * p.n_chunks;
-  const int g = i / per_group;
-  const int mg_sz = min(p.mg, p.n_mtiles - g * p.mg);
-  const int r = i - g * per_group;
-  const int h = r / (mg_sz * p.cg);
-  const int cg_sz = min(p.cg, p.n_chunks - h * p.cg);
-  const int r2 = r - h * mg_sz * p.cg;
+  // Work order. A wave of CTAs covers mg row tiles x cg sub-slices. Either the row-tile group is
+  // the outer loop and its rows of H stay in L2 while all of W streams past once per group
+  // (c_outer = 0), or the group of sub-slices is the outer loop and its columns of W stay in
+  // L2 while all row tiles of the panel stream past once per group (c_outer = 1: less memory
+  // traffic when this rank's W is small, as with a vocabulary sharded eight ways).
+  int g, h, mg_sz, cg_sz, r2;
+  if (p.c_outer) {
+    const int full = p.n_mtiles * p.cg;          // items of a full group of sub-slices
+    h = i / full;
+    cg_sz = min(p.cg, p.n_chunks - h * p.cg);
+    const int r = i - h * full;
+    g = r / (p.mg * cg_sz);
+    mg_sz = min(p.mg, p.n_mtiles - g * p.mg);
+    r2 = r - g * p.mg * cg_sz;
+  } else {
+    const int per_group = p.mg * p.n_chunks;
+    g = i / per_group;
+    mg_sz = min(p.mg, p.n_mtiles - g * p.mg);
+    const int r = i - g * per_group;
+    h = r / (mg_sz * p.cg);
+    cg_sz = min(p.cg, p.n_chunks - h * p.cg);
+    r2 = r - h * mg_sz * p.cg;
+  }
   // Which of the two indices runs fastest over consecutive CTAs decides which CTAs are
   // neighbours: the sub-slices of one row tile (m_fast = 0), or the row tiles of one sub-slice.
   int m_local, c_local;
@@ -952,7 +968,8 @@ int forward_impl(const FwdArgs& a) {
     const int v = atoi(e);
     if (v >= 0 && v <= 3) p.l2_hint = v;
   }
-  p.m_fast = a.m_fast ? 1 : 0;
+  p.m_fast = (a.m_fast & 1) ? 1 : 0;
+  p.c_outer = (a.m_fast & 2) ? 1 : 0;
   p.cg = p.n_chunks < cg_pref ? p.n_chunks : cg_pref;
   {
     const int pairs = a.num_sms / a.cta_group;

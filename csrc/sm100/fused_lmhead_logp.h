@@ -36,6 +36,7 @@ struct LogpParams {
   int mt_rot;            // rotation of the row-tile order (row-sharded input: own rows first)
   int l2_hint;           // L2 eviction hints of the operand loads, see the producer
   int m_fast;            // work order inside a wave: 1 = consecutive CTAs take consecutive row tiles
+  int c_outer;           // 1 = groups of sub-slices are the outer loop (W stays in L2, H streams)
 
   // ---- row-sharded input (gather != 0): rank r holds rows [r * m_local, (r + 1) * m_local) of
   // the hidden states and the ids; the kernel pushes its rows of the panel into every peer's
@@ -81,8 +82,9 @@ int ka_lmhead_logp_forward(const void* hidden, const void* weight, const long lo
 
 // The same with an explicit schedule: `cg_pref` sub-slices of the vocabulary run side by side
 // (0: the default, 8), the CTAs that are left over them work on different row tiles; `m_fast`
-// says whether consecutive CTAs take consecutive row tiles of one sub-slice (1) or the
-// sub-slices of one row tile (0); `l2_hint` gives the operand loads an L2 eviction priority
+// bit 0 says whether consecutive CTAs take consecutive row tiles of one sub-slice (1) or the
+// sub-slices of one row tile (0), bit 1 whether the groups of sub-slices are the outer loop of
+// the work order (W stays in L2 and H streams) instead of the groups of row tiles; `l2_hint` gives the operand loads an L2 eviction priority
 // (0 none, 1 keep the hidden rows and let the weight tiles go first, 2 keep the hidden rows,
 // 3 keep the weight tiles). The schedule changes which tiles share the L2 at a time, hence
 // memory traffic and power, never a result: every combination gives the same bits.

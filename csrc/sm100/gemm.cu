@@ -111,12 +111,16 @@ struct RowCtx {
 // shared-memory tile so that the global stores are whole 64 / 128-byte row segments: eight
 // (fp32) or four (bf16) lanes cover one row segment contiguously. This matters most for the
 // partial tiles that go to another GPU, where every store instruction becomes NVLink packets.
+//
+// bf16 outputs are staged two 32-column groups at a time (`half` 0 then 1) and stored after the
+// second, so that a row segment is 128 bytes: a whole line for the peer's memory system instead
+// of two half-line writes (64-byte segments reached about 140 GB/s over NVLink).
 __device__ __forceinline__ void store_group_warp(const GemmParams& p, const uint32_t (&v)[32], uint32_t* wbuf,
                                                  long long row_w0, int col, int slice_global, const RowCtx& rc,
-                                                 int lane) {
-  if (col >= p.n) return;  // uniform over the warp
+                                                 int lane, int half) {
   const bool f32 = p.epilogue == kEpiStoreF32;
-  uint32_t* mine = wbuf + lane * 33;
+  if (f32 && col >= p.n) return;  // uniform over the warp
+  uint32_t* mine = wbuf + lane * 33 + (f32 ? 0 : half * 16);
   if (f32) {
 #pragma unroll
     for (int j = 0; j < 32; ++j) mine[j] = v[j];
@@ -136,6 +140,11 @@ __device__ __forceinline__ void store_group_warp(const GemmParams& p, const uint
     for (int j = 0; j < 16; ++j) mine[j] = pack_bf16(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
   }
   __syncwarp();
+  if (!f32) {
+    if (half == 0) return;   // stored together with the next group
+    col -= 32;               // first column of the staged pair of groups
+    if (col >= p.n) return;  // uniform over the warp
+  }
   if (f32) {
     float* base = static_cast<float*>(p.c) + row_w0 * p.ldc + col;
     const long long ld = p.ldc;
@@ -162,11 +171,11 @@ __device__ __forceinline__ void store_group_warp(const GemmParams& p, const uint
       base = static_cast<__nv_bfloat16*>(p.c) + row_w0 * p.ldc + col;
       ld = p.ldc;
     }
-    const int c = lane & 3, r0 = lane >> 2;
+    const int c = lane & 7, r0 = lane >> 3;   // eight lanes cover the 128 bytes of one row
     const bool col_ok = col + c * 8 + 8 <= p.n;
 #pragma unroll
-    for (int it = 0; it < 4; ++it) {
-      const int r = r0 + 8 * it;
+    for (int it = 0; it < 8; ++it) {
+      const int r = r0 + 4 * it;
       if (col_ok && row_w0 + r < p.m) {
         const uint32_t* src = wbuf + r * 33 + c * 4;
         *reinterpret_cast<uint4*>(base + r * ld + c * 8) = make_uint4(src[0], src[1], src[2], src[3]);
@@ -429,11 +438,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       for (int g = 0; g < kBN / 64; g += 2) {
         __syncwarp();
         tmem_ld_32x32(trow + (g + 1) * 32, vb);
-        store_group_warp(p, va, wbuf, row_w0, col0 + g * 32, slice_global, rc, lane);
+        store_group_warp(p, va, wbuf, row_w0, col0 + g * 32, slice_global, rc, lane, 0);
         __syncwarp();
         tmem_ld_wait_dep(vb);
         if (g + 2 < kBN / 64) tmem_ld_32x32(trow + (g + 2) * 32, va);
-        store_group_warp(p, vb, wbuf, row_w0, col0 + (g + 1) * 32, slice_global, rc, lane);
+        store_group_warp(p, vb, wbuf, row_w0, col0 + (g + 1) * 32, slice_global, rc, lane, 1);
         __syncwarp();
         if (g + 2 < kBN / 64) tmem_ld_wait_dep(va);
       }

@@ -830,16 +830,19 @@ int launch_sampling(const void* logits, long long row_stride, int rows, int v, c
       if (e != cudaSuccess) return -10;
       configured = true;
     }
-    // few rows of 16-bit logits: several CTAs per row (a cluster), so that every SM has work
+    // few rows of 16-bit logits may be given several CTAs per row (a cluster)
     int cluster = 1;
     if constexpr (Elem<T>::kPacked) {
       int dev = 0, sms = 0;
       cudaGetDevice(&dev);
       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
       const bool aligned = (reinterpret_cast<uintptr_t>(lp) & 15u) == 0 && (row_stride * sizeof(T)) % 16 == 0 && v >= 8192;
-      if (aligned && rows * 4 <= sms * 2) cluster = 4;
-      else if (aligned && rows * 2 <= sms * 2) cluster = 2;
-      if (const char* e = getenv("KA_SAMPLE_CLUSTER")) {      // 1 / 2 / 4: pin the variant (tuning, tests)
+      // Measured (bf16 [G, 128256], k = 50, L2 flushed): 28.7 / 28.7 / 30.6 us for 1 / 2 / 4 CTAs
+      // per row at G = 64, 31.6 / 35.7 / 50.0 at G = 128. A row's two passes are a small part of
+      // the kernel's latency chain (bound search, candidate sort, masses, draw), so more SMs per
+      // row buy nothing here; the variant stays available but is not chosen by default.
+      (void)sms;
+      if (const char* e = getenv("KA_SAMPLE_CLUSTER")) {      // 2 / 4: CTAs per row (opt-in)
         const int c = atoi(e);
         if (c == 1 || ((c == 2 || c == 4) && aligned)) cluster = c;
       }

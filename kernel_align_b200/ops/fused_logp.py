@@ -100,12 +100,16 @@ def check_status(ws_status: torch.Tensor) -> None:
 # fewer cycles, the single-CTA variant draws less power per cycle. A B200 that runs this kernel
 # back to back sits at its power cap and clocks down, so there the second one is often faster,
 # by an amount that depends on the GPU; in a short burst at full clock the first one wins. So
-# the first large call of a shape times the candidates on the actual inputs, three calls each,
-# and keeps the fastest (as cuDNN's benchmark mode does for convolutions).
+# the first large call of a shape times the candidates on the actual inputs, a quarter of a
+# second each, and keeps the fastest (as cuDNN's benchmark mode does for convolutions).
 # KA_LOGP_SCHEDULE="<cta_group>,<cg>[,<m_fast>[,<l2_hint>]]" pins a schedule; KA_LOGP_AUTOTUNE=0 keeps the default.
-# (cta_group, sub-slices side by side, 1 = consecutive CTAs take consecutive row tiles,
-#  L2 eviction hint of the operand loads: 0 none, 1 keep H / stream W, 2 keep H, 3 keep W)
-_SCHEDULES = [(2, 8, 0, 0), (2, 8, 0, 2), (2, 4, 1, 0), (1, 4, 0, 1), (1, 4, 0, 0), (1, 2, 0, 3), (1, 2, 0, 0)]
+# (cta_group, sub-slices side by side, work order, L2 eviction hint of the operand loads)
+#   work order: bit 0 = consecutive CTAs take consecutive row tiles (else consecutive sub-slices),
+#               bit 1 = groups of sub-slices are the outer loop (W stays in L2, H streams)
+#   L2 hint: 0 none, 1 keep H / stream W, 2 keep H, 3 keep W
+_SCHEDULES = [(2, 8, 0, 0), (2, 8, 0, 2), (2, 8, 2, 3), (2, 4, 2, 3), (2, 4, 1, 0), (1, 4, 0, 1), (1, 4, 0, 0),
+              (1, 2, 0, 3), (1, 4, 2, 3)]
+_TUNE_MIN_MS = 250.0      # a candidate runs at least this long: the clock settles under the power cap
 _DEFAULT_SCHEDULE = (2, 0, 0, 0)
 _AUTOTUNE_MIN_MACS = 2.0e12      # smaller calls take a few milliseconds at most: default schedule
 _tuned: dict = {}
@@ -122,8 +126,8 @@ def _pinned_schedule():
         hint = parts[3] if len(parts) > 3 else 0
     except (ValueError, IndexError):
         raise ValueError('KA_LOGP_SCHEDULE must look like "2,8", "1,4", "1,2,1" or "1,2,0,3"') from None
-    if g not in (1, 2) or not 0 <= cg <= 64 or m_fast not in (0, 1) or hint not in (0, 1, 2, 3):
-        raise ValueError("KA_LOGP_SCHEDULE: cta_group is 1 or 2, cg between 0 and 64, m_fast 0 or 1, l2_hint 0..3")
+    if g not in (1, 2) or not 0 <= cg <= 64 or m_fast not in (0, 1, 2, 3) or hint not in (0, 1, 2, 3):
+        raise ValueError("KA_LOGP_SCHEDULE: cta_group is 1 or 2, cg between 0 and 64, work order 0..3, l2_hint 0..3")
     return g, cg, m_fast, hint
 
 
@@ -137,20 +141,23 @@ def _choose_schedule(key, macs: float, device, launch):
     if macs < _AUTOTUNE_MIN_MACS or os.environ.get("KA_LOGP_AUTOTUNE", "1") == "0" or \
             torch.cuda.is_current_stream_capturing():
         return _DEFAULT_SCHEDULE
-    # Each candidate runs three times back to back and the last two are timed: what decides
-    # under the power cap is the rate a schedule sustains, and the first call after a change
-    # of schedule still runs at the clock the previous one left behind.
-    events = {}
+    # What decides under the power cap is the rate a schedule sustains, and the clock needs a
+    # few hundred milliseconds to settle after a change of load: a candidate first runs once
+    # (timed, to size the rest), then as many calls as fill _TUNE_MIN_MS (at least two), and
+    # those are what is compared.
+    timings = {}
     for sched in _SCHEDULES:
-        launch(*sched)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
         e0.record()
         launch(*sched)
-        launch(*sched)
         e1.record()
-        events[sched] = (e0, e1)
-    torch.cuda.synchronize(device)
-    timings = {k: v[0].elapsed_time(v[1]) / 2 for k, v in events.items()}
+        e1.synchronize()
+        n = max(2, min(64, int(_TUNE_MIN_MS / max(e0.elapsed_time(e1), 1e-3)) + 1))
+        for _ in range(n):
+            launch(*sched)
+        e2.record()
+        e2.synchronize()
+        timings[sched] = e1.elapsed_time(e2) / n
     best = min(timings, key=timings.get)
     _tuned[key] = best
     from ..utils.logger import logger

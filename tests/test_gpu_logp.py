@@ -64,12 +64,13 @@ def test_fused_logp_every_schedule_gives_the_same_bits_and_autotune_picks_one(cu
     case goes through the same code."""
     h, w, ids = _inputs(cuda_device, 3000, 512, 30000, seed=4)
     want, want_lse = fused_logp.lmhead_logp(h, w, ids, cta_group=2, return_lse=True, check=True)
-    for sched in ("2,8", "2,3", "1,4", "1,2", "1,3", "1,1", "1,2,1", "2,4,1", "1,5,1", "1,4,0,1", "2,8,0,2", "1,2,0,3"):
+    for sched in ("2,8", "2,3", "1,4", "1,2", "1,3", "1,1", "1,2,1", "2,4,1", "1,5,1", "1,4,0,1", "2,8,0,2", "1,2,0,3", "2,4,2", "1,3,3,1", "2,5,2,3"):
         monkeypatch.setenv("KA_LOGP_SCHEDULE", sched)
         out, lse = fused_logp.lmhead_logp(h, w, ids, return_lse=True, check=True)
         assert torch.equal(out, want) and torch.equal(lse, want_lse), sched
     monkeypatch.delenv("KA_LOGP_SCHEDULE")
     monkeypatch.setattr(fused_logp, "_AUTOTUNE_MIN_MACS", 0.0)
+    monkeypatch.setattr(fused_logp, "_TUNE_MIN_MS", 1.0)
     fused_logp._tuned.clear()
     out = fused_logp.lmhead_logp(h, w, ids, check=True)
     assert torch.equal(out, want)

@@ -111,7 +111,15 @@ _SCHEDULES = [(2, 8, 0, 0), (2, 8, 0, 2), (2, 8, 2, 3), (2, 4, 2, 3), (2, 4, 1, 
               (1, 2, 0, 3), (1, 4, 2, 3)]
 _TUNE_MIN_MS = 250.0      # a candidate runs at least this long: the clock settles under the power cap
 _DEFAULT_SCHEDULE = (2, 0, 0, 0)
-_AUTOTUNE_MIN_MACS = 2.0e12      # smaller calls take a few milliseconds at most: default schedule
+# A shard of the LM head that about fits the L2 twice over (a vocabulary sharded 4 or 8 ways) is
+# walked W-stationary with the keep-W hint: 12.9 ms against 13.5 - 14.0 ms for the default order
+# on a 16128-column shard, in a burst and at the power cap alike.
+_SMALL_SHARD_SCHEDULE = (2, 8, 2, 3)
+_SMALL_SHARD_BYTES = 300 << 20
+# Timing the candidates takes a quarter of a second each, two seconds in all, at full power: it
+# pays for calls of tens of milliseconds (one or two GPUs at G = 256), not for shorter ones,
+# which take the default for their shard size.
+_AUTOTUNE_MIN_MACS = 3.0e13
 _tuned: dict = {}
 
 
@@ -131,7 +139,7 @@ def _pinned_schedule():
     return g, cg, m_fast, hint
 
 
-def _choose_schedule(key, macs: float, device, launch):
+def _choose_schedule(key, macs: float, device, launch, shard_bytes: int = 1 << 62):
     """The schedule for this call: pinned, tuned earlier, tuned now, or the default."""
     pinned = _pinned_schedule()
     if pinned is not None:
@@ -140,7 +148,7 @@ def _choose_schedule(key, macs: float, device, launch):
         return _tuned[key]
     if macs < _AUTOTUNE_MIN_MACS or os.environ.get("KA_LOGP_AUTOTUNE", "1") == "0" or \
             torch.cuda.is_current_stream_capturing():
-        return _DEFAULT_SCHEDULE
+        return _SMALL_SHARD_SCHEDULE if shard_bytes <= _SMALL_SHARD_BYTES and macs >= 1.0e11 else _DEFAULT_SCHEDULE
     # What decides under the power cap is the rate a schedule sustains, and the clock needs a
     # few hundred milliseconds to settle after a change of load: a candidate first runs once
     # (timed, to size the rest), then as many calls as fill _TUNE_MIN_MS (at least two), and
@@ -345,7 +353,8 @@ def _lmhead_logp_forward(
         # ranks tune (a collective sequence of calls when the vocabulary is sharded) or none does
         rows_total = m * world if sharded else m
         key = (hidden.device.index, rows_total, k, v_global, world, sharded)
-        sched = _choose_schedule(key, float(rows_total) * k * (v_global / world), hidden.device, launch)
+        sched = _choose_schedule(key, float(rows_total) * k * (v_global / world), hidden.device, launch,
+                                 shard_bytes=int(v_global / world) * k * 2)
     else:
         sched = (int(cta_group), 0, 0, 0)
     launch(*sched)

@@ -47,13 +47,18 @@ __device__ __forceinline__ void report_failure(const WaitCtx& ctx, int code, int
 }
 
 // Wait for the phase with the given parity of an mbarrier in this CTA's shared memory.
+// `sleep_ns` > 0 makes the waiter sleep between polls: for warps that wait most of the time
+// (an epilogue that needs a tenth of a tile's duration) a polling loop costs issue slots and
+// power for nothing, and a few hundred nanoseconds of extra latency are hidden by the
+// double-buffered accumulator.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, const WaitCtx& ctx,
-                                                  int where, int aux0) {
+                                                  int where, int aux0, unsigned sleep_ns = 0u) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
   for (;;) {
     if (mbar_try_wait(bar, parity)) return true;
+    if (sleep_ns) __nanosleep(sleep_ns);
     if ((++spins & 31u) == 0u) {
       if (*ctx.abort_flag) return false;
       if (globaltimer_ns() - t0 > ctx.timeout_ns) {

@@ -37,6 +37,7 @@ struct LogpParams {
   int l2_hint;           // L2 eviction hints of the operand loads, see the producer
   int m_fast;            // work order inside a wave: 1 = consecutive CTAs take consecutive row tiles
   int c_outer;           // 1 = groups of sub-slices are the outer loop (W stays in L2, H streams)
+  int epi_sleep_ns;      // the epilogue warps sleep this long between polls of the accumulator barrier
 
   // ---- row-sharded input (gather != 0): rank r holds rows [r * m_local, (r + 1) * m_local) of
   // the hidden states and the ids; the kernel pushes its rows of the panel into every peer's

@@ -106,6 +106,22 @@ struct RowCtx {
   long long tgt;   // target column inside this shard (or out of range)
 };
 
+// Layout of the reduce-scatter staging buffer of one owner rank. A partial tile is not stored
+// row-major: the 32 rows x 64 columns that one epilogue warp stores at a time are one contiguous
+// 4 KiB fragment, [slice][row block][column tile][row quarter][column half][column pair], so
+// that a warp's stores to the owner (another GPU for 7/8 of the tiles at TP = 8) cover whole
+// contiguous kilobytes instead of 128-byte pieces 8 KiB apart (which reached 160 GB/s over
+// NVLink). The reduce tail reads with the same function.
+constexpr int kFragElems = 32 * 64;                  // bf16 elements of a fragment
+constexpr int kTileElems = kBM * kBN;                // 16 fragments
+__device__ __forceinline__ long long stage_offset(int slice, int rblks, int tiles_n, int lr, int col) {
+  const int rblk = lr / kBM, r = lr - rblk * kBM;
+  const int nb = col / kBN, c = col - nb * kBN;
+  const int frag = ((r >> 5) * 2 + (c >> 7)) * 2 + ((c >> 6) & 1);
+  return ((static_cast<long long>(slice) * rblks + rblk) * tiles_n + nb) * kTileElems +
+         static_cast<long long>(frag) * kFragElems + (r & 31) * 64 + (c & 63);
+}
+
 // Store 32 consecutive accumulator columns of the warp's 32 rows. Each lane holds one row
 // (that is how tcgen05.ld hands out TMEM lanes); the values are transposed through a padded
 // shared-memory tile so that the global stores are whole 64 / 128-byte row segments: eight
@@ -163,10 +179,10 @@ __device__ __forceinline__ void store_group_warp(const GemmParams& p, const uint
     long long ld;
     if (p.epilogue == kEpiPartialF32) {
       const int owner = static_cast<int>(row_w0 / p.rows_per_rank);
-      const long long lr = row_w0 - static_cast<long long>(owner) * p.rows_per_rank;
+      const int lr = static_cast<int>(row_w0 - static_cast<long long>(owner) * p.rows_per_rank);
       base = static_cast<__nv_bfloat16*>(p.stage[owner]) +
-             (static_cast<long long>(slice_global) * p.rows_per_rank + lr) * p.n + col;
-      ld = p.n;
+             stage_offset(slice_global, p.rows_per_rank / kBM, (p.n + kBN - 1) / kBN, lr, col);
+      ld = 64;  // rows of a fragment are 64 elements apart
     } else {
       base = static_cast<__nv_bfloat16*>(p.c) + row_w0 * p.ldc + col;
       ld = p.ldc;
@@ -480,14 +496,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         if (ctl->abort_flag) break;
         const int ncols = min(kBN, p.n - nb * kBN);
         const int vec_per_row = ncols / 8;  // 8 bf16 = 16 bytes
-        const size_t slice_stride = static_cast<size_t>(p.rows_per_rank) * p.n;
+        const size_t slice_stride = static_cast<size_t>(rblks) * tiles_n * kTileElems;
 #pragma unroll 2
         for (int i = tid; i < kBM * vec_per_row; i += kEpiThreads) {
           const int r = i / vec_per_row, c8 = i - r * vec_per_row;
           const int lr = rblk * kBM + r;
           if (lr >= rows_valid) continue;
-          const size_t off = static_cast<size_t>(lr) * p.n + nb * kBN + c8 * 8;
-          const __nv_bfloat16* base = static_cast<const __nv_bfloat16*>(p.stage[p.rank]) + off;
+          const size_t off = static_cast<size_t>(lr) * p.n + nb * kBN + c8 * 8;  // in out / residual (row-major)
+          const __nv_bfloat16* base = static_cast<const __nv_bfloat16*>(p.stage[p.rank]) +
+                                      stage_offset(0, rblks, tiles_n, lr, nb * kBN + c8 * 8);
           float4 lo[8], hi[8];
 #pragma unroll
           for (int q = 0; q < 8; ++q) {

@@ -39,7 +39,7 @@ struct GemmParams {
   int total_slices;       // canonical slice count (8)
   int world, rank;
   int rows_per_rank;      // rows of the output each rank owns (multiple of 128)
-  void* stage[8];         // per owner rank: [total_slices][rows_per_rank][n] bf16
+  void* stage[8];         // per owner rank: [total_slices][row blocks][column tiles][128 x 256] bf16, fragment-major
   unsigned* flags[8];     // per owner rank: [total_slices][row blocks of 128][n tiles of 256]
   unsigned epoch;
   void* out;              // reduced bf16 [rows_per_rank, n] of this rank

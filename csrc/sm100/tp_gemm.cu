@@ -33,10 +33,12 @@ inline int rows_per_rank_of(int m, int world) {
 extern "C" {
 
 // Bytes of the symmetric buffer a rank maps for ka_gemm_reduce_scatter: two generations of
-// [8 slices][rows_per_rank][n] bf16 staging, then the flags of both generations.
+// [8 slices][row blocks][column tiles][128 x 256] bf16 staging (whole tiles, each stored as 16
+// contiguous warp fragments, see stage_offset in gemm.cu), then the flags of both generations.
 size_t ka_gemm_rs_exchange_bytes(int m, int n, int world) {
   const size_t rpr = rows_per_rank_of(m, world);
-  const size_t stage = round256(static_cast<size_t>(kSlices) * rpr * n * sizeof(__nv_bfloat16));
+  const size_t stage = round256(static_cast<size_t>(kSlices) * (rpr / kBlk) * ((n + kTileN - 1) / kTileN) * kBlk * kTileN *
+                                sizeof(__nv_bfloat16));
   const size_t flags = round256(static_cast<size_t>(kSlices) * (rpr / kBlk) * ((n + kTileN - 1) / kTileN) * 4);
   return 2 * stage + 2 * flags;
 }
@@ -68,7 +70,8 @@ int ka_gemm_reduce_scatter(const void* a, long long lda, const void* b, long lon
   p.rank = rank;
   p.rows_per_rank = rows_per_rank_of(m, world);
   const size_t rpr = p.rows_per_rank;
-  const size_t stage = round256(static_cast<size_t>(kSlices) * rpr * n * sizeof(__nv_bfloat16));
+  const size_t stage = round256(static_cast<size_t>(kSlices) * (rpr / kBlk) * ((n + kTileN - 1) / kTileN) * kBlk * kTileN *
+                                sizeof(__nv_bfloat16));
   const size_t flags = round256(static_cast<size_t>(kSlices) * (rpr / kBlk) * ((n + kTileN - 1) / kTileN) * 4);
   const unsigned gen = epoch & 1u;
   for (int r = 0; r < world; ++r) {

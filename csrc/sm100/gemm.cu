@@ -27,7 +27,7 @@ constexpr int kUmmaK = 16;
 constexpr int kEpiWarps = 8;        // two per TMEM lane quarter: columns [0,128) and [128,256)
 constexpr int kEpiThreads = kEpiWarps * 32;
 constexpr int kWarpTma = kEpiWarps, kWarpMma = kEpiWarps + 1, kWarpPub = kEpiWarps + 2;
-constexpr int kThreads = kEpiThreads + 96;  // epilogue warps, TMA producer, MMA issuer, flag publisher
+constexpr int kThreads = kEpiThreads + 96;  // epilogue warps, TMA producer, MMA issuer, one spare warp
 constexpr int kStages = 6;
 constexpr int kABytes = kBM * kBK * 2;            // 16 KiB
 constexpr int kBBytes = (kBN / kG) * kBK * 2;     // 16 KiB
@@ -43,8 +43,6 @@ struct Control {
   uint64_t empty[kStages];
   uint64_t tfull[2];
   uint64_t tempty[2];
-  uint64_t pub_full[2];   // a unit's partial tile has been stored by every epilogue warp
-  uint64_t pub_empty[2];  // the publisher has raised the flag of the unit that used this slot
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -240,8 +238,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&ctl->tfull[b]), 1);
       mbar_init(smem_u32(&ctl->tempty[b]), kEpiWarps * kG);
-      mbar_init(smem_u32(&ctl->pub_full[b]), kEpiWarps);
-      mbar_init(smem_u32(&ctl->pub_empty[b]), 1);
     }
     ctl->abort_flag = 0;
     fence_mbar_init_cluster();
@@ -353,32 +349,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       }
     }
   } else if (warp == kWarpPub) {
-    // ------------------------------------------------------------------ flag publisher
-    // Partial tiles become visible to their owner through a system-scope fence and a flag
-    // store. The fence waits for this SM's outstanding (possibly NVLink) writes, which takes
-    // microseconds, so it runs in a warp of its own, off the epilogue's critical path.
-    if (lane == 0 && p.epilogue == kEpiPartialF32) {
-      int slot = 0;
-      uint32_t phase = 0;
-      const int rblks = p.rows_per_rank / kBM;
-      for (int u = pair_id; u < n_units; u += n_pairs) {
-        Unit un;
-        decode_unit(p, tiles_m, tiles_n, u, un);
-        if (!mbar_wait_bounded(smem_u32(&ctl->pub_full[slot]), phase, wctx, kWReduceFlag, slot)) break;
-        __threadfence_system();
-        const long long row0 = static_cast<long long>(un.m_blk) * (kBM * kG) + cta_rank * kBM;
-        if (row0 < p.m) {
-          const int owner = static_cast<int>(row0 / p.rows_per_rank);
-          const int rblk = static_cast<int>((row0 - static_cast<long long>(owner) * p.rows_per_rank) / kBM);
-          st_release_sys_u32(p.flags[owner] + (static_cast<size_t>(p.slice_base + un.slice) * rblks + rblk) * tiles_n +
-                                 un.n_blk,
-                             p.epoch);
-        }
-        mbar_arrive(smem_u32(&ctl->pub_empty[slot]));
-        slot ^= 1;
-        if (slot == 0) phase ^= 1u;
-      }
-    }
+    // (spare warp: the flags of the partial tiles are raised by the epilogue warps once, after
+    // the CTA's last unit; a fence and a flag per unit cost 50 us per unit under an all-to-all load)
   } else {
     // ------------------------------------------------------------------ epilogue (warps 0-7)
     // Warp w reads TMEM lanes 32 * (w & 3) .. +31 (its rows) and columns 128 * (w >> 2) .. +127.
@@ -465,21 +437,34 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(tempty_leader + static_cast<uint32_t>(abuf) * 8u);
-      if (p.epilogue == kEpiPartialF32) {
-        // this warp's part of the partial tile has been stored: let the publisher count it, once
-        // the publisher is done with the unit that used this slot two units ago
-        const bool free_slot = mbar_wait_bounded(smem_u32(&ctl->pub_empty[abuf]), aphase ^ 1u, wctx, kWReduceFlag, 100 + abuf);
-        ok = __all_sync(0xffffffffu, free_slot) != 0;
-        if (!ok) break;
-        if (lane == 0) mbar_arrive(smem_u32(&ctl->pub_full[abuf]));
-      }
       abuf ^= 1;
       if (abuf == 0) aphase ^= 1u;
     }
 
     if (p.epilogue == kEpiPartialF32) {
+      // Publish the partial tiles: every thread makes its own stores visible system-wide, the
+      // CTA meets, then the flags of all units this CTA computed are raised (the owners read
+      // them in their reduce tails, which start after their own last unit anyway).
+      __threadfence_system();
       epi_bar();  // every epilogue thread gets here, whether or not its loop ran to the end
       if (ctl->abort_flag) ok = false;
+      if (ok) {
+        const int rblks = p.rows_per_rank / kBM;
+        int k = 0;
+        for (int u = pair_id; u < n_units; u += n_pairs, ++k) {
+          if ((k % kEpiThreads) != tid) continue;
+          Unit un;
+          decode_unit(p, tiles_m, tiles_n, u, un);
+          const long long row0 = static_cast<long long>(un.m_blk) * (kBM * kG) + cta_rank * kBM;
+          if (row0 < p.m) {
+            const int owner = static_cast<int>(row0 / p.rows_per_rank);
+            const int rblk = static_cast<int>((row0 - static_cast<long long>(owner) * p.rows_per_rank) / kBM);
+            st_release_sys_u32(p.flags[owner] + (static_cast<size_t>(p.slice_base + un.slice) * rblks + rblk) * tiles_n +
+                                   un.n_blk,
+                               p.epoch);
+          }
+        }
+      }
     }
     if (p.epilogue == kEpiPartialF32 && ok && p.out != nullptr) {
       // ---- reduce-scatter tail (skipped when the caller only wants the partials staged): the rows this rank owns, slices combined by a balanced tree

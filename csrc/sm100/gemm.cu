@@ -77,6 +77,12 @@ __device__ __forceinline__ void decode_unit(const GemmParams& p, int tiles_m, in
   out.m_blk = g * kGroupM + (r - out.n_blk * gm);
   // all-gather mode: start with the row tiles whose source is this rank, they need no wait
   if (p.a_gather) out.m_blk = (out.m_blk + (p.rank * p.a_rows_per_rank) / (kBM * kG)) % tiles_m;
+  // reduce-scatter mode: start with the row tiles this rank owns, then the next rank's, ... so
+  // that at any time every rank stores to a different owner; with one order for all ranks
+  // everybody would send to rank 0 first, then to rank 1, ... and each owner's link in turn
+  // would carry the whole traffic while the others idle
+  if (p.epilogue == kEpiPartialF32 && p.world > 1)
+    out.m_blk = (out.m_blk + static_cast<int>((static_cast<long long>(p.rank) * p.rows_per_rank) / (kBM * kG))) % tiles_m;
 }
 
 __device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory"); }

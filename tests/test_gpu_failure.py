@@ -42,3 +42,46 @@ def test_all_reduce_wait_runs_out_and_reports(cuda_device):
     assert torch.equal(bufs[0], torch.ones(n, device=cuda_device))  # nothing was reduced
     # the context is intact: ordinary work still runs
     assert (torch.arange(10, device=cuda_device).sum().item()) == 45
+
+
+def test_fused_logp_gather_wait_runs_out_and_reports(cuda_device):
+    """Row-sharded fused log-prob as "rank 0" of two whose peer never launches: the kernel works
+    through its own rows, pushes them to the peer's arena (memory of this GPU here), waits for
+    the peer's rows at the gather flag, runs into the 100 ms limit, reports the site and
+    returns; nothing hangs and the context stays usable."""
+    lib = _native.cuda()
+    m_local, k, vocab, panel = 512, 256, 4096, 1024
+    g = torch.Generator(device=cuda_device).manual_seed(0)
+    h = torch.randn(m_local, k, device=cuda_device, generator=g).to(torch.bfloat16)
+    w = (torch.randn(vocab // 2, k, device=cuda_device, generator=g) * 0.02).to(torch.bfloat16)   # slices 0..3
+    ids = torch.randint(0, vocab, (m_local,), device=cuda_device, generator=g)
+    logp = torch.zeros(m_local, device=cuda_device)
+    ws_bytes = lib.ka_lmhead_logp_workspace_bytes(vocab, panel)
+    ws = torch.zeros(ws_bytes, dtype=torch.uint8, device=cuda_device)
+    xb = lib.ka_lmhead_logp_exchange_bytes(2, panel)
+    gb = lib.ka_lmhead_logp_gather_bytes(2, panel, k)
+    exch = [torch.zeros(xb, dtype=torch.uint8, device=cuda_device) for _ in range(2)]
+    gath = [torch.zeros(gb, dtype=torch.uint8, device=cuda_device) for _ in range(2)]
+    xp = (c_void_p * 2)(*[t.data_ptr() for t in exch])
+    gp = (c_void_p * 2)(*[t.data_ptr() for t in gath])
+    sms = torch.cuda.get_device_properties(cuda_device).multi_processor_count
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    rc = lib.ka_lmhead_logp_forward_sharded(
+        h.data_ptr(), w.data_ptr(), ids.data_ptr(), logp.data_ptr(), None, ws.data_ptr(), ws_bytes, xp, gp,
+        m_local, k, vocab, vocab // 2, 0, 2, 0, 1, 1.0, panel, 0, 2, 0, 0, 0, sms, 100_000_000,
+        torch.cuda.current_stream().cuda_stream)
+    t1.record()
+    torch.cuda.synchronize()
+    assert rc == 0
+    off = lib.ka_lmhead_logp_status_offset(vocab, panel)
+    st = ws[off:off + 32].view(torch.int32).cpu().tolist()
+    # a wait ran out: normally the producer's wait for the peer's rows (site 6), which starts first;
+    # the waits downstream of it (operands 2, accumulator 4, the peer's partial results 5) are also legitimate
+    assert st[0] in (1, 2) and st[1] in (2, 4, 5, 6), st
+    assert 90 < t0.elapsed_time(t1) < 3000
+    # this rank's rows did reach the "peer": the pusher does not depend on anybody
+    pl = panel // 2
+    pushed = gath[1][: 2 * 2 * pl * k * 2].view(torch.bfloat16).view(2, 2, pl, k)[1, 0, :m_local]   # generation 1 (epoch 1), source 0
+    assert torch.equal(pushed, h)
+    assert (torch.arange(10, device=cuda_device).sum().item()) == 45

@@ -6,10 +6,13 @@
 
 One step = log-probabilities of G*L target tokens given hidden states [G*L, 4096] (bf16)
 and the LM-head weight [128256, 4096] (bf16), G=256, L=512, synthetic N(0,1) / N(0,0.02)
-data. Own arm: the fused tcgen05 LM-head+logprob kernel; on N > 1 GPUs the vocabulary is
-sharded over the ranks and so are the rows: every rank receives G*L/N rows, the kernel pushes
-them to the peers over NVLink while it computes, exchanges the partial (max, sum-exp, target)
-triples the same way, and every rank ends with the results of its own rows. Reference arm:
+data. Own arm: the fused tcgen05 LM-head+logprob kernel. On N > 1 GPUs the headline is the
+layout of the reference arm: every rank holds the whole LM head and receives G*L/N rows, no
+communication inside the step. The vocabulary-parallel layout is timed as well and reported
+under ``other_layout``: vocabulary and rows sharded over the ranks, the kernel pushes the rows to
+the peers over NVLink while it computes, exchanges the partial (max, sum-exp, target) triples
+the same way, and every rank ends with the results of its own rows (what a model with a
+tensor-parallel LM head needs; ``--layout vocab`` makes it the headline). Reference arm:
 `torch.matmul` (cuBLAS) feeding the reference's `SamplerBackend.compute_logp` from
 baseline/_ref, rows split over the ranks (the reference has no distributed code, so data
 parallelism over rows is the only way to use it unmodified on N GPUs).
@@ -232,6 +235,68 @@ def time_sampling(sample, calls: int = 30) -> dict:
     return out
 
 
+def all_ranks_ok(ok: bool, world: int) -> bool:
+    """True when ``ok`` holds on every rank (so that all ranks take the same branch)."""
+    if world == 1:
+        return ok
+    t = torch.tensor([0 if ok else 1], dtype=torch.int32, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return int(t.item()) == 0
+
+
+def measure_own_layout(layout, args, rank, world, local, sampler, fused_logp):
+    """Device-timed and end-to-end step of one layout of the own arm.
+
+    ``rows``   every rank holds the whole LM head and takes G*L/N rows: no communication, the
+               layout of the reference arm.
+    ``vocab``  vocabulary and rows sharded; the kernel gathers the rows over NVLink and exchanges
+               the partial (max, sum-exp, target) triples, every rank ends with its own rows.
+    """
+    rows = args.g * args.seq_len
+    rows_local = rows // world
+    extra = fused_logp.workspace_bytes(VOCAB)
+    kw = dict(vocab=VOCAB)
+    if layout == "vocab":
+        from kernel_align_b200 import _native
+        from kernel_align_b200.parallel.peer import gather_arena_bytes, vocab_parallel_group
+
+        lo, hi = fused_logp.vocab_shard_range(VOCAB, rank, world)
+        group = vocab_parallel_group(VOCAB)
+        kw.update(group=group, row_sharded=True)
+        extra += int(_native.cuda().ka_lmhead_logp_exchange_bytes(world, group.panel_rows))
+        extra += gather_arena_bytes(group, HIDDEN)
+        n_panels = -(-rows // fused_logp.DEFAULT_PANEL_ROWS)
+        name = f"vp{world} (vocabulary sharded, rows sharded and gathered in-kernel)"
+    else:
+        lo, hi = 0, VOCAB
+        n_panels = -(-rows_local // fused_logp.DEFAULT_PANEL_ROWS)
+        name = f"dp{world} (rows split, full vocabulary per rank)" if world > 1 else "single"
+    hidden, weight, ids = make_inputs(rows, hi - lo, seed=1234)
+    hidden = hidden[rank * rows_local:(rank + 1) * rows_local].clone()
+    ids = ids[rank * rows_local:(rank + 1) * rows_local].clone()
+
+    ms, clock_info = time_device(lambda: sampler.fused_logp(hidden, weight, ids, **kw), args, world, local)
+    status = fused_logp.last_status(hidden.device, VOCAB)
+    if not all_ranks_ok(int(status[0]) == 0, world):
+        fused_logp.check_status(status)
+        raise RuntimeError("a peer rank reported a device-side timeout")
+
+    # ---- end to end through the public API: pinned host inputs in, log-probs out, per step
+    h_host = hidden.cpu().pin_memory()
+    ids_host = ids.cpu().pin_memory()
+    out_host = torch.empty(rows_local, dtype=torch.float32).pin_memory()
+    e2e_ms = time_end_to_end(lambda h, i: sampler.fused_logp(h, weight, i, **kw), h_host, ids_host, out_host, args,
+                             world)
+    status = fused_logp.last_status(hidden.device, VOCAB)
+    if not all_ranks_ok(int(status[0]) == 0, world):
+        fused_logp.check_status(status)
+        raise RuntimeError("a peer rank reported a device-side timeout")
+    return {"parallelism": name, "ms_per_step": ms, "clocks": clock_info, "e2e_ms_per_step": e2e_ms,
+            "h2d_bytes_per_step": (h_host.numel() * 2 + ids_host.numel() * 8) * world,
+            "d2h_bytes_per_step": out_host.numel() * 4 * world, "extra_vram_bytes": extra,
+            "gpu_launches": args.steps * n_panels}
+
+
 def run_own(args, rank, world, local):
     sys.path.insert(0, ROOT)
     from kernel_align_b200.kernels.sampling import SamplerBackend
@@ -240,60 +305,51 @@ def run_own(args, rank, world, local):
     rows = args.g * args.seq_len
     if rows % world:
         raise SystemExit("G * L must be divisible by the number of GPUs")
-    rows_local = rows // world
-    lo, hi = fused_logp.vocab_shard_range(VOCAB, rank, world)
     sampler = SamplerBackend()
     sampling = None
     if rank == 0:
         sampling = time_sampling(lambda x: sampler.sample(x, top_k=50, top_p=0.9, temperature=0.7))
-    hidden, weight, ids = make_inputs(rows, hi - lo, seed=1234)
-    # every rank keeps only its rows of the batch; the kernel gathers the others over NVLink
-    hidden = hidden[rank * rows_local:(rank + 1) * rows_local].clone()
-    ids = ids[rank * rows_local:(rank + 1) * rows_local].clone()
-    group = None
-    extra = fused_logp.workspace_bytes(VOCAB)
-    kw = dict(vocab=VOCAB)
-    if world > 1:
-        from kernel_align_b200 import _native
-        from kernel_align_b200.parallel.peer import gather_arena_bytes, vocab_parallel_group
+    if world == 1:
+        layouts = ["rows"]
+    elif args.layout == "auto":
+        layouts = ["rows", "vocab"]   # the first one is the headline, the second a further record
+    else:
+        layouts = [args.layout]
+    head = measure_own_layout(layouts[0], args, rank, world, local, sampler, fused_logp)
+    other = None
+    for layout in layouts[1:]:
+        torch.cuda.empty_cache()
+        try:
+            r = measure_own_layout(layout, args, rank, world, local, sampler, fused_logp)
+            other = {"parallelism": r["parallelism"], "ms_per_step": r["ms_per_step"],
+                     "tokens_per_s": rows / r["ms_per_step"] * 1e3, "e2e_ms_per_step": r["e2e_ms_per_step"],
+                     "e2e_tokens_per_s": rows / r["e2e_ms_per_step"] * 1e3, "extra_vram_bytes": r["extra_vram_bytes"],
+                     "clocks": r["clocks"]}
+        except Exception as e:  # noqa: BLE001  (all ranks leave together: see all_ranks_ok)
+            other = {"parallelism": layout, "unavailable": f"{type(e).__name__}: {str(e)[:200]}"}
 
-        group = vocab_parallel_group(VOCAB)
-        kw.update(group=group, row_sharded=True)
-        extra += int(_native.cuda().ka_lmhead_logp_exchange_bytes(world, group.panel_rows))
-        extra += gather_arena_bytes(group, HIDDEN)
-    n_panels = -(-rows // fused_logp.DEFAULT_PANEL_ROWS)
-
-    ms, clock_info = time_device(lambda: sampler.fused_logp(hidden, weight, ids, **kw), args, world, local)
-    fused_logp.check_status(fused_logp.last_status(hidden.device, VOCAB))
-
-    # ---- end to end through the public API: pinned host inputs in, log-probs out, per step
-    h_host = hidden.cpu().pin_memory()
-    ids_host = ids.cpu().pin_memory()
-    out_host = torch.empty(rows_local, dtype=torch.float32).pin_memory()
-    e2e_ms = time_end_to_end(lambda h, i: sampler.fused_logp(h, weight, i, **kw), h_host, ids_host, out_host, args,
-                             world)
-    fused_logp.check_status(fused_logp.last_status(hidden.device, VOCAB))
-
+    ms, e2e_ms = head["ms_per_step"], head["e2e_ms_per_step"]
     value = rows / ms * 1e3
-    return {
+    line = {
         "metric": "grpo_logp_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": (value / BASELINE_TOKENS_PER_S) if BASELINE_TOKENS_PER_S else None,
         "dtype": "bf16", "data": "synthetic",
         "config": {"model": "Llama-3-8B LM head (V=128256, d=4096)", "global_batch": args.g, "seq_len": args.seq_len,
-                   "parallelism": f"vp{world} (vocabulary sharded, rows sharded and gathered in-kernel)"
-                   if world > 1 else "single",
-                   "l2": "inputs (hidden rows + vocab shard) larger than the 126 MB L2",
-                   "extra_vram_bytes": extra},
-        "clocks": clock_info,
+                   "parallelism": head["parallelism"],
+                   "l2": "inputs (hidden rows + LM head) larger than the 126 MB L2",
+                   "extra_vram_bytes": head["extra_vram_bytes"]},
+        "clocks": head["clocks"],
         "e2e": {"value": rows / e2e_ms * 1e3, "unit": "tokens/s", "ms_per_step": e2e_ms,
-                "h2d_bytes_per_step": (h_host.numel() * 2 + ids_host.numel() * 8) * world,
-                "d2h_bytes_per_step": out_host.numel() * 4 * world,
+                "h2d_bytes_per_step": head["h2d_bytes_per_step"], "d2h_bytes_per_step": head["d2h_bytes_per_step"],
                 "staging": "double-buffered H2D on a copy stream, total bytes over all ranks"},
         "sampling": sampling, "sampling_config": SAMPLING_CONFIG,
-        "gpu_launches": args.steps * n_panels,
+        "gpu_launches": head["gpu_launches"],
         "impl": "own",
     }
+    if other is not None:
+        line["other_layout"] = other
+    return line
 
 
 def run_reference(args, rank, world, local):
@@ -362,6 +418,10 @@ def main():
     ap.add_argument("--impl", choices=["own", "reference"], default="own")
     ap.add_argument("--g", type=int, default=256, help="group size G (rows = G * seq_len)")
     ap.add_argument("--seq-len", type=int, default=512)
+    ap.add_argument("--layout", choices=["auto", "rows", "vocab"], default="auto",
+                    help="own arm on N > 1 GPUs: rows split (full LM head per rank), vocabulary-parallel with "
+                         "the in-kernel row gather, or (auto) the first as the headline and the second as a "
+                         "further record")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

@@ -110,7 +110,10 @@ def check_status(ws_status: torch.Tensor) -> None:
 _SCHEDULES = [(2, 8, 0, 0), (2, 8, 0, 2), (2, 8, 2, 3), (2, 4, 2, 3), (2, 4, 1, 0), (1, 4, 0, 1), (1, 4, 0, 0),
               (1, 2, 0, 3), (1, 4, 2, 3)]
 _TUNE_MIN_MS = 250.0      # a candidate runs at least this long: the clock settles under the power cap
-_DEFAULT_SCHEDULE = (2, 0, 0, 0)
+# Calls too short to be worth timing take the CTA pair, four sub-slices side by side, row tiles
+# fastest: 16384 / 32768 rows against the whole 128256-column head took 13.4 / 28.2 ms with it,
+# 14.1 / 29.5 ms with the kernel's own choice of the group (cg 0), 13.9 / 28.9 ms with (2, 8, 2, 3).
+_DEFAULT_SCHEDULE = (2, 4, 1, 0)
 # A shard of the LM head that about fits the L2 twice over (a vocabulary sharded 4 or 8 ways) is
 # walked W-stationary with the keep-W hint: 12.9 ms against 13.5 - 14.0 ms for the default order
 # on a 16128-column shard, in a burst and at the power cap alike.

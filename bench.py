@@ -145,6 +145,18 @@ def make_inputs(rows: int, v_rows: int, seed: int):
     return hidden, weight, ids
 
 
+def settle(first_call, args):
+    """Set-up work outside the measurements, the same for both arms: one call of the step
+    (library initialisation, schedule timing, allocator growth), then an idle pause. Each of
+    the two timed loops (device, end to end) then starts from the same state, W warm-up calls
+    after a pause, instead of the second one inheriting the heat of the first: on these
+    power-capped GPUs a loop that follows seconds of load ran up to 14 % slower."""
+    if first_call is not None:
+        first_call()
+    torch.cuda.synchronize()
+    time.sleep(args.cooldown)
+
+
 def time_device(step, args, world, local):
     """W warm-up calls, then K calls between two CUDA events; max over ranks, with the clocks
     sampled while the timed calls run."""
@@ -275,6 +287,7 @@ def measure_own_layout(layout, args, rank, world, local, sampler, fused_logp):
     hidden = hidden[rank * rows_local:(rank + 1) * rows_local].clone()
     ids = ids[rank * rows_local:(rank + 1) * rows_local].clone()
 
+    settle(lambda: sampler.fused_logp(hidden, weight, ids, **kw), args)   # the first call times the schedules
     ms, clock_info = time_device(lambda: sampler.fused_logp(hidden, weight, ids, **kw), args, world, local)
     status = fused_logp.last_status(hidden.device, VOCAB)
     if not all_ranks_ok(int(status[0]) == 0, world):
@@ -285,6 +298,7 @@ def measure_own_layout(layout, args, rank, world, local, sampler, fused_logp):
     h_host = hidden.cpu().pin_memory()
     ids_host = ids.cpu().pin_memory()
     out_host = torch.empty(rows_local, dtype=torch.float32).pin_memory()
+    settle(None, args)
     e2e_ms = time_end_to_end(lambda h, i: sampler.fused_logp(h, weight, i, **kw), h_host, ids_host, out_host, args,
                              world)
     status = fused_logp.last_status(hidden.device, VOCAB)
@@ -338,6 +352,7 @@ def run_own(args, rank, world, local):
         "config": {"model": "Llama-3-8B LM head (V=128256, d=4096)", "global_batch": args.g, "seq_len": args.seq_len,
                    "parallelism": head["parallelism"],
                    "l2": "inputs (hidden rows + LM head) larger than the 126 MB L2",
+                   "idle_s_before_each_timed_loop": args.cooldown,
                    "extra_vram_bytes": head["extra_vram_bytes"]},
         "clocks": head["clocks"],
         "e2e": {"value": rows / e2e_ms * 1e3, "unit": "tokens/s", "ms_per_step": e2e_ms,
@@ -382,12 +397,14 @@ def run_reference(args, rank, world, local):
         logits = torch.matmul(h, weight.t()).view(g_local, args.seq_len, VOCAB)
         return sampler.compute_logp(logits, i)
 
+    settle(lambda: step(hidden, ids), args)
     ms, clock_info = time_device(lambda: step(hidden, ids), args, world, local)
     peak = torch.cuda.max_memory_allocated()
 
     h_host = hidden.cpu().pin_memory()
     ids_host = ids.cpu().pin_memory()
     out_host = torch.empty(g_local, args.seq_len, dtype=hidden.dtype).pin_memory()
+    settle(None, args)
     e2e_ms = time_end_to_end(step, h_host, ids_host, out_host, args, world)
     value = rows / ms * 1e3
     return {
@@ -397,6 +414,7 @@ def run_reference(args, rank, world, local):
         "config": {"model": "Llama-3-8B LM head (V=128256, d=4096)", "global_batch": args.g, "seq_len": args.seq_len,
                    "parallelism": f"dp{world} (rows split, full vocabulary per rank)" if world > 1 else "single",
                    "l2": "inputs and logits larger than the 126 MB L2",
+                   "idle_s_before_each_timed_loop": args.cooldown,
                    "path": "torch.matmul (cuBLAS) -> rl_engine SamplerBackend.compute_logp",
                    "peak_allocated_bytes": peak},
         "clocks": clock_info,
@@ -418,6 +436,9 @@ def main():
     ap.add_argument("--impl", choices=["own", "reference"], default="own")
     ap.add_argument("--g", type=int, default=256, help="group size G (rows = G * seq_len)")
     ap.add_argument("--seq-len", type=int, default=512)
+    ap.add_argument("--cooldown", type=float, default=4.0,
+                    help="idle seconds before each timed loop (after set-up, and between the device and the "
+                         "end-to-end loop), both arms")
     ap.add_argument("--layout", choices=["auto", "rows", "vocab"], default="auto",
                     help="own arm on N > 1 GPUs: rows split (full LM head per rank), vocabulary-parallel with "
                          "the in-kernel row gather, or (auto) the first as the headline and the second as a "

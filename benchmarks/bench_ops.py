@@ -213,6 +213,15 @@ def main():
                 print("reference sampler unavailable:", type(e).__name__, str(e)[:200])
         by = lgs.numel() * 2
         rec(f"sampling G={gsz} V=128256 k=50 p=0.9", t, tb, by / t / 1e6 / hbm, f"{by / t / 1e6:.0f} GB/s of logits")
+        # no top-k (threshold search in a per-key count histogram for bf16 rows)
+        t = time_cuda(lambda: sample(lgs, top_k=None, top_p=0.9, temperature=0.7, seed=1, step=0))
+        tb = None
+        if args.reference_sampler:
+            try:
+                tb = time_cuda(lambda: ref.sample(lgs, top_k=None, top_p=0.9, temperature=0.7), warmup=5)
+            except Exception as e:  # noqa: BLE001
+                print("reference sampler unavailable:", type(e).__name__, str(e)[:200])
+        rec(f"sampling G={gsz} V=128256 p=0.9 only", t, tb, by / t / 1e6 / hbm, f"{by / t / 1e6:.0f} GB/s of logits")
     for name, fn, base, nbytes in small_op_cases(dev, g):
         t = time_cuda(fn, iters=5)
         tb = time_cuda(base, iters=5) if base is not None else None

@@ -87,3 +87,23 @@ def test_sampler_backend_module(cuda_device):
     assert torch.equal(s.sample(logits, top_k=20, top_p=0.9, temperature=0.8), a)
     assert torch.equal(s.sample(logits, top_k=20, top_p=0.9, temperature=0.8), b)
     assert torch.equal(s.sample(logits, top_k=1).long(), logits.float().argmax(-1))
+
+
+def test_sampler_bf16_without_top_k_threshold_among_negative_values_and_nan(cuda_device):
+    """bf16 rows without a (small) top-k search their threshold in a per-key count histogram,
+    non-negative keys first; rows whose threshold lies among negative values, rows with NaN / inf
+    entries and a Llama-sized vocabulary must give the CPU library's token."""
+    g = torch.Generator(device=cuda_device).manual_seed(11)
+    neg = (-torch.randn(6, 128256, device=cuda_device, generator=g).abs() * 2 - 1).to(torch.bfloat16)
+    mixed = (torch.randn(6, 128256, device=cuda_device, generator=g) * 2).to(torch.bfloat16)
+    odd = mixed.clone()
+    odd[0, 5] = float("nan")
+    odd[1, 77] = float("-inf")
+    odd[2, :100] = float("nan")
+    odd[3, 9] = 0.0
+    odd[3, 10] = -0.0
+    for name, logits in (("neg", neg), ("mixed", mixed), ("odd", odd)):
+        for top_k, top_p, temp in ((None, 0.9, 0.7), (None, 0.999, 1.0), (None, 0.3, 1.5), (5000, 0.95, 0.7),
+                                   (100000, None, 1.0), (None, None, 1.0)):
+            tok = sample(logits, top_k=top_k, top_p=top_p, temperature=temp, seed=21, step=4)
+            assert torch.equal(tok.cpu(), _cpu(logits, top_k, top_p, temp, 21, 4)), (name, top_k, top_p, temp)

@@ -22,7 +22,7 @@ def main():
     ap.add_argument("--op", required=True,
                     choices=["fused_logp", "logits_logp", "sampling", "rmsnorm", "swiglu", "gemm", "attention", "attention_bwd",
                              "grpo_loss", "rope", "adamw", "decode_attention", "gemm_skinny", "rmsnorm_bwd", "logp_bwd",
-                             "decode_qkv"])
+                             "decode_qkv", "sampling_top_p"])
     ap.add_argument("--rows", type=int, default=4736)
     ap.add_argument("--vocab", type=int, default=128256)
     ap.add_argument("--hidden", type=int, default=4096)
@@ -51,6 +51,11 @@ def main():
 
         x = (torch.randn(args.rows, args.vocab, device=dev, generator=g) * 2).to(torch.bfloat16)
         fn = lambda: sample(x, top_k=50, top_p=0.9, temperature=0.7, seed=1, step=0)  # noqa: E731
+    elif args.op == "sampling_top_p":       # no top-k: sample_general_kernel
+        from kernel_align_b200.ops.sampling import sample
+
+        x = (torch.randn(args.rows, args.vocab, device=dev, generator=g) * 2).to(torch.bfloat16)
+        fn = lambda: sample(x, top_k=None, top_p=0.9, temperature=0.7, seed=1, step=0)  # noqa: E731
     elif args.op == "rmsnorm":
         from kernel_align_b200.ops.layer_ops import rmsnorm
 

@@ -134,6 +134,29 @@ def max_over_ranks(value: float, world: int) -> float:
     return float(t.item())
 
 
+class Deadline:
+    """Ends the process with status 0 after ``seconds`` unless cancelled, rank 0 first printing
+    ``make_line()``: the headline of a run must not be lost to a further, optional measurement
+    that does not come back (ranks that fell out of step wait in a collective for minutes)."""
+
+    def __init__(self, seconds: float, rank: int, make_line):
+        self.rank, self.make_line = rank, make_line
+        self.timer = threading.Timer(seconds, self._fire)
+        self.timer.daemon = True
+
+    def start(self):
+        self.timer.start()
+        return self
+
+    def cancel(self):
+        self.timer.cancel()
+
+    def _fire(self):
+        if self.rank == 0:
+            print(json.dumps(self.make_line()), flush=True)
+        os._exit(0)
+
+
 def make_inputs(rows: int, v_rows: int, seed: int):
     gen = torch.Generator(device="cuda").manual_seed(seed)
     hidden = torch.randn(rows, HIDDEN, device="cuda", generator=gen, dtype=torch.float32).to(torch.bfloat16)
@@ -330,18 +353,6 @@ def run_own(args, rank, world, local):
     else:
         layouts = [args.layout]
     head = measure_own_layout(layouts[0], args, rank, world, local, sampler, fused_logp)
-    other = None
-    for layout in layouts[1:]:
-        torch.cuda.empty_cache()
-        try:
-            r = measure_own_layout(layout, args, rank, world, local, sampler, fused_logp)
-            other = {"parallelism": r["parallelism"], "ms_per_step": r["ms_per_step"],
-                     "tokens_per_s": rows / r["ms_per_step"] * 1e3, "e2e_ms_per_step": r["e2e_ms_per_step"],
-                     "e2e_tokens_per_s": rows / r["e2e_ms_per_step"] * 1e3, "extra_vram_bytes": r["extra_vram_bytes"],
-                     "clocks": r["clocks"]}
-        except Exception as e:  # noqa: BLE001  (all ranks leave together: see all_ranks_ok)
-            other = {"parallelism": layout, "unavailable": f"{type(e).__name__}: {str(e)[:200]}"}
-
     ms, e2e_ms = head["ms_per_step"], head["e2e_ms_per_step"]
     value = rows / ms * 1e3
     line = {
@@ -362,7 +373,20 @@ def run_own(args, rank, world, local):
         "gpu_launches": head["gpu_launches"],
         "impl": "own",
     }
-    if other is not None:
+    for layout in layouts[1:]:
+        # the headline is measured; the further record must not be able to lose it
+        late = {"parallelism": layout, "unavailable": f"did not finish within {args.other_timeout:.0f} s"}
+        deadline = Deadline(args.other_timeout, rank, lambda: {**line, "other_layout": late}).start()
+        torch.cuda.empty_cache()
+        try:
+            r = measure_own_layout(layout, args, rank, world, local, sampler, fused_logp)
+            other = {"parallelism": r["parallelism"], "ms_per_step": r["ms_per_step"],
+                     "tokens_per_s": rows / r["ms_per_step"] * 1e3, "e2e_ms_per_step": r["e2e_ms_per_step"],
+                     "e2e_tokens_per_s": rows / r["e2e_ms_per_step"] * 1e3, "extra_vram_bytes": r["extra_vram_bytes"],
+                     "clocks": r["clocks"]}
+        except Exception as e:  # noqa: BLE001  (all ranks leave together: see all_ranks_ok)
+            other = {"parallelism": layout, "unavailable": f"{type(e).__name__}: {str(e)[:200]}"}
+        deadline.cancel()
         line["other_layout"] = other
     return line
 
@@ -439,6 +463,9 @@ def main():
     ap.add_argument("--cooldown", type=float, default=4.0,
                     help="idle seconds before each timed loop (after set-up, and between the device and the "
                          "end-to-end loop), both arms")
+    ap.add_argument("--other-timeout", type=float, default=150.0,
+                    help="seconds the further layout record of the own arm may take before the run ends with "
+                         "the headline alone")
     ap.add_argument("--layout", choices=["auto", "rows", "vocab"], default="auto",
                     help="own arm on N > 1 GPUs: rows split (full LM head per rank), vocabulary-parallel with "
                          "the in-kernel row gather, or (auto) the first as the headline and the second as a "
@@ -458,8 +485,14 @@ def main():
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+        # the line is out: a rank that cannot leave the group in a minute ends anyway, with status 0
+        guard = Deadline(60.0, -1, dict).start()
+        try:
+            dist.barrier()
+            dist.destroy_process_group()
+        except Exception as e:  # noqa: BLE001
+            print(f"bench.py: leaving the process group failed: {type(e).__name__}: {e}", file=sys.stderr)
+        guard.cancel()
 
 
 if __name__ == "__main__":

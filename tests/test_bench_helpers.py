@@ -65,3 +65,31 @@ def test_bench_without_a_gpu_prints_one_json_line_and_exits_zero():
         assert r.returncode == 0, r.stderr[-500:]
         line = json.loads(r.stdout.strip().splitlines()[-1])
         assert line["impl"] == impl and "unavailable" in line
+
+
+def test_deadline_prints_the_line_on_rank_zero_and_ends_the_process_with_status_zero():
+    code = (
+        "import importlib.util, time, sys\n"
+        f"spec = importlib.util.spec_from_file_location('ka_bench', {os.path.join(ROOT, 'bench.py')!r})\n"
+        "m = importlib.util.module_from_spec(spec); spec.loader.exec_module(m)\n"
+        "rank = int(sys.argv[1])\n"
+        "m.Deadline(0.3, rank, lambda: {'value': 1.5, 'other_layout': {'unavailable': 'late'}}).start()\n"
+        "time.sleep(20)\n"
+        "print('not reached')\n"
+    )
+    for rank, want in ((0, {"value": 1.5, "other_layout": {"unavailable": "late"}}), (1, None)):
+        r = subprocess.run([sys.executable, "-c", code, str(rank)], capture_output=True, text=True, timeout=120)
+        assert r.returncode == 0 and "not reached" not in r.stdout
+        if want is None:
+            assert r.stdout.strip() == ""
+        else:
+            assert json.loads(r.stdout.strip()) == want
+
+
+def test_deadline_cancelled_in_time_does_nothing():
+    bench = _bench()
+    d = bench.Deadline(0.2, 0, lambda: {"never": True}).start()
+    d.cancel()
+    import time
+
+    time.sleep(0.5)   # the process is still here
